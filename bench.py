@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the recurrent-scan hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the D-LinOSS imex1 scan over one
+synthetic batch at the op boundary (``bu`` and the upstream gradient in,
+``x``, ``grad_bu`` and the three coefficient gradients out).  The workload is
+BASELINE.json's config 1 (B=64, L=4096, P=256 oscillators, fp32 / complex64).
+With N > 1 (launched by torchrun, one rank per GPU) every rank scans its own
+256-oscillator shard of a P = 256*N layer: the series are independent, so there
+is no data-path collective (weak scaling).
+
+Prints ONE JSON line (rank 0).  ``value`` is scan elements (B*L*P) per second
+with inputs resident in HBM; ``e2e`` is the same metric through the public op
+(``ossm_b200.dlinoss.run_dlinoss`` + autograd) with pinned HOST buffers, the
+host->device and device->host copies inside the timed region.
+
+``--impl reference`` times the reference's own compiled CPU kernels
+(``oracle/_ref``, built from the ossm checkout by ``oracle/build_ref.py``) on
+the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "dlinoss_scan_fwd_bwd_gelem_per_s"
+UNIT = "Gelem/s"
+FWD_BYTES = 16      # read bu 8 + write x 8                        (per scan element)
+BWD_BYTES = 24      # read grad_x 8 + read bu 8 + write grad_bu 8  (per scan element)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", default="imex1")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--length", type=int, default=4096)
+    ap.add_argument("--ssm", type=int, default=256, help="oscillators per GPU")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-batch", type=int, default=8, help="batch slice timed on the host cores")
+    return ap.parse_args()
+
+
+def workload_name(args):
+    return (f"D-LinOSS {args.variant} scan fwd+bwd at the op boundary, B={args.batch} L={args.length} "
+            f"P={args.ssm} per GPU, complex64 (BASELINE config 1)")
+
+
+def make_params(P, device, seed):
+    """BASELINE config 0/1 distributions: A=relu(N), G=relu(N), dt=sigmoid(N)."""
+    import torch
+
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    a = torch.relu(torch.randn(P, generator=gen))
+    g = torch.relu(torch.randn(P, generator=gen))
+    dt = torch.sigmoid(torch.randn(P, generator=gen))
+    return a.to(device), g.to(device), dt.to(device)
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------
+# reference CPU arm / cpu_baseline
+# ---------------------------------------------------------------------------
+def time_reference_cpu(args, min_seconds, max_steps, warmup):
+    """Times the reference's compiled CPU kernels (fwd + bwd) on a batch slice of
+    the workload.  Returns (Gelem/s, description dict) or (None, reason)."""
+    import torch
+    from oracle.ref_loader import load_reference_kernels
+
+    ref = load_reference_kernels()
+    if ref is None:
+        return None, "oracle/_ref/ossm_ref_kernels.so not built (run oracle/build_ref.py where the ossm checkout is)"
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    L, B, P = args.length, min(args.cpu_batch, args.batch), args.ssm
+    a, g, dt = make_params(P, "cpu", 0)
+    gen = torch.Generator().manual_seed(1)
+    bu = torch.complex(torch.randn(L, B, P, generator=gen), torch.randn(L, B, P, generator=gen)) * 0.5
+    gx = torch.complex(torch.randn(L, B, P, generator=gen), torch.randn(L, B, P, generator=gen))
+    fwd = getattr(ref, f"dlinoss_{args.variant}_forward")
+    bwd = getattr(ref, f"dlinoss_{args.variant}_backward")
+
+    def step():
+        states = fwd(a, g, dt, bu)
+        return bwd(a, g, dt, bu, states, gx)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_steps and (len(times) < 3 or time.perf_counter() - t_start < min_seconds):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    sec = statistics.mean(times)
+    elems = L * B * P
+    desc = {
+        "kind": "reference", "cores": cores,
+        "sample": (f"reference CPU kernels dlinoss_{args.variant}_forward+backward (ossm csrc, -O3 -ffast-math, "
+                   f"at::parallel_for over {cores} threads) on a batch slice B={B} of the workload "
+                   f"(L={L}, P={P}); {len(times)} steps of {sec * 1e3:.1f} ms"),
+        "ms_per_step": sec * 1e3, "steps": len(times),
+    }
+    return elems / sec / 1e9, desc
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    val, desc = time_reference_cpu(args, min_seconds=20.0, max_steps=max(args.steps, 3), warmup=min(args.warmup, 2))
+    if val is None:
+        print(json.dumps({"impl": "reference", "unavailable": desc}))
+        return
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": desc["steps"], "warmup": min(args.warmup, 2), "ms_per_step": desc["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "timing": "host wall clock, CPU tensors"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "kind": desc["kind"], "cores": desc["cores"],
+                         "sample": desc["sample"]},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ossm_b200 import _lib, kernels
+    from ossm_b200.dlinoss import run_dlinoss
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the scan has no CPU path; use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    L, B, P = args.length, args.batch, args.ssm
+    variant = args.variant
+    a, g, dt = make_params(P, dev, seed=rank)         # this rank's oscillator shard
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    bu = torch.randn(L, B, P, 2, generator=gen, device=dev)
+    bu = torch.view_as_complex(bu.mul_(0.5))
+    gx = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev))
+    elems = L * B * P
+
+    def step(record=None):
+        if record is not None:
+            record[0].record()
+        x, _, carries = kernels.lti_scan_forward(variant, a, g, dt, bu)
+        if record is not None:
+            record[1].record()
+        grads = kernels.lti_scan_backward(variant, a, g, dt, bu, carries, gx)
+        if record is not None:
+            record[2].record()
+        return x, grads
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_begin.record()
+    for i in range(args.steps):
+        step(evs[i])
+    t_end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    total_ms = t_begin.elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    status = _lib.device_status()
+    if status != 0:
+        raise SystemExit(f"bench.py: device status {status} (a bounded wait inside a kernel gave up)")
+    ms_per_step = total_ms / args.steps
+    value = elems * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end-to-end through the public op with host buffers ----------------
+    e2e = None
+    if not args.no_e2e:
+        h_bu = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
+        h_gx = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
+        h_bu.copy_(bu)
+        h_gx.copy_(gx)
+        h_x = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
+        h_gbu = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
+        h_pg = torch.empty((3, P), dtype=torch.float32, pin_memory=True)
+        d_bu = torch.empty_like(bu)
+        d_gx = torch.empty_like(gx)
+
+        def e2e_step():
+            d_bu.copy_(h_bu, non_blocking=True)
+            d_gx.copy_(h_gx, non_blocking=True)
+            a_, g_, dt_ = (t.detach().requires_grad_(True) for t in (a, g, dt))
+            bu_ = d_bu.detach().requires_grad_(True)
+            x = run_dlinoss(variant, a_, g_, dt_, bu_)
+            x.backward(d_gx)
+            h_x.copy_(x.detach(), non_blocking=True)
+            h_gbu.copy_(bu_.grad, non_blocking=True)
+            h_pg[0].copy_(a_.grad, non_blocking=True)
+            h_pg[1].copy_(g_.grad, non_blocking=True)
+            h_pg[2].copy_(dt_.grad, non_blocking=True)
+
+        e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": elems * world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": 2 * elems * 8, "d2h_bytes_per_step": 2 * elems * 8 + 3 * P * 4,
+               "ms_per_step": e2e_ms, "api": "ossm_b200.dlinoss.run_dlinoss + autograd, pinned host buffers"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    bwd_gbs = elems * BWD_BYTES / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = elems * FWD_BYTES / (fwd_ms * 1e-3) / 1e9
+    step_gbs = elems * (FWD_BYTES + BWD_BYTES) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "lti_backward_kernel (dominant; + lti_param_grad_kernel)",
+        "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
+        "traffic": None, "peak_source": peak_src,
+        "algorithmic_bytes_per_launch": elems * BWD_BYTES, "ms_per_launch": bwd_ms,
+        "forward": {"kernel": "lti_forward_kernel", "achieved": fwd_gbs, "frac": fwd_gbs / peak,
+                    "algorithmic_bytes_per_launch": elems * FWD_BYTES, "ms_per_launch": fwd_ms},
+        "step": {"achieved": step_gbs, "frac": step_gbs / peak,
+                 "algorithmic_bytes": elems * (FWD_BYTES + BWD_BYTES)},
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        tr = json.load(open(traffic_file))
+        per_elem = tr.get("lti_backward_kernel", {}).get("dram_bytes_per_elem")
+        if per_elem:
+            roofline["traffic"] = per_elem * elems
+            roofline["traffic_source"] = tr["lti_backward_kernel"].get("source")
+    except Exception:
+        pass
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        val, desc = time_reference_cpu(args, min_seconds=10.0, max_steps=20, warmup=1)
+        if val is not None:
+            cpu_baseline = {"value": val, "unit": UNIT, "cores": desc["cores"], "kind": desc["kind"],
+                            "sample": desc["sample"]}
+        else:
+            cpu_baseline = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                            "sample": "unavailable: " + desc}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "variant": variant, "batch": B, "length": L,
+                   "ssm_per_gpu": P, "sharding": f"oscillators split over {world} GPU(s), no collective",
+                   "l2": "inputs (2 x %d MB) larger than L2, no flush" % (elems * 8 // 2**20)},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+        "gpu_launches": 3 * args.steps, "clocks": clocks,
+        "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,102 @@
+/* ossm_b200 -- C ABI of the B200 (sm_100a) recurrent-scan library.
+ *
+ * Drop-in boundary for the scan hot path of ossm (b-vitamins/ossm): these are
+ * the entry points a binding for `ossm._kernels` calls instead of the
+ * reference's pybind11 functions (src/ossm/csrc/bindings.cpp:159-223).  Plain
+ * pointers and extents only; no allocation, no synchronisation, no exceptions.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device;
+ *   - complex64 buffers are passed as `void*` to interleaved (re, im) float pairs;
+ *   - all tensors are dense and contiguous in the stated layout;
+ *   - kernels are enqueued on `stream` and the call returns immediately;
+ *   - return value 0 = success, negative = error (see OSSM_B200_ERR_*), with a
+ *     per-thread message available from ossm_b200_last_error().
+ */
+#ifndef OSSM_B200_H_
+#define OSSM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ossm_b200_stream_t; /* == cudaStream_t */
+
+#define OSSM_B200_ERR_INVALID_ARGUMENT (-1)
+#define OSSM_B200_ERR_CUDA (-2)
+#define OSSM_B200_ERR_UNSUPPORTED (-3)
+#define OSSM_B200_ERR_WORKSPACE (-4)
+
+/* Recurrence variants of the time-invariant 2x2 oscillator scan. */
+#define OSSM_B200_VARIANT_IMEX1 0       /* D-LinOSS imex1  (_dlinoss_scan.py:54-68)  */
+#define OSSM_B200_VARIANT_IMEX2 1       /* D-LinOSS imex2  (_dlinoss_scan.py:69-75)  */
+#define OSSM_B200_VARIANT_IM 2          /* D-LinOSS im     (_dlinoss_scan.py:76-84)  */
+#define OSSM_B200_VARIANT_EX 3          /* D-LinOSS ex     (_dlinoss_scan.py:85-91)  */
+#define OSSM_B200_VARIANT_LINOSS_IM 4   /* LinOSS IM       (linoss.py:244-251)       */
+#define OSSM_B200_VARIANT_LINOSS_IMEX 5 /* LinOSS IMEX     (linoss.py:253-258)       */
+
+/* ---- library ------------------------------------------------------------ */
+int ossm_b200_version(void);
+const char* ossm_b200_last_error(void);
+/* Reads (and optionally clears) the device status word that a kernel sets when
+ * one of its bounded waits gives up (0 = fine).  Synchronises the device. */
+int ossm_b200_device_status(int* status, int clear);
+
+/* ---- D-LinOSS / LinOSS oscillator scan ------------------------------------
+ * Replaces ossm::dlinoss_{imex1,imex2,im,ex}_forward / _backward
+ * (src/ossm/csrc/dlinoss_imex1.cpp:317-390, dlinoss_imex2.cpp:329-402,
+ * dlinoss_im.cpp:347-420, dlinoss_ex.cpp:264-337; bindings.cpp:161-169) and,
+ * for the two LinOSS variants, LinOSSLayer._run_recurrence with
+ * _LinossScanFn.backward (src/ossm/models/linoss.py:83-151, 260-315).
+ *
+ *   a, g, step : float32 [P] (g may be NULL for the LinOSS variants)
+ *   bu         : complex64 [L, B, P], time-major, P contiguous
+ */
+
+/* Steps between saved states ("carries") = rows per shared-memory stage. */
+int ossm_b200_lti_chunk(void);
+/* Bytes of the carry buffer written by forward and read by backward:
+ * (ceil(L/chunk) - 1) * B * P * 16. */
+size_t ossm_b200_lti_carry_bytes(int64_t L, int64_t B, int64_t P);
+/* Bytes of scratch the backward needs (per-series partial sums, 6*B*P floats). */
+size_t ossm_b200_lti_backward_workspace_bytes(int64_t L, int64_t B, int64_t P);
+
+/* Forward.  Any of the three outputs may be NULL, but not both x and states:
+ *   x       : complex64 [L, B, P]      position state x_t (the op's result)
+ *   states  : complex64 [L, B, P, 2]   full trajectory, the layout
+ *             `ossm._kernels.dlinoss_*_forward` returns (bindings.cpp:12-15)
+ *   carries : complex64 [ceil(L/chunk)-1, B, P, 2]  state after every chunk-th step
+ */
+int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, const float* step, const void* bu,
+                               void* x, void* states, void* carries, int64_t L, int64_t B, int64_t P,
+                               ossm_b200_stream_t stream);
+
+/* Backward from the saved carries (recomputes the states chunk by chunk).
+ *   grad_x : complex64 [L, B, P]  upstream gradient on x (contiguous)
+ *   grad_bu: complex64 [L, B, P];  grad_a / grad_g / grad_step: float32 [P]
+ *   (grad_g may be NULL for the LinOSS variants). */
+int ossm_b200_lti_scan_backward(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                const void* carries, const void* grad_x, void* grad_bu, float* grad_a,
+                                float* grad_g, float* grad_step, void* workspace, size_t workspace_bytes, int64_t L,
+                                int64_t B, int64_t P, ossm_b200_stream_t stream);
+
+/* Backward with the reference's argument list: the full trajectory `states`
+ * ([L,B,P,2], as returned by forward) stands in for the carries
+ * (dlinoss_imex1.cpp:354-390 takes a_diag, g_diag, step, bu, states, grad_output). */
+int ossm_b200_lti_scan_backward_states(int variant, const float* a, const float* g, const float* step,
+                                       const void* bu, const void* states, const void* grad_x, void* grad_bu,
+                                       float* grad_a, float* grad_g, float* grad_step, void* workspace,
+                                       size_t workspace_bytes, int64_t L, int64_t B, int64_t P,
+                                       ossm_b200_stream_t stream);
+
+/* Launch-shape knobs ("fwd_ring", "fwd_warps", "bwd_ring", "bwd_warps",
+ * "force_plain"); process-wide, meant for benchmarking. */
+int ossm_b200_lti_set_tuning(const char* key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OSSM_B200_H_ */

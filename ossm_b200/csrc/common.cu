@@ -1,0 +1,116 @@
+// Host-side plumbing shared by all entry points: error strings, CUDA error
+// mapping, tensor-map encoding through the driver entry point, device status.
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/ossm_b200.h"
+
+namespace ossm_b200 {
+
+static thread_local char tls_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+}
+
+int check_cuda(cudaError_t err, const char* what) {
+  if (err == cudaSuccess) return kOk;
+  set_last_error("%s: %s", what, cudaGetErrorString(err));
+  return kErrCuda;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+static bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, uint32_t esize, const void* base, uint64_t cols,
+                      uint64_t rows, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                      CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return false;
+  if ((pitch_bytes & 15u) != 0 || pitch_bytes >= (1ull << 40)) return false;
+  if (cols == 0 || rows == 0 || cols > 0xffffffffull || rows > 0xffffffffull) return false;
+  if (box_cols > 256 || box_rows > 256 || ((uint64_t)box_cols * esize) % 16 != 0) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap tmp;
+  CUresult r = fn(&tmp, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  memcpy(map, &tmp, sizeof(tmp));
+  return true;
+}
+
+bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                            uint32_t box_cols, uint32_t box_rows) {
+  return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, pitch_bytes, box_cols, box_rows,
+                   CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                            uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
+  return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, cols, rows, pitch_bytes, box_cols, box_rows,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace ossm_b200
+
+extern "C" {
+
+const char* ossm_b200_last_error(void) { return ossm_b200::tls_error; }
+
+int ossm_b200_version(void) { return 1; }
+
+int ossm_b200_device_status(int* status, int clear) {
+  using namespace ossm_b200;
+  if (status == nullptr) {
+    set_last_error("device_status: null output pointer");
+    return kErrInvalidArgument;
+  }
+  int v = 0;
+  if (int rc = check_cuda(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)), "device_status read")) return rc;
+  *status = v;
+  if (clear && v != 0) {
+    int z = 0;
+    if (int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)), "device_status clear")) return rc;
+  }
+  return kOk;
+}
+
+}  // extern "C"

@@ -1,0 +1,132 @@
+// Shared device/host helpers for the ossm_b200 scan kernels (sm_100a only).
+//
+//  * mbarrier + TMA (cp.async.bulk.tensor) wrappers in inline PTX.  Every wait
+//    is bounded: after kSpinLimit failed polls the waiter records an error in a
+//    device status word and the kernel returns, so a lost copy can never hang
+//    the GPU.
+//  * host-side tensor-map construction through the driver entry point (the
+//    library does not link libcuda).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ossm_b200 {
+
+// ---- error plumbing (host) -------------------------------------------------
+enum : int {
+  kOk = 0,
+  kErrInvalidArgument = -1,
+  kErrCuda = -2,
+  kErrUnsupported = -3,
+  kErrWorkspace = -4,
+};
+
+void set_last_error(const char* fmt, ...);
+int check_cuda(cudaError_t err, const char* what);
+
+// Device status word: 0 = fine, otherwise the code of the first bounded wait
+// that gave up (kStatus*).  Read with ossm_b200_device_status().
+enum : int { kStatusTmaTimeout = 1 };
+// (defined here: the library is built as a single translation unit)
+__device__ int g_device_status = 0;
+
+// ---- tensor maps (host) ----------------------------------------------------
+// 2-D fp32 view [rows, cols] with row pitch `pitch_bytes`; box = box_cols x box_rows.
+// Returns false (and leaves `map` untouched) when the view violates a TMA rule
+// (16-byte base / pitch alignment, extent limits) so the caller can take the
+// plain-load kernel instead.
+bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                            uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+// Same for 16-bit elements (bf16 payloads are moved as raw 16-bit words).
+bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                            uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                            bool swizzle128);
+
+int sm_count();
+
+// ---- device helpers --------------------------------------------------------
+#ifdef __CUDACC__
+constexpr uint32_t kSpinLimit = 1u << 24;  // polls of mbarrier.try_wait (each blocks up to a HW time slice)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false after kSpinLimit polls (the caller must bail out).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  atomicCAS(&g_device_status, 0, kStatusTmaTimeout);
+  return false;
+}
+
+// 2-D tiled TMA load global -> shared, completion on `bar` (non-multicast).
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t x,
+                                            int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ float2 ld_nc_f2(const float2* p) {
+  float2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float4 ld_nc_f4(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void st_cs_f2(float2* p, float2 v) {
+  asm volatile("st.global.cs.v2.f32 [%0], {%1, %2};" ::"l"(p), "f"(v.x), "f"(v.y) : "memory");
+}
+
+__device__ __forceinline__ void st_cs_f4(float4* p, float4 v) {
+  asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+#endif  // __CUDACC__
+
+}  // namespace ossm_b200

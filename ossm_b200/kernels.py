@@ -1,0 +1,174 @@
+"""Stand-in for ``ossm._kernels`` on B200: same function names, argument order
+and error behaviour as the reference's pybind11 module
+(``src/ossm/csrc/bindings.cpp:159-223``), implemented by calls into the C ABI of
+``libossm_b200.so``.  Tensors must live on a CUDA device; there is no CPU path.
+
+Besides the reference-compatible functions (``dlinoss_*_forward/backward``,
+``linoss_scan``, ``selective_scan_cuda`` ...) it exposes the leaner entry points
+the autograd wrappers of this package use (``lti_scan_forward`` /
+``lti_scan_backward``: no full-state materialisation, states recomputed from
+chunk carries in the backward).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+VARIANT_IDS = {
+    "imex1": 0, "imex2": 1, "im": 2, "ex": 3, "linoss_im": 4, "linoss_imex": 5,
+}
+
+
+def _p(t: Optional[Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(name: str, t: Tensor) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"ossm_b200: {name} must be a CUDA tensor (this library has no CPU path)")
+
+
+def lti_chunk() -> int:
+    return int(_lib.load().ossm_b200_lti_chunk())
+
+
+def _check_lti_inputs(a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor) -> Tuple[int, int, int]:
+    # same checks and messages as dlinoss_imex1.cpp:321-341
+    coeffs = [a, step] + ([g] if g is not None else [])
+    if any(c.dim() != 1 for c in coeffs):
+        raise RuntimeError("Coefficient diagonals must be 1-D tensors")
+    if bu.dim() != 3:
+        raise RuntimeError("bu must have shape (length, batch, ssm_size)")
+    length, batch, ssm = bu.shape
+    if any(c.size(0) != ssm for c in coeffs):
+        raise RuntimeError("Coefficient diagonals must match state size")
+    _require_cuda("bu", bu)
+    if bu.dtype != torch.complex64 or any(c.dtype != torch.float32 for c in coeffs):
+        raise RuntimeError("ossm_b200: the scan runs in float32 / complex64 only")
+    if any(c.device != bu.device for c in coeffs):
+        raise RuntimeError("ossm_b200: coefficient tensors must be on the device of bu")
+    if length > 0:
+        if not all(c.is_contiguous() for c in coeffs):
+            raise RuntimeError("Coefficient diagonals must be contiguous")
+        if not bu.is_contiguous():
+            raise RuntimeError("bu must be contiguous")
+    return int(length), int(batch), int(ssm)
+
+
+def lti_scan_forward(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor, *,
+                     want_x: bool = True, want_states: bool = False,
+                     want_carries: bool = True) -> Tuple[Optional[Tensor], Optional[Tensor], Optional[Tensor]]:
+    """Runs the oscillator scan.  Returns ``(x [L,B,P], states [L,B,P,2], carries)``
+    (entries not asked for are ``None``)."""
+    vid = VARIANT_IDS[variant]
+    L, B, P = _check_lti_inputs(a, g, step, bu)
+    lib = _lib.load()
+    dev = bu.device
+    x = torch.empty((L, B, P), dtype=torch.complex64, device=dev) if want_x else None
+    states = torch.empty((L, B, P, 2), dtype=torch.complex64, device=dev) if want_states else None
+    carries = None
+    if want_carries:
+        rows = max((L + lti_chunk() - 1) // lti_chunk() - 1, 0)
+        carries = torch.empty((rows, B, P, 2), dtype=torch.complex64, device=dev)
+    if L == 0 or B == 0 or P == 0:
+        return x, states, carries
+    with torch.cuda.device(dev):
+        rc = lib.ossm_b200_lti_scan_forward(vid, _p(a), _p(g), _p(step), _p(bu), _p(x), _p(states),
+                                            _p(carries) if carries is not None and carries.numel() else None,
+                                            L, B, P, _stream(dev))
+    _lib.check(rc, "lti_scan_forward")
+    return x, states, carries
+
+
+def _lti_backward(fn_name: str, variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor,
+                  carry_src: Optional[Tensor], grad_x: Tensor):
+    vid = VARIANT_IDS[variant]
+    L, B, P = _check_lti_inputs(a, g, step, bu)
+    if grad_x.shape != bu.shape:
+        raise RuntimeError("grad_output must match bu shape")
+    dev = bu.device
+    grad_a = torch.empty_like(a)
+    grad_g = torch.empty_like(g) if g is not None else None
+    grad_step = torch.empty_like(step)
+    grad_bu = torch.empty_like(bu)
+    if L == 0 or B == 0 or P == 0:
+        grad_a.zero_()
+        grad_step.zero_()
+        if grad_g is not None:
+            grad_g.zero_()
+        return grad_a, grad_g, grad_step, grad_bu
+    if grad_x.dtype != torch.complex64 or grad_x.device != dev:
+        raise RuntimeError("ossm_b200: grad_output must be complex64 on the device of bu")
+    if not grad_x.is_contiguous():
+        raise RuntimeError("states and grad_output must be contiguous")
+    lib = _lib.load()
+    ws_bytes = int(lib.ossm_b200_lti_backward_workspace_bytes(L, B, P))
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    fn = getattr(lib, fn_name)
+    with torch.cuda.device(dev):
+        rc = fn(vid, _p(a), _p(g), _p(step), _p(bu),
+                _p(carry_src) if carry_src is not None and carry_src.numel() else None,
+                _p(grad_x), _p(grad_bu), _p(grad_a), _p(grad_g), _p(grad_step), _p(workspace), ws_bytes,
+                L, B, P, _stream(dev))
+    _lib.check(rc, fn_name)
+    return grad_a, grad_g, grad_step, grad_bu
+
+
+def lti_scan_backward(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor,
+                      carries: Optional[Tensor], grad_x: Tensor):
+    """Gradients ``(grad_a, grad_g, grad_step, grad_bu)`` from the carries saved by
+    :func:`lti_scan_forward` (``grad_g`` is ``None`` for the LinOSS variants)."""
+    if carries is not None:
+        if carries.dtype != torch.complex64 or not carries.is_contiguous():
+            raise RuntimeError("ossm_b200: carries must be a contiguous complex64 tensor")
+        L = bu.shape[0] if bu.dim() == 3 else 0
+        rows = max((L + lti_chunk() - 1) // lti_chunk() - 1, 0)
+        if tuple(carries.shape) != (rows, *bu.shape[1:], 2):
+            raise RuntimeError("ossm_b200: carries do not match bu (wrong sequence length or chunk)")
+    return _lti_backward("ossm_b200_lti_scan_backward", variant, a, g, step, bu, carries, grad_x)
+
+
+# ---- reference-compatible D-LinOSS entry points ----------------------------
+def _make_dlinoss(variant: str):
+    def forward(a_diag: Tensor, g_diag: Tensor, step: Tensor, bu: Tensor) -> Tensor:
+        _, states, _ = lti_scan_forward(variant, a_diag, g_diag, step, bu, want_x=False, want_states=True,
+                                        want_carries=False)
+        return states
+
+    def backward(a_diag: Tensor, g_diag: Tensor, step: Tensor, bu: Tensor, states: Tensor, grad_output: Tensor):
+        if states.dim() != 4 or states.size(3) != 2:
+            raise RuntimeError("states must have shape (length, batch, ssm_size, 2)")
+        if bu.dim() == 3 and tuple(states.shape[:3]) != tuple(bu.shape):
+            raise RuntimeError("states must have shape (length, batch, ssm_size, 2)")
+        if bu.dim() == 3 and bu.size(0) > 0 and (not states.is_contiguous() or states.dtype != torch.complex64):
+            raise RuntimeError("states and grad_output must be contiguous")
+        ga, gg, gs, gbu = _lti_backward("ossm_b200_lti_scan_backward_states", variant, a_diag, g_diag, step, bu,
+                                        states, grad_output)
+        return ga, gg, gs, gbu
+
+    forward.__name__ = f"dlinoss_{variant}_forward"
+    backward.__name__ = f"dlinoss_{variant}_backward"
+    forward.__doc__ = (f"``ossm._kernels.dlinoss_{variant}_forward`` (bindings.cpp:161-168): returns the full "
+                       "state trajectory ``[L,B,P,2]`` complex64.")
+    backward.__doc__ = (f"``ossm._kernels.dlinoss_{variant}_backward``: ``(grad_a, grad_g, grad_step, grad_bu)``.")
+    return forward, backward
+
+
+dlinoss_imex1_forward, dlinoss_imex1_backward = _make_dlinoss("imex1")
+dlinoss_imex2_forward, dlinoss_imex2_backward = _make_dlinoss("imex2")
+dlinoss_im_forward, dlinoss_im_backward = _make_dlinoss("im")
+dlinoss_ex_forward, dlinoss_ex_backward = _make_dlinoss("ex")
+
+
+def set_tuning(key: str, value: int) -> None:
+    _lib.check(_lib.load().ossm_b200_lti_set_tuning(key.encode(), int(value)), "lti_set_tuning")
