@@ -96,6 +96,24 @@ int ossm_b200_lti_scan_backward_states(int variant, const float* a, const float*
  * "force_plain"); process-wide, meant for benchmarking. */
 int ossm_b200_lti_set_tuning(const char* key, int value);
 
+/* ---- generic LinOSS scan (complex 2x2 per channel, forcing per step) --------
+ * Replaces ossm::linoss_scan (src/ossm/csrc/linoss_scan.cpp:115-146; bindings.cpp:160)
+ * and the Python-loop backward of _LinossScanFn (src/ossm/models/linoss.py:83-151).
+ *
+ *   m11, m12, m21, m22 : complex64 [P]
+ *   b_seq, out/states, grad_out, grad_b : complex64 [L, B, P, 2] (16-byte aligned)
+ *   grad_m : complex64 [P, 2, 2]  =  sum_{t,b} G_t conj(s_{t-1})^T   (the caller keeps
+ *            the real part when the transition matrix is real, linoss.py:133-138)
+ */
+int ossm_b200_linoss_scan_forward(const void* m11, const void* m12, const void* m21, const void* m22,
+                                  const void* b_seq, void* out, int64_t L, int64_t B, int64_t P,
+                                  ossm_b200_stream_t stream);
+size_t ossm_b200_linoss_scan_backward_workspace_bytes(int64_t L, int64_t B, int64_t P);
+int ossm_b200_linoss_scan_backward(const void* m11, const void* m12, const void* m21, const void* m22,
+                                   const void* states, const void* grad_out, void* grad_b, void* grad_m,
+                                   void* workspace, size_t workspace_bytes, int64_t L, int64_t B, int64_t P,
+                                   ossm_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,3 +4,4 @@
 
 #include "common.cu"
 #include "lti_scan.cu"
+#include "linoss_generic.cu"

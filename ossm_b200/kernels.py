@@ -172,3 +172,58 @@ dlinoss_ex_forward, dlinoss_ex_backward = _make_dlinoss("ex")
 
 def set_tuning(key: str, value: int) -> None:
     _lib.check(_lib.load().ossm_b200_lti_set_tuning(key.encode(), int(value)), "lti_set_tuning")
+
+
+# ---- generic LinOSS scan (reference-compatible) ------------------------------
+def linoss_scan(m11: Tensor, m12: Tensor, m21: Tensor, m22: Tensor, b_seq: Tensor) -> Tensor:
+    """``ossm._kernels.linoss_scan`` (linoss_scan.cpp:115-146): complex per-channel
+    2x2 transition, ``b_seq`` ``[L,B,P,2]`` complex64 -> states of the same shape."""
+    out = torch.empty_like(b_seq)
+    if b_seq.size(0) == 0:
+        return out
+    if b_seq.dim() != 4 or b_seq.size(-1) != 2:
+        raise RuntimeError(f"b_seq must have shape (length, batch, ssm_size, 2), got {tuple(b_seq.shape)}")
+    _require_cuda("b_seq", b_seq)
+    coeffs = (m11, m12, m21, m22)
+    if not all(c.is_contiguous() for c in coeffs):
+        raise RuntimeError("Coefficient tensors must be contiguous")
+    if not b_seq.is_contiguous():
+        raise RuntimeError("b_seq must be contiguous")
+    L, B, P, _ = b_seq.shape
+    if b_seq.dtype != torch.complex64 or any(c.dtype != torch.complex64 or c.numel() != P or c.device != b_seq.device
+                                             for c in coeffs):
+        raise RuntimeError("ossm_b200: linoss_scan needs complex64 coefficients of length P on the device of b_seq")
+    if B == 0 or P == 0:
+        return out
+    dev = b_seq.device
+    with torch.cuda.device(dev):
+        rc = _lib.load().ossm_b200_linoss_scan_forward(_p(m11), _p(m12), _p(m21), _p(m22), _p(b_seq), _p(out),
+                                                       L, B, P, _stream(dev))
+    _lib.check(rc, "linoss_scan_forward")
+    return out
+
+
+def linoss_scan_backward(m11: Tensor, m12: Tensor, m21: Tensor, m22: Tensor, states: Tensor,
+                         grad_output: Tensor) -> Tuple[Tensor, Tensor]:
+    """Adjoint of :func:`linoss_scan` (what ``_LinossScanFn.backward`` computes in a
+    Python loop, linoss.py:83-151): returns ``(grad_m [P,2,2] complex64, grad_b [L,B,P,2])``."""
+    L, B, P, _ = grad_output.shape
+    dev = grad_output.device
+    _require_cuda("grad_output", grad_output)
+    grad_m = torch.zeros((P, 2, 2), dtype=torch.complex64, device=dev)
+    grad_b = torch.empty_like(grad_output)
+    if L == 0 or B == 0 or P == 0:
+        return grad_m, grad_b
+    if not (states.is_contiguous() and grad_output.is_contiguous()):
+        raise RuntimeError("states and grad_output must be contiguous")
+    if states.shape != grad_output.shape or states.dtype != torch.complex64 or grad_output.dtype != torch.complex64:
+        raise RuntimeError("ossm_b200: states and grad_output must be complex64 tensors of the same shape")
+    lib = _lib.load()
+    ws_bytes = int(lib.ossm_b200_linoss_scan_backward_workspace_bytes(L, B, P))
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.ossm_b200_linoss_scan_backward(_p(m11), _p(m12), _p(m21), _p(m22), _p(states), _p(grad_output),
+                                                _p(grad_b), _p(grad_m), _p(workspace), ws_bytes, L, B, P,
+                                                _stream(dev))
+    _lib.check(rc, "linoss_scan_backward")
+    return grad_m, grad_b
