@@ -114,6 +114,41 @@ int ossm_b200_linoss_scan_backward(const void* m11, const void* m12, const void*
                                    void* workspace, size_t workspace_bytes, int64_t L, int64_t B, int64_t P,
                                    ossm_b200_stream_t stream);
 
+/* ---- Mamba selective scan ------------------------------------------------------
+ * Replaces ossm::selective_scan_cuda_forward / selective_scan_cuda_backward
+ * (src/ossm/csrc/selective_scan_cuda.cu:253-393; bindings.cpp:199-222) and the CPU
+ * pair selective_scan / selective_scan_backward (selective_scan_cpu.cpp:78-360).
+ *
+ *   u, z, out, dout, du, dz : [B, D, L]  element type `io_dtype` (time contiguous)
+ *   dt, ddt                 : [B, D, L]  float32
+ *   A, dA                   : [D, N]     float32
+ *   Bm, Cm                  : [B, N, L]  element type `io_dtype` (time contiguous; the
+ *                             transpose of ossm's [B, L, N] argument)
+ *   dB, dC                  : [B, N, L]  float32 (zeroed by the call)
+ *   z / dz, Dskip / dD      : optional (NULL): SiLU gate and skip term Dskip[d]*u
+ *   chunk_states            : float32 [B, D, ceil(L/chunk), N], the state entering each
+ *                             chunk; written by forward (may be NULL when no backward
+ *                             will follow), read by backward.
+ */
+#define OSSM_B200_DTYPE_F32 0
+#define OSSM_B200_DTYPE_BF16 1
+
+/* Time steps per chunk for a given state size N (256 for N<=16, 128 for N<=32, ...). */
+int ossm_b200_selective_scan_chunk(int64_t N);
+size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
+size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
+
+int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float* A, const void* Bm, const void* Cm,
+                                     const void* z, const float* Dskip, void* out, float* chunk_states, int64_t B,
+                                     int64_t D, int64_t L, int64_t N, int io_dtype, ossm_b200_stream_t stream);
+
+int ossm_b200_selective_scan_backward(const void* u, const float* dt, const float* A, const void* Bm,
+                                      const void* Cm, const void* z, const float* Dskip, const void* dout,
+                                      const float* chunk_states, void* du, float* ddt, float* dA, float* dB,
+                                      float* dC, void* dz, float* dD, void* workspace, size_t workspace_bytes,
+                                      int64_t B, int64_t D, int64_t L, int64_t N, int io_dtype,
+                                      ossm_b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

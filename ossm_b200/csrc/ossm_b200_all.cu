@@ -5,3 +5,4 @@
 #include "common.cu"
 #include "lti_scan.cu"
 #include "linoss_generic.cu"
+#include "selective_scan.cu"

@@ -227,3 +227,167 @@ def linoss_scan_backward(m11: Tensor, m12: Tensor, m21: Tensor, m22: Tensor, sta
                                                 _stream(dev))
     _lib.check(rc, "linoss_scan_backward")
     return grad_m, grad_b
+
+
+# ---- Mamba selective scan ----------------------------------------------------
+_IO_DTYPES = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def selective_scan_chunk(d_state: int) -> int:
+    return int(_lib.load().ossm_b200_selective_scan_chunk(int(d_state)))
+
+
+def _time_major_bc(t: Tensor) -> Tensor:
+    """``[B, L, N]`` (ossm's argument) -> contiguous ``[B, N, L]``; free when the caller
+    already holds the operand time-contiguous and passes a transposed view."""
+    tt = t.transpose(1, 2)
+    return tt if tt.is_contiguous() else tt.contiguous()
+
+
+def _check_selective(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor]):
+    # mirrors _check_inputs of selective_scan_cpu.cpp / selective_scan_cuda.cu:196-250
+    if inputs.dim() != 3:
+        raise RuntimeError("inputs must have shape (batch, channels, length)")
+    if dt.shape != inputs.shape:
+        raise RuntimeError("dt must match the shape of inputs")
+    if A.dim() != 2 or A.size(0) != inputs.size(1):
+        raise RuntimeError("A must have shape (channels, state)")
+    bsz, _, length = inputs.shape
+    n = A.size(1)
+    if tuple(B.shape) != (bsz, length, n) or tuple(C.shape) != (bsz, length, n):
+        raise RuntimeError("B and C must have shape (batch, length, state)")
+    if gate is not None and gate.shape != inputs.shape:
+        raise RuntimeError("gate must match the shape of inputs")
+    _require_cuda("inputs", inputs)
+    if inputs.dtype not in _IO_DTYPES:
+        raise RuntimeError("ossm_b200: selective scan supports float32 or bfloat16 inputs")
+    for name, t in (("B", B), ("C", C), ("gate", gate)):
+        if t is not None and t.dtype != inputs.dtype:
+            raise RuntimeError(f"ossm_b200: {name} must have the dtype of inputs ({inputs.dtype})")
+    for t in (dt, A, B, C, gate):
+        if t is not None and t.device != inputs.device:
+            raise RuntimeError("ossm_b200: all selective-scan operands must be on one device")
+
+
+def selective_scan_fwd(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor] = None,
+                       D: Optional[Tensor] = None, save_states: bool = True) -> Tuple[Tensor, Optional[Tensor]]:
+    """Fused selective scan; returns ``(out [B,D,L], chunk_states or None)``.
+    ``inputs/gate/B/C`` float32 or bfloat16, ``dt``/``A``/``D`` float32 (cast if not)."""
+    _check_selective(inputs, dt, A, B, C, gate)
+    bsz, ch, length = inputs.shape
+    n = A.size(1)
+    dev = inputs.device
+    out = torch.empty_like(inputs, memory_format=torch.contiguous_format)
+    lib = _lib.load()
+    states = None
+    if save_states:
+        chunk = selective_scan_chunk(n) if n > 0 else 1
+        states = torch.empty((bsz, ch, (length + chunk - 1) // chunk, n), dtype=torch.float32, device=dev)
+    if inputs.numel() == 0:
+        return out, states
+    if n == 0:
+        raise RuntimeError("A must have a positive state dimension")
+    u = inputs.contiguous()
+    dtc = dt.float().contiguous()
+    Ac = A.float().contiguous()
+    Bt, Ct = _time_major_bc(B), _time_major_bc(C)
+    zc = gate.contiguous() if gate is not None else None
+    Dc = D.float().contiguous() if D is not None else None
+    with torch.cuda.device(dev):
+        rc = lib.ossm_b200_selective_scan_forward(_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(out),
+                                                  _p(states), bsz, ch, length, n, _IO_DTYPES[inputs.dtype],
+                                                  _stream(dev))
+    _lib.check(rc, "selective_scan_forward")
+    return out, states
+
+
+def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor,
+                       gate: Optional[Tensor], chunk_states: Tensor, D: Optional[Tensor] = None):
+    """Gradients ``(du, ddt, dA, dB, dC, dgate, dD)`` (``dgate``/``dD`` ``None`` when absent)."""
+    _check_selective(inputs, dt, A, B, C, gate)
+    if grad_output.shape != inputs.shape:
+        raise RuntimeError("grad_output must match the shape of inputs")
+    bsz, ch, length = inputs.shape
+    n = A.size(1)
+    dev = inputs.device
+    du = torch.empty_like(inputs, memory_format=torch.contiguous_format)
+    ddt = torch.empty(inputs.shape, dtype=torch.float32, device=dev)
+    dA = torch.empty((ch, n), dtype=torch.float32, device=dev)
+    dBt = torch.empty((bsz, n, length), dtype=torch.float32, device=dev)
+    dCt = torch.empty((bsz, n, length), dtype=torch.float32, device=dev)
+    dz = torch.empty_like(du) if gate is not None else None
+    dD = torch.empty(ch, dtype=torch.float32, device=dev) if D is not None else None
+    if inputs.numel() == 0 or n == 0:
+        for t in (dA, dBt, dCt, dD):
+            if t is not None:
+                t.zero_()
+    else:
+        lib = _lib.load()
+        ws_bytes = int(lib.ossm_b200_selective_scan_backward_workspace_bytes(bsz, ch, length, n))
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        u = inputs.contiguous()
+        dtc = dt.float().contiguous()
+        Ac = A.float().contiguous()
+        Bt, Ct = _time_major_bc(B), _time_major_bc(C)
+        zc = gate.contiguous() if gate is not None else None
+        Dc = D.float().contiguous() if D is not None else None
+        go = grad_output.to(inputs.dtype).contiguous()
+        chunk = selective_scan_chunk(n)
+        if (chunk_states.dtype != torch.float32 or not chunk_states.is_contiguous()
+                or tuple(chunk_states.shape) != (bsz, ch, (length + chunk - 1) // chunk, n)):
+            raise RuntimeError("ossm_b200: chunk_states do not belong to these inputs")
+        with torch.cuda.device(dev):
+            rc = lib.ossm_b200_selective_scan_backward(
+                _p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(go), _p(chunk_states), _p(du), _p(ddt),
+                _p(dA), _p(dBt), _p(dCt), _p(dz), _p(dD), _p(workspace), ws_bytes, bsz, ch, length, n,
+                _IO_DTYPES[inputs.dtype], _stream(dev))
+        _lib.check(rc, "selective_scan_backward")
+    dB = dBt.transpose(1, 2).to(B.dtype)
+    dC = dCt.transpose(1, 2).to(C.dtype)
+    return du, ddt.to(dt.dtype), dA.to(A.dtype), dB, dC, dz, (dD.to(D.dtype) if dD is not None else None)
+
+
+# reference-compatible names (bindings.cpp:180-222)
+def selective_scan_cuda(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor] = None,
+                        chunk_length: int = 16):
+    """Returns ``(outputs, chunk_states, raw_outputs)``.  ``chunk_length`` is accepted and
+    ignored, as in the reference wrapper (selective_scan_cuda.cu:259); ``raw_outputs`` is an
+    empty tensor because the backward recomputes the ungated output instead of reading it."""
+    out, states = selective_scan_fwd(inputs, dt, A, B, C, gate)
+    return out, states, inputs.new_empty(0)
+
+
+def selective_scan_cuda_backward(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor,
+                                 gate: Optional[Tensor], chunk_states: Tensor, raw_outputs: Tensor,
+                                 chunk_length: int):
+    du, ddt, dA, dB, dC, dz, _ = selective_scan_bwd(grad_output, inputs, dt, A, B, C, gate, chunk_states)
+    if dz is None:
+        dz = torch.zeros_like(inputs)           # the reference returns zeros for an absent gate
+    return du, ddt, dA, dB, dC, dz
+
+
+def selective_scan(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor] = None):
+    """Name of the reference's CPU entry point; here it needs CUDA tensors like everything else."""
+    return selective_scan_fwd(inputs, dt, A, B, C, gate, save_states=False)[0]
+
+
+def selective_scan_backward(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor,
+                            gate: Optional[Tensor] = None):
+    _, states = selective_scan_fwd(inputs, dt, A, B, C, gate)
+    return selective_scan_cuda_backward(grad_output, inputs, dt, A, B, C, gate, states, inputs.new_empty(0), 0)
+
+
+# ---- names ossm calls unconditionally but that are outside this library ------
+def _out_of_scope(name: str):
+    def stub(*_args, **_kwargs):
+        # ossm's shims catch RuntimeError and take their own PyTorch path
+        # (_lru_scan.py:33, _s5_scan.py, _rnn_scan.py:38).
+        raise RuntimeError(f"ossm_b200 does not provide {name}; use ossm's PyTorch implementation")
+
+    stub.__name__ = name
+    return stub
+
+
+lru_scan = _out_of_scope("lru_scan")
+s5_scan = _out_of_scope("s5_scan")
+linear_rnn_scan = _out_of_scope("linear_rnn_scan")
