@@ -122,56 +122,144 @@ __device__ __forceinline__ void store_items(IO* row, long long t0, long long L, 
     if (t0 + j < L) io_store<IO>(row + t0 + j, v[j]);
 }
 
-// Stages the [N][T] fp32 tile of a [B, N, L] operand for chunk starting at t_base.
-template <typename IO>
-__device__ __forceinline__ void stage_tile(float* dst, const IO* src_b, int N, int T, long long t_base, long long L) {
-  const int total = N * T;
-  for (int idx = threadIdx.x; idx < total; idx += kThreads) {
+// ---------------------------------------------------------------------------
+// Shared-memory tiles.  States are processed two at a time (n = 2p, 2p+1) so that
+// every per-(step, state) operation is one packed f32x2 instruction on a
+// (state 2p, state 2p+1) register pair.  A tile holds, per state pair, the T
+// steps of a chunk as float2 (one value per state); a thread's kItems steps are
+// spread over kItems/2 float4 slots laid out [pair][slot][lane][4] so that the 32
+// lanes of a warp read 512 contiguous bytes per 16-byte access (no bank
+// conflicts).  An odd last state is padded with a zero partner.
+// ---------------------------------------------------------------------------
+template <int kItems>
+__device__ __forceinline__ int tile_index(int pair, int t_local, int s) {
+  if constexpr (kItems >= 2) {
+    const int lane = t_local / kItems, j = t_local % kItems;
+    return ((pair * (kItems / 2) + (j >> 1)) * 32 + lane) * 4 + (j & 1) * 2 + s;
+  } else {
+    return (pair * 32 + t_local) * 2 + s;
+  }
+}
+
+template <int kItems>
+__device__ __forceinline__ void lds_pairs(const float* tile, int pair, int lane, float2 (&v)[kItems]) {
+  if constexpr (kItems >= 2) {
+#pragma unroll
+    for (int q = 0; q < kItems / 2; ++q) {
+      const float4 x = reinterpret_cast<const float4*>(tile)[(pair * (kItems / 2) + q) * 32 + lane];
+      v[2 * q] = make_float2(x.x, x.y);
+      v[2 * q + 1] = make_float2(x.z, x.w);
+    }
+  } else {
+    v[0] = reinterpret_cast<const float2*>(tile)[pair * 32 + lane];
+  }
+}
+
+template <int kItems>
+__device__ __forceinline__ void sts_pairs(float* tile, int pair, int lane, const float2 (&v)[kItems]) {
+  if constexpr (kItems >= 2) {
+#pragma unroll
+    for (int q = 0; q < kItems / 2; ++q)
+      reinterpret_cast<float4*>(tile)[(pair * (kItems / 2) + q) * 32 + lane] =
+          make_float4(v[2 * q].x, v[2 * q].y, v[2 * q + 1].x, v[2 * q + 1].y);
+  } else {
+    reinterpret_cast<float2*>(tile)[pair * 32 + lane] = v[0];
+  }
+}
+
+// Stages the chunk tile of a [B, N, L] operand (converted to fp32) for the chunk
+// starting at t_base; global reads are coalesced along time.
+template <typename IO, int kItems>
+__device__ __forceinline__ void stage_tile(float* dst, const IO* src_b, int N, long long t_base, long long L) {
+  constexpr int T = 32 * kItems;
+  const int rows = 2 * ((N + 1) / 2);
+  for (int idx = threadIdx.x; idx < rows * T; idx += kThreads) {
     const int n = idx / T, t = idx - n * T;
     const long long tt = t_base + t;
-    dst[idx] = tt < L ? io_load<IO>(src_b + (long long)n * L + tt) : 0.0f;
+    const float v = (n < N && tt < L) ? io_load<IO>(src_b + (long long)n * L + tt) : 0.0f;
+    dst[tile_index<kItems>(n >> 1, t, n & 1)] = v;
   }
 }
 
-// Inclusive warp scan of affine maps x -> P*x + H (lane order = time order),
-// returned as the EXCLUSIVE prefix (the map applied before this lane) and the
-// total over the warp.
-__device__ __forceinline__ void warp_scan_affine(float P, float H, int lane, float& Pex, float& Hex, float& Ptot,
-                                                 float& Htot) {
+__device__ __forceinline__ float2 shfl_up2(float2 v, int off) {
+  return make_float2(__shfl_up_sync(0xffffffffu, v.x, off), __shfl_up_sync(0xffffffffu, v.y, off));
+}
+__device__ __forceinline__ float2 shfl_down2(float2 v, int off) {
+  return make_float2(__shfl_down_sync(0xffffffffu, v.x, off), __shfl_down_sync(0xffffffffu, v.y, off));
+}
+__device__ __forceinline__ float2 shfl2(float2 v, int src) {
+  return make_float2(__shfl_sync(0xffffffffu, v.x, src), __shfl_sync(0xffffffffu, v.y, src));
+}
+
+// Warp scan of affine maps x -> P*x + H in time order (lane 0 first), two states
+// at once.  Returns the EXCLUSIVE prefix map of each lane and the map of the
+// whole warp.
+__device__ __forceinline__ void warp_scan_affine(float2 P, float2 H, int lane, float2& Pex, float2& Hex,
+                                                 float2& Ptot, float2& Htot) {
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const float Pp = __shfl_up_sync(0xffffffffu, P, off);
-    const float Hp = __shfl_up_sync(0xffffffffu, H, off);
+    const float2 Pp = shfl_up2(P, off);
+    const float2 Hp = shfl_up2(H, off);
     if (lane >= off) {
-      H = fmaf(P, Hp, H);
-      P = P * Pp;
+      H = __ffma2_rn(P, Hp, H);
+      P = __fmul2_rn(P, Pp);
     }
   }
-  Ptot = __shfl_sync(0xffffffffu, P, 31);
-  Htot = __shfl_sync(0xffffffffu, H, 31);
-  Pex = __shfl_up_sync(0xffffffffu, P, 1);
-  Hex = __shfl_up_sync(0xffffffffu, H, 1);
-  if (lane == 0) { Pex = 1.0f; Hex = 0.0f; }
+  Ptot = shfl2(P, 31);
+  Htot = shfl2(H, 31);
+  Pex = shfl_up2(P, 1);
+  Hex = shfl_up2(H, 1);
+  if (lane == 0) { Pex = make_float2(1.f, 1.f); Hex = make_float2(0.f, 0.f); }
 }
 
-// Same in reverse time order: suffix maps (lane 31 is applied first).
-__device__ __forceinline__ void warp_scan_affine_rev(float P, float H, int lane, float& Pex, float& Hex,
-                                                     float& Ptot, float& Htot) {
+// Same in reverse time order (lane 31 is applied first).
+__device__ __forceinline__ void warp_scan_affine_rev(float2 P, float2 H, int lane, float2& Pex, float2& Hex,
+                                                     float2& Ptot, float2& Htot) {
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const float Pp = __shfl_down_sync(0xffffffffu, P, off);
-    const float Hp = __shfl_down_sync(0xffffffffu, H, off);
+    const float2 Pp = shfl_down2(P, off);
+    const float2 Hp = shfl_down2(H, off);
     if (lane + off < 32) {
-      H = fmaf(P, Hp, H);
-      P = P * Pp;
+      H = __ffma2_rn(P, Hp, H);
+      P = __fmul2_rn(P, Pp);
     }
   }
-  Ptot = __shfl_sync(0xffffffffu, P, 0);
-  Htot = __shfl_sync(0xffffffffu, H, 0);
-  Pex = __shfl_down_sync(0xffffffffu, P, 1);
-  Hex = __shfl_down_sync(0xffffffffu, H, 1);
-  if (lane == 31) { Pex = 1.0f; Hex = 0.0f; }
+  Ptot = shfl2(P, 0);
+  Htot = shfl2(H, 0);
+  Pex = shfl_down2(P, 1);
+  Hex = shfl_down2(H, 1);
+  if (lane == 31) { Pex = make_float2(1.f, 1.f); Hex = make_float2(0.f, 0.f); }
 }
+
+// Forward (P,H: lane 0 first) and reverse (Q,R: lane 31 first) scans in the same
+// five rounds, so their shuffle latencies overlap.
+__device__ __forceinline__ void warp_scan_dual(float2 P, float2 H, float2 Q, float2 R, int lane, float2& Pex,
+                                               float2& Hex, float2& Qex, float2& Rex, float2& Qtot,
+                                               float2& Rtot) {
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float2 Pp = shfl_up2(P, off), Hp = shfl_up2(H, off);
+    const float2 Qp = shfl_down2(Q, off), Rp = shfl_down2(R, off);
+    if (lane >= off) {
+      H = __ffma2_rn(P, Hp, H);
+      P = __fmul2_rn(P, Pp);
+    }
+    if (lane + off < 32) {
+      R = __ffma2_rn(Q, Rp, R);
+      Q = __fmul2_rn(Q, Qp);
+    }
+  }
+  Qtot = shfl2(Q, 0);
+  Rtot = shfl2(R, 0);
+  Pex = shfl_up2(P, 1);
+  Hex = shfl_up2(H, 1);
+  Qex = shfl_down2(Q, 1);
+  Rex = shfl_down2(R, 1);
+  if (lane == 0) { Pex = make_float2(1.f, 1.f); Hex = make_float2(0.f, 0.f); }
+  if (lane == 31) { Qex = make_float2(1.f, 1.f); Rex = make_float2(0.f, 0.f); }
+}
+
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
 
 struct Params {
   const void* u;
@@ -193,18 +281,30 @@ struct Params {
   float* dA_part;  // [B, D, N]
   float* dD_part;  // [B, D] (nullable)
   long long B, D, L, N;
+  long long nstates;   // saved states per lane = ceil(L / state_interval)
+  int state_interval;  // steps between saved states (= the backward's chunk)
   bool vec_ok;
 };
 
-// Shared memory (floats): Bs[N*T] | Cs[N*T] | carry[kWarps*kCI*N]
+// (A[d,2p], A[d,2p+1]) * log2(e); a missing odd partner gets 0 (decay 1, no forcing).
+__device__ __forceinline__ float2 load_A_pair(const float* A, long long d, int N, int pair, bool active) {
+  if (!active) return make_float2(0.f, 0.f);
+  const int n0 = 2 * pair;
+  const float a0 = __ldg(A + d * N + n0);
+  const float a1 = n0 + 1 < N ? __ldg(A + d * N + n0 + 1) : 0.0f;
+  return make_float2(a0, a1);
+}
+
+// Shared memory (floats): Bs[NP*T*2] | Cs[NP*T*2] | carry[kWarps*kCI*NP*2]   (NP = ceil(N/2))
 template <typename IO, int kItems>
 __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
   constexpr int T = 32 * kItems;
   extern __shared__ __align__(16) float smem[];
   const int N = (int)p.N;
+  const int NP = (N + 1) / 2;
   float* Bs = smem;
-  float* Cs = Bs + N * T;
-  float* carry = Cs + N * T;
+  float* Cs = Bs + NP * T * 2;
+  float2* carry = reinterpret_cast<float2*>(Cs + NP * T * 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
   const long long d0 = (long long)blockIdx.x * kChannelsPerCta + warp * kCI;
@@ -212,13 +312,13 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
 
-  for (int i = threadIdx.x; i < kWarps * kCI * N; i += kThreads) carry[i] = 0.0f;
+  for (int i = threadIdx.x; i < kWarps * kCI * NP; i += kThreads) carry[i] = make_float2(0.f, 0.f);
 
   for (long long c = 0; c < nchunks; ++c) {
     const long long t_base = c * T;
     __syncthreads();  // everyone is done with the previous tiles (and carry init)
-    stage_tile<IO>(Bs, Bm_b, N, T, t_base, p.L);
-    stage_tile<IO>(Cs, Cm_b, N, T, t_base, p.L);
+    stage_tile<IO, kItems>(Bs, Bm_b, N, t_base, p.L);
+    stage_tile<IO, kItems>(Cs, Cm_b, N, t_base, p.L);
     __syncthreads();
     const long long t0 = t_base + (long long)lane * kItems;
 #pragma unroll 1
@@ -226,40 +326,51 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
       const long long d = d0 + ci;
       if (d >= p.D) break;  // warp-uniform
       const long long row = (b * p.D + d) * p.L;
-      float u[kItems], dt[kItems], y[kItems];
+      float u[kItems], dt[kItems];
+      float2 y2[kItems], dtu2[kItems];
       load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, p.L, p.vec_ok, u);
       load_items<float, kItems>(p.dt + row, t0, p.L, p.vec_ok, dt);
-      float dtu[kItems];
 #pragma unroll
-      for (int j = 0; j < kItems; ++j) { dtu[j] = dt[j] * u[j]; y[j] = 0.0f; }
-      float* cw = carry + (warp * kCI + ci) * N;
-      float* cs_out = p.chunk_states ? p.chunk_states + ((b * p.D + d) * nchunks + c) * p.N : nullptr;
+      for (int j = 0; j < kItems; ++j) { dtu2[j] = splat(dt[j] * u[j]); y2[j] = make_float2(0.f, 0.f); }
+      float2* cw = carry + (warp * kCI + ci) * NP;
+      // States are saved every p.state_interval steps (the backward's chunk): the
+      // lanes whose first step starts such an interval write the state entering it.
+      const int lanes_per_save = p.state_interval / kItems;
+      const bool saver = p.chunk_states != nullptr && (lane % lanes_per_save) == 0 && t0 < p.L;
+      float* cs_out = saver ? p.chunk_states + ((b * p.D + d) * p.nstates + t0 / p.state_interval) * p.N : nullptr;
 #pragma unroll 1
-      for (int n = 0; n < N; ++n) {
-        const float A2 = __ldg(p.A + d * p.N + n) * kLog2e;
-        const float* Bn = Bs + n * T + lane * kItems;
-        const float* Cn = Cs + n * T + lane * kItems;
-        float hloc[kItems], cp[kItems];
-        float P = 1.0f, H = 0.0f;
+      for (int pr = 0; pr < NP; ++pr) {
+        const float2 Ap = load_A_pair(p.A, d, N, pr, true);
+        const float2 A2 = make_float2(Ap.x * kLog2e, Ap.y * kLog2e);
+        float2 Bv[kItems], Cv[kItems];
+        lds_pairs<kItems>(Bs, pr, lane, Bv);
+        lds_pairs<kItems>(Cs, pr, lane, Cv);
+        float2 hloc[kItems], cp[kItems];
+        float2 P = make_float2(1.f, 1.f), H = make_float2(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < kItems; ++j) {
-          const float a = ex2(dt[j] * A2);
-          H = fmaf(a, H, dtu[j] * Bn[j]);
-          P *= a;
+          const float2 x = __fmul2_rn(splat(dt[j]), A2);
+          const float2 a = make_float2(ex2(x.x), ex2(x.y));
+          H = __ffma2_rn(a, H, __fmul2_rn(dtu2[j], Bv[j]));
+          P = __fmul2_rn(P, a);
           hloc[j] = H;
           cp[j] = P;
         }
-        const float h_in = cw[n];  // read before the scan: its shuffles order this read before lane 0's update
-        float Pex, Hex, Ptot, Htot;
+        const float2 h_in = cw[pr];  // read before the scan: its shuffles order this read before lane 0's update
+        float2 Pex, Hex, Ptot, Htot;
         warp_scan_affine(P, H, lane, Pex, Hex, Ptot, Htot);
-        const float hstart = fmaf(Pex, h_in, Hex);
+        const float2 hstart = __ffma2_rn(Pex, h_in, Hex);
 #pragma unroll
-        for (int j = 0; j < kItems; ++j) y[j] = fmaf(fmaf(cp[j], hstart, hloc[j]), Cn[j], y[j]);
-        if (lane == 0) {
-          if (cs_out) cs_out[n] = h_in;
-          cw[n] = fmaf(Ptot, h_in, Htot);
+        for (int j = 0; j < kItems; ++j) y2[j] = __ffma2_rn(__ffma2_rn(cp[j], hstart, hloc[j]), Cv[j], y2[j]);
+        if (cs_out) {
+          cs_out[2 * pr] = hstart.x;
+          if (2 * pr + 1 < N) cs_out[2 * pr + 1] = hstart.y;
         }
+        if (lane == 0) cw[pr] = __ffma2_rn(Ptot, h_in, Htot);
       }
+      float y[kItems];
+#pragma unroll
+      for (int j = 0; j < kItems; ++j) y[j] = y2[j].x + y2[j].y;
       if (p.Dskip) {
         const float ds = __ldg(p.Dskip + d);
 #pragma unroll
@@ -277,180 +388,193 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
   }
 }
 
-// Shared memory (floats):
-//   Bs[N*T] | Cs[N*T] | dBs[N*T] | dCs[N*T] | red[2][kWarps][T] | lam[kWarps*kCI*N] | dAacc[kWarps*kCI*N]
+// Shared memory (floats), NP = ceil(N/2), tile = NP*T*2:
+//   Bs | Cs (one tile each) | acc[kWarps][2 (dB,dC)][tile] | lam[kWarps*kCI*NP*2] | dAacc[kWarps*kCI*NP*2]
 //   | dDacc[kWarps*kCI]
+// Every warp owns a private dB/dC accumulator tile, so the warps of a CTA run
+// independently between the three barriers of a chunk (tile staging, flush).
 template <typename IO, int kItems>
 __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   constexpr int T = 32 * kItems;
   extern __shared__ __align__(16) float smem[];
   const int N = (int)p.N;
+  const int NP = (N + 1) / 2;
+  const int tile = NP * T * 2;
   float* Bs = smem;
-  float* Cs = Bs + N * T;
-  float* dBs = Cs + N * T;
-  float* dCs = dBs + N * T;
-  float* red = dCs + N * T;                 // [2][kWarps][T]
-  float* lam = red + 2 * kWarps * T;        // adjoint carried from the later chunk
-  float* dAacc = lam + kWarps * kCI * N;
-  float* dDacc = dAacc + kWarps * kCI * N;
+  float* Cs = Bs + tile;
+  float* acc = Cs + tile;
+  float2* lam = reinterpret_cast<float2*>(acc + kWarps * 2 * tile);   // adjoint carried from the later chunk
+  float2* dAacc = lam + kWarps * kCI * NP;
+  float* dDacc = reinterpret_cast<float*>(dAacc + kWarps * kCI * NP);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
   const long long d0 = (long long)blockIdx.x * kChannelsPerCta + warp * kCI;
   const long long nchunks = (p.L + T - 1) / T;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
-  // number of channel iterations in which at least one warp of this CTA is active
-  const long long ch_left = p.D - (long long)blockIdx.x * kChannelsPerCta;
+  float* accB = acc + warp * 2 * tile;
+  float* accC = accB + tile;
 
-  for (int i = threadIdx.x; i < kWarps * kCI * N; i += kThreads) { lam[i] = 0.0f; dAacc[i] = 0.0f; }
+  for (int i = threadIdx.x; i < kWarps * kCI * NP; i += kThreads) {
+    lam[i] = make_float2(0.f, 0.f);
+    dAacc[i] = make_float2(0.f, 0.f);
+  }
   for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) dDacc[i] = 0.0f;
 
   for (long long c = nchunks - 1; c >= 0; --c) {
     const long long t_base = c * T;
-    __syncthreads();
-    stage_tile<IO>(Bs, Bm_b, N, T, t_base, p.L);
-    stage_tile<IO>(Cs, Cm_b, N, T, t_base, p.L);
-    for (int i = threadIdx.x; i < 2 * N * T; i += kThreads) dBs[i] = 0.0f;  // dBs and dCs are adjacent
+    __syncthreads();  // previous flush finished
+    stage_tile<IO, kItems>(Bs, Bm_b, N, t_base, p.L);
+    stage_tile<IO, kItems>(Cs, Cm_b, N, t_base, p.L);
+    for (int i = threadIdx.x; i < kWarps * 2 * tile; i += kThreads) acc[i] = 0.0f;
     __syncthreads();
     const long long t0 = t_base + (long long)lane * kItems;
+
+    // operands of the first channel; those of channel ci+1 are fetched while ci is processed
+    float u[kItems], dt[kItems], go[kItems], zz[kItems];
+    auto fetch = [&](int ci, float (&fu)[kItems], float (&fdt)[kItems], float (&fgo)[kItems], float (&fz)[kItems]) {
+      const long long d = d0 + ci;
+      const bool ok = ci < kCI && d < p.D;
+      const long long row = ok ? (b * p.D + d) * p.L : 0;
+      const long long tl = ok ? p.L : 0;
+      load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, tl, p.vec_ok, fu);
+      load_items<float, kItems>(p.dt + row, t0, tl, p.vec_ok, fdt);
+      load_items<IO, kItems>(static_cast<const IO*>(p.dout) + row, t0, tl, p.vec_ok, fgo);
+      if (p.z) load_items<IO, kItems>(static_cast<const IO*>(p.z) + row, t0, tl, p.vec_ok, fz);
+    };
+    fetch(0, u, dt, go, zz);
 #pragma unroll 1
     for (int ci = 0; ci < kCI; ++ci) {
-      if ((long long)ci >= ch_left) break;                   // CTA-uniform: no channel left in any warp
       const long long d = d0 + ci;
-      const bool active = d < p.D;                            // warp-uniform
-      const long long row = active ? (b * p.D + d) * p.L : 0;
-      const long long tl = active ? p.L : 0;                  // inactive warps load nothing, contribute zeros
-      float u[kItems], dt[kItems], gy[kItems], dtu[kItems];
-      float dus[kItems], ddts[kItems], y[kItems];
-      load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, tl, p.vec_ok, u);
-      load_items<float, kItems>(p.dt + row, t0, tl, p.vec_ok, dt);
-      load_items<IO, kItems>(static_cast<const IO*>(p.dout) + row, t0, tl, p.vec_ok, gy);
-      float zz[kItems], dout_raw[kItems];
-      if (p.z) {
-        load_items<IO, kItems>(static_cast<const IO*>(p.z) + row, t0, tl, p.vec_ok, zz);
+      if (d >= p.D) break;                                    // warp-uniform; no CTA barrier inside this loop
+      const long long row = (b * p.D + d) * p.L;
+      float nu[kItems], ndt[kItems], ngo[kItems], nz[kItems];
+      fetch(ci + 1, nu, ndt, ngo, nz);
+      float gy[kItems];
+      float2 dtu2[kItems], dus2[kItems], ddts2[kItems], y2[kItems];
 #pragma unroll
-        for (int j = 0; j < kItems; ++j) { dout_raw[j] = gy[j]; gy[j] *= zz[j] * sigmoidf(zz[j]); }
+      for (int j = 0; j < kItems; ++j) {
+        gy[j] = p.z ? go[j] * (zz[j] * sigmoidf(zz[j])) : go[j];
+        dtu2[j] = splat(dt[j] * u[j]);
+        dus2[j] = make_float2(0.f, 0.f);
+        ddts2[j] = make_float2(0.f, 0.f);
+        y2[j] = make_float2(0.f, 0.f);
       }
-#pragma unroll
-      for (int j = 0; j < kItems; ++j) { dtu[j] = dt[j] * u[j]; dus[j] = 0.f; ddts[j] = 0.f; y[j] = 0.f; }
-      const int slot = (warp * kCI + ci) * N;
-      const float* cs_in = active ? p.chunk_states + ((b * p.D + d) * nchunks + c) * p.N : nullptr;
+      const int slot = (warp * kCI + ci) * NP;
+      const float* cs_in = p.chunk_states + ((b * p.D + d) * nchunks + c) * p.N;
 #pragma unroll 1
-      for (int n = 0; n < N; ++n) {
-        const float An = active ? __ldg(p.A + d * p.N + n) : 0.0f;
-        const float A2 = An * kLog2e;
-        const float* Bn = Bs + n * T + lane * kItems;
-        const float* Cn = Cs + n * T + lane * kItems;
-        float a[kItems], hloc[kItems], cp[kItems], Bv[kItems], Cv[kItems];
-        float P = 1.0f, H = 0.0f;
+      for (int pr = 0; pr < NP; ++pr) {
+        const float2 Ap = load_A_pair(p.A, d, N, pr, true);
+        const float2 A2 = make_float2(Ap.x * kLog2e, Ap.y * kLog2e);
+        float2 a[kItems], Bv[kItems], Cv[kItems];
+        lds_pairs<kItems>(Bs, pr, lane, Bv);
+        lds_pairs<kItems>(Cs, pr, lane, Cv);
+        // summaries of this thread's steps: forward map (P,H), adjoint map (Q,R)
+        //   lam_t = a_t * (gy_t*C_t + lam_{t+1})
+        float2 P = make_float2(1.f, 1.f), H = make_float2(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < kItems; ++j) {
-          Bv[j] = Bn[j];
-          Cv[j] = Cn[j];
-          a[j] = ex2(dt[j] * A2);
-          H = fmaf(a[j], H, dtu[j] * Bv[j]);
-          P *= a[j];
-          hloc[j] = H;
-          cp[j] = P;
+          const float2 x = __fmul2_rn(splat(dt[j]), A2);
+          a[j] = make_float2(ex2(x.x), ex2(x.y));
+          H = __ffma2_rn(a[j], H, __fmul2_rn(dtu2[j], Bv[j]));
+          P = __fmul2_rn(P, a[j]);
         }
-        float Pex, Hex, Ptot, Htot;
-        warp_scan_affine(P, H, lane, Pex, Hex, Ptot, Htot);
-        const float h_in = active ? __ldg(cs_in + n) : 0.0f;
-        const float hstart = fmaf(Pex, h_in, Hex);
-        // adjoint: lam_t = a_t * (gy_t*C_t + lam_{t+1}), right to left
-        float lloc[kItems], cq[kItems];
-        float Q = 1.0f, R = 0.0f;
+        float2 Q = make_float2(1.f, 1.f), R = make_float2(0.f, 0.f);
 #pragma unroll
         for (int j = kItems - 1; j >= 0; --j) {
-          R = a[j] * fmaf(gy[j], Cv[j], R);
-          Q *= a[j];
-          lloc[j] = R;
-          cq[j] = Q;
+          R = __fmul2_rn(a[j], __ffma2_rn(splat(gy[j]), Cv[j], R));
+          Q = __fmul2_rn(Q, a[j]);
         }
-        const float lam_in = lam[slot + n];                // lam entering the chunk from the right
-        float Qex, Rex, Qtot, Rtot;
-        warp_scan_affine_rev(Q, R, lane, Qex, Rex, Qtot, Rtot);
-        const float lstart = fmaf(Qex, lam_in, Rex);       // lam_{t+1} for this lane's last item
-        float dA_t = 0.0f;
-        float dBv[kItems], dCv[kItems];
+        float2 h_in;
+        h_in.x = __ldg(cs_in + 2 * pr);
+        h_in.y = (2 * pr + 1 < N) ? __ldg(cs_in + 2 * pr + 1) : 0.0f;
+        const float2 lam_in = lam[slot + pr];              // adjoint entering the chunk from the right
+        float2 Pex, Hex, Qex, Rex, Qtot, Rtot;
+        warp_scan_dual(P, H, Q, R, lane, Pex, Hex, Qex, Rex, Qtot, Rtot);
+        float2 h = __ffma2_rn(Pex, h_in, Hex);             // state entering this thread's steps
+        float2 lnext = __ffma2_rn(Qex, lam_in, Rex);       // lam_{t+1} of this thread's last step
+        // true states left to right (kept), then the adjoint right to left
+        float2 hprev[kItems], dCv[kItems], dBv[kItems];
+        lds_pairs<kItems>(accC, pr, lane, dCv);
+        lds_pairs<kItems>(accB, pr, lane, dBv);
+#pragma unroll
+        for (int j = 0; j < kItems; ++j) {
+          hprev[j] = h;
+          h = __ffma2_rn(a[j], h, __fmul2_rn(dtu2[j], Bv[j]));
+          y2[j] = __ffma2_rn(h, Cv[j], y2[j]);
+          dCv[j] = __ffma2_rn(splat(gy[j]), h, dCv[j]);
+        }
+        float2 dA2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int j = kItems - 1; j >= 0; --j) {
-          const float h = fmaf(cp[j], hstart, hloc[j]);
-          const float hprev = j > 0 ? fmaf(cp[j - 1], hstart, hloc[j - 1]) : hstart;
-          const float lam_next = j < kItems - 1 ? fmaf(cq[j + 1], lstart, lloc[j + 1]) : lstart;
-          const float G = fmaf(gy[j], Cv[j], lam_next);
-          const float q = (G * a[j]) * hprev;              // G * a_t * h_{t-1}
-          y[j] = fmaf(h, Cv[j], y[j]);
-          dCv[j] = gy[j] * h;
-          dBv[j] = G * dtu[j];
-          dus[j] = fmaf(G, Bv[j], dus[j]);
-          dA_t = fmaf(q, dt[j], dA_t);
-          ddts[j] = fmaf(q, An, ddts[j]);
+          const float2 G = __ffma2_rn(splat(gy[j]), Cv[j], lnext);
+          lnext = __fmul2_rn(G, a[j]);                     // lam_t
+          const float2 q = __fmul2_rn(lnext, hprev[j]);    // G * a_t * h_{t-1}
+          dBv[j] = __ffma2_rn(G, dtu2[j], dBv[j]);
+          dus2[j] = __ffma2_rn(G, Bv[j], dus2[j]);
+          dA2 = __ffma2_rn(q, splat(dt[j]), dA2);
+          ddts2[j] = __ffma2_rn(q, Ap, ddts2[j]);
         }
-        // carries for the next (earlier) chunk and per-channel dA
+        sts_pairs<kItems>(accC, pr, lane, dCv);
+        sts_pairs<kItems>(accB, pr, lane, dBv);
+        // carry for the next (earlier) chunk and per-channel dA
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) dA_t += __shfl_xor_sync(0xffffffffu, dA_t, off);
+        for (int off = 16; off > 0; off >>= 1) {
+          dA2.x += __shfl_xor_sync(0xffffffffu, dA2.x, off);
+          dA2.y += __shfl_xor_sync(0xffffffffu, dA2.y, off);
+        }
         if (lane == 0) {
-          lam[slot + n] = fmaf(Qtot, lam_in, Rtot);
-          dAacc[slot + n] += dA_t;
+          lam[slot + pr] = __ffma2_rn(Qtot, lam_in, Rtot);
+          dAacc[slot + pr] = __fadd2_rn(dAacc[slot + pr], dA2);
         }
-        // dB_t[n], dC_t[n]: sum over the kWarps channels processed in this iteration
-        // (single staging buffer, guarded by the two barriers below)
-        float* redB = red + warp * T + lane * kItems;
-        float* redC = red + kWarps * T + warp * T + lane * kItems;
-#pragma unroll
-        for (int j = 0; j < kItems; ++j) { redB[j] = dBv[j]; redC[j] = dCv[j]; }
-        __syncthreads();
-        for (int i = threadIdx.x; i < 2 * T; i += kThreads) {
-          const int which = i / T, t = i - which * T;
-          const float* src = red + which * kWarps * T + t;
-          float s = 0.0f;
-#pragma unroll
-          for (int w = 0; w < kWarps; ++w) s += src[w * T];
-          float* acc = (which ? dCs : dBs) + n * T + t;
-          *acc += s;
-        }
-        __syncthreads();
       }
-      if (active) {
-        // du_t = dt_t * sum_n G*B (+ gy*Dskip) ; ddt_t = sum_n q*A + u_t * sum_n G*B
-        float ds = 0.0f, dD_t = 0.0f;
-        if (p.Dskip) ds = __ldg(p.Dskip + d);
-        float duv[kItems], ddv[kItems];
+      // du_t = dt_t * sum_n G*B (+ gy*Dskip) ; ddt_t = sum_n q*A + u_t * sum_n G*B
+      float ds = 0.0f, dD_t = 0.0f;
+      if (p.Dskip) ds = __ldg(p.Dskip + d);
+      float duv[kItems], ddv[kItems];
+#pragma unroll
+      for (int j = 0; j < kItems; ++j) {
+        const float gb = dus2[j].x + dus2[j].y;
+        duv[j] = fmaf(dt[j], gb, gy[j] * ds);
+        ddv[j] = fmaf(u[j], gb, ddts2[j].x + ddts2[j].y);
+        dD_t = fmaf(gy[j], u[j], dD_t);
+      }
+      store_items<IO, kItems>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, duv);
+      store_items<float, kItems>(p.ddt + row, t0, p.L, p.vec_ok, ddv);
+      if (p.z) {
+        float dzv[kItems];
 #pragma unroll
         for (int j = 0; j < kItems; ++j) {
-          duv[j] = fmaf(dt[j], dus[j], gy[j] * ds);
-          ddv[j] = fmaf(u[j], dus[j], ddts[j]);
-          dD_t = fmaf(gy[j], u[j], dD_t);
+          const float sg = sigmoidf(zz[j]);
+          const float yy = fmaf(ds, u[j], y2[j].x + y2[j].y);
+          dzv[j] = go[j] * yy * (sg * (1.0f + zz[j] * (1.0f - sg)));
         }
-        store_items<IO, kItems>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, duv);
-        store_items<float, kItems>(p.ddt + row, t0, p.L, p.vec_ok, ddv);
-        if (p.z) {
-          float dzv[kItems];
-#pragma unroll
-          for (int j = 0; j < kItems; ++j) {
-            const float sg = sigmoidf(zz[j]);
-            const float yy = fmaf(ds, u[j], y[j]);
-            dzv[j] = dout_raw[j] * yy * (sg * (1.0f + zz[j] * (1.0f - sg)));
-          }
-          store_items<IO, kItems>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dzv);
-        }
-        if (p.dD_part) {
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) dD_t += __shfl_xor_sync(0xffffffffu, dD_t, off);
-          if (lane == 0) dDacc[warp * kCI + ci] += dD_t;
-        }
+        store_items<IO, kItems>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dzv);
       }
+      if (p.dD_part) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dD_t += __shfl_xor_sync(0xffffffffu, dD_t, off);
+        if (lane == 0) dDacc[warp * kCI + ci] += dD_t;
+      }
+#pragma unroll
+      for (int j = 0; j < kItems; ++j) { u[j] = nu[j]; dt[j] = ndt[j]; go[j] = ngo[j]; zz[j] = nz[j]; }
       __syncwarp();
     }
-    // flush this chunk's dB/dC sums (over this CTA's channels) to global
+    // sum the warps' private tiles and flush this chunk's dB/dC to global
     __syncthreads();
     for (int i = threadIdx.x; i < N * T; i += kThreads) {
       const int n = i / T, t = i - n * T;
       const long long tt = t_base + t;
       if (tt < p.L) {
-        atomicAdd(p.dB + (b * p.N + n) * p.L + tt, dBs[i]);
-        atomicAdd(p.dC + (b * p.N + n) * p.L + tt, dCs[i]);
+        const int ti = tile_index<kItems>(n >> 1, t, n & 1);
+        float sb = 0.0f, sc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          sb += acc[w * 2 * tile + ti];
+          sc += acc[w * 2 * tile + tile + ti];
+        }
+        atomicAdd(p.dB + (b * p.N + n) * p.L + tt, sb);
+        atomicAdd(p.dC + (b * p.N + n) * p.L + tt, sc);
       }
     }
   }
@@ -458,7 +582,10 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   for (int i = threadIdx.x; i < kWarps * kCI * N; i += kThreads) {
     const int wc = i / N, n = i - wc * N;
     const long long d = (long long)blockIdx.x * kChannelsPerCta + wc;
-    if (d < p.D) p.dA_part[(b * p.D + d) * p.N + n] = dAacc[i];
+    if (d < p.D) {
+      const float2 v = dAacc[wc * NP + (n >> 1)];
+      p.dA_part[(b * p.D + d) * p.N + n] = (n & 1) ? v.y : v.x;
+    }
   }
   if (p.dD_part) {
     for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) {
@@ -478,7 +605,16 @@ __global__ void sscan_reduce_batch_kernel(const float* __restrict__ part, float*
   out[i] = (float)s;
 }
 
-static int items_for(long long N) {
+// Steps per thread.  The backward keeps more per-step values in registers and a
+// private accumulator tile per warp in shared memory, so it works on shorter
+// chunks than the forward; the forward saves the states the backward needs at
+// the backward's chunk interval.
+static int items_bwd(long long N) {
+  if (N <= 16) return 4;
+  if (N <= 32) return 2;
+  return 1;
+}
+static int items_fwd(long long N) {
   if (N <= 16) return 8;
   if (N <= 32) return 4;
   if (N <= 64) return 2;
@@ -494,7 +630,8 @@ static int set_smem(K kernel, size_t bytes) {
 template <typename IO, int kItems>
 static int launch_fwd(const Params& p, cudaStream_t stream) {
   const int T = 32 * kItems;
-  const size_t smem = sizeof(float) * (2 * (size_t)p.N * T + (size_t)kWarps * kCI * p.N);
+  const size_t np2 = 2 * (size_t)((p.N + 1) / 2);
+  const size_t smem = sizeof(float) * (2 * np2 * T + (size_t)kWarps * kCI * np2);
   if (smem > 200 * 1024) { set_last_error("selective_scan_forward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_forward_kernel<IO, kItems>, smem)) return rc;
   dim3 grid((unsigned)((p.D + kChannelsPerCta - 1) / kChannelsPerCta), (unsigned)p.B);
@@ -505,9 +642,10 @@ static int launch_fwd(const Params& p, cudaStream_t stream) {
 template <typename IO, int kItems>
 static int launch_bwd(const Params& p, cudaStream_t stream) {
   const int T = 32 * kItems;
-  const size_t smem = sizeof(float) * (4 * (size_t)p.N * T + 2 * (size_t)kWarps * T +
-                                       2 * (size_t)kWarps * kCI * p.N + kWarps * kCI);
-  if (smem > 200 * 1024) { set_last_error("selective_scan_backward: d_state too large"); return kErrUnsupported; }
+  const size_t np2 = 2 * (size_t)((p.N + 1) / 2);
+  const size_t smem = sizeof(float) * ((2 + 2 * (size_t)kWarps) * np2 * T + 2 * (size_t)kWarps * kCI * np2 +
+                                       kWarps * kCI);
+  if (smem > 220 * 1024) { set_last_error("selective_scan_backward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_backward_kernel<IO, kItems>, smem)) return rc;
   dim3 grid((unsigned)((p.D + kChannelsPerCta - 1) / kChannelsPerCta), (unsigned)p.B);
   sscan_backward_kernel<IO, kItems><<<grid, kThreads, smem, stream>>>(p);
@@ -516,11 +654,18 @@ static int launch_bwd(const Params& p, cudaStream_t stream) {
 
 template <typename IO>
 static int dispatch_items(bool backward, const Params& p, cudaStream_t stream) {
-  switch (items_for(p.N)) {
-    case 8: return backward ? launch_bwd<IO, 8>(p, stream) : launch_fwd<IO, 8>(p, stream);
-    case 4: return backward ? launch_bwd<IO, 4>(p, stream) : launch_fwd<IO, 4>(p, stream);
-    case 2: return backward ? launch_bwd<IO, 2>(p, stream) : launch_fwd<IO, 2>(p, stream);
-    default: return backward ? launch_bwd<IO, 1>(p, stream) : launch_fwd<IO, 1>(p, stream);
+  if (backward) {
+    switch (items_bwd(p.N)) {
+      case 4: return launch_bwd<IO, 4>(p, stream);
+      case 2: return launch_bwd<IO, 2>(p, stream);
+      default: return launch_bwd<IO, 1>(p, stream);
+    }
+  }
+  switch (items_fwd(p.N)) {
+    case 8: return launch_fwd<IO, 8>(p, stream);
+    case 4: return launch_fwd<IO, 4>(p, stream);
+    case 2: return launch_fwd<IO, 2>(p, stream);
+    default: return launch_fwd<IO, 1>(p, stream);
   }
 }
 
@@ -533,11 +678,11 @@ extern "C" {
 
 using namespace ossm_b200;
 
-int ossm_b200_selective_scan_chunk(int64_t N) { return 32 * sscan::items_for(N); }
+int ossm_b200_selective_scan_chunk(int64_t N) { return 32 * sscan::items_bwd(N); }
 
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N) {
   if (B <= 0 || D <= 0 || L <= 0 || N <= 0) return 0;
-  const int64_t T = 32 * sscan::items_for(N);
+  const int64_t T = 32 * sscan::items_bwd(N);
   return (size_t)B * D * ((L + T - 1) / T) * N * sizeof(float);
 }
 
@@ -553,7 +698,7 @@ static int sscan_check(const char* fn, const void* u, const float* dt, const flo
     set_last_error("%s: unknown io dtype %d", fn, io_dtype);
     return kErrInvalidArgument;
   }
-  if (N > 128) { set_last_error("%s: d_state > 128 is not supported", fn); return kErrUnsupported; }
+  if (N > 64) { set_last_error("%s: d_state > 64 is not supported", fn); return kErrUnsupported; }
   if (B > 65535) { set_last_error("%s: batch > 65535 is not supported", fn); return kErrUnsupported; }
   if (B == 0 || D == 0 || L == 0 || N == 0) return kOk;
   if (!u || !dt || !A || !Bm || !Cm) { set_last_error("%s: null input pointer", fn); return kErrInvalidArgument; }
@@ -574,6 +719,8 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
   p.u = u; p.dt = dt; p.A = A; p.Bm = Bm; p.Cm = Cm; p.z = z; p.Dskip = Dskip; p.out = out;
   p.chunk_states = chunk_states;
   p.B = B; p.D = D; p.L = L; p.N = N;
+  p.state_interval = 32 * sscan::items_bwd(N);
+  p.nstates = (L + p.state_interval - 1) / p.state_interval;
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(out) && (!z || sscan::aligned16(z)) &&
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
@@ -611,6 +758,8 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.dA_part = static_cast<float*>(workspace);
   p.dD_part = Dskip ? p.dA_part + (size_t)B * D * N : nullptr;
   p.B = B; p.D = D; p.L = L; p.N = N;
+  p.state_interval = 32 * sscan::items_bwd(N);
+  p.nstates = (L + p.state_interval - 1) / p.state_interval;
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(dout) && sscan::aligned16(du) &&
              sscan::aligned16(ddt) && (!z || (sscan::aligned16(z) && sscan::aligned16(dz))) &&

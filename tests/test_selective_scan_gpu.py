@@ -93,7 +93,7 @@ def test_reference_fixtures(tag):
 
 SHAPES = [
     (1, 1, 1, 1), (2, 3, 7, 4), (1, 5, 255, 16), (2, 9, 256, 16), (1, 70, 257, 16),   # around one chunk, ragged D
-    (2, 64, 600, 16), (1, 8, 300, 32), (1, 4, 200, 64), (1, 3, 100, 100), (3, 130, 33, 8),
+    (2, 64, 600, 16), (1, 8, 300, 32), (1, 4, 200, 64), (1, 3, 100, 48), (3, 130, 33, 8),
 ]
 
 
