@@ -220,7 +220,10 @@ def run_ours(args):
 
     L, B, P = args.length, args.batch, args.ssm
     variant = args.variant
-    a, g, dt = make_params(P, dev, seed=rank)         # this rank's oscillator shard
+    from ossm_b200.sharding import aggregate_throughput, shard_channels
+
+    # one layer of P * world oscillators; this rank owns a contiguous shard of P of them
+    a, g, dt = (shard_channels(t, world, rank) for t in make_params(P * world, dev, seed=0))
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     bu = torch.randn(L, B, P, 2, generator=gen, device=dev)
     bu = torch.view_as_complex(bu.mul_(0.5))
@@ -238,16 +241,15 @@ def run_ours(args):
             record[2].record()
         return x, grads
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()             # sampled over warm-up + timed region (both run the same kernels back to back)
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     t_begin = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
@@ -263,15 +265,12 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
-    if world > 1:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    total_elems, total_ms = aggregate_throughput(elems, total_ms, dev)   # sum of units, max of time over ranks
     status = _lib.device_status()
     if status != 0:
         raise SystemExit(f"bench.py: device status {status} (a bounded wait inside a kernel gave up)")
     ms_per_step = total_ms / args.steps
-    value = elems * world / (ms_per_step * 1e-3) / 1e9
+    value = total_elems / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end through the public op with host buffers ----------------
     e2e = None
@@ -311,11 +310,8 @@ def run_ours(args):
         e1.record()
         torch.cuda.synchronize()
         e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        e2e = {"value": elems * world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+        _, e2e_ms = aggregate_throughput(elems, e2e_ms, dev)
+        e2e = {"value": total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": 2 * elems * 8, "d2h_bytes_per_step": 2 * elems * 8 + 3 * P * 4,
                "ms_per_step": e2e_ms, "api": "ossm_b200.dlinoss.run_dlinoss + autograd, pinned host buffers"}
 
