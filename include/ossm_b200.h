@@ -92,6 +92,27 @@ int ossm_b200_lti_scan_backward_states(int variant, const float* a, const float*
                                        size_t workspace_bytes, int64_t L, int64_t B, int64_t P,
                                        ossm_b200_stream_t stream);
 
+/* Backward for callers that cannot provide scratch memory (no counterpart in the
+ * reference).  Same arguments and results as ossm_b200_lti_scan_backward minus the
+ * workspace: the per-series partial sums go to a fixed 1.5 MiB array that is part of
+ * the library image on every GPU that loads it.  Meant for hosts that may not
+ * allocate device memory when the call is made -- a serving or control process that
+ * freezes its allocations after start-up, or a foreign-language stub (cgo, JNI) that
+ * owns no CUDA allocator.  Limits and rules:
+ *   - B*P must not exceed ossm_b200_lti_scan_backward_static_max_series() (65536);
+ *     larger problems are refused with OSSM_B200_ERR_WORKSPACE;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU
+ *     (different streams) race -- keep them on one stream or serialise them;
+ *   - the first call on each device looks up the array's device address; make that
+ *     call, with the device current, before starting any stream capture;
+ *   - nothing in the array has to be cleared between calls (every element that is
+ *     read has been written by the same call). */
+size_t ossm_b200_lti_scan_backward_static_max_series(void);
+int ossm_b200_lti_scan_backward_static(int variant, const float* a, const float* g, const float* step,
+                                       const void* bu, const void* carries, const void* grad_x, void* grad_bu,
+                                       float* grad_a, float* grad_g, float* grad_step, int64_t L, int64_t B,
+                                       int64_t P, ossm_b200_stream_t stream);
+
 /* Launch-shape knobs ("fwd_ring", "fwd_warps", "bwd_ring", "bwd_warps",
  * "force_plain"); process-wide, meant for benchmarking. */
 int ossm_b200_lti_set_tuning(const char* key, int value);

@@ -31,6 +31,8 @@ SIGNATURES = {
     "ossm_b200_lti_scan_backward_states": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_size_t, c_int64, c_int64, c_int64, c_void_p]),
+    "ossm_b200_lti_scan_backward_static_max_series": (c_size_t, []),
+    "ossm_b200_lti_scan_backward_static": (c_int, [c_int] + [c_void_p] * 10 + [c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_lti_set_tuning": (c_int, [c_char_p, c_int]),
     "ossm_b200_selective_scan_chunk": (c_int, [c_int64]),
     "ossm_b200_selective_scan_state_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),

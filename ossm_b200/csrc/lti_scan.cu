@@ -761,6 +761,65 @@ int ossm_b200_lti_scan_backward(int variant, const float* a, const float* g, con
                          grad_g, grad_step, workspace, workspace_bytes, L, B, P, stream);
 }
 
+// ---------------------------------------------------------------------------
+// Backward without any allocation by the caller or by this library.
+//
+// Some hosts of this code cannot hand out scratch memory at call time: a plugin
+// running inside an inference server or a real-time control loop that forbids
+// device allocation after start-up, or a binding written in a language whose
+// runtime owns no CUDA allocator (a cgo / JNI stub that only forwards pointers it
+// was given).  For them the per-series partial sums of the backward live in a
+// fixed array inside the library image instead of a caller-supplied workspace.
+// The array is part of every context that loads the library (kStaticSeries * 6
+// floats = 1.5 MiB per GPU, held until the process exits).
+// ---------------------------------------------------------------------------
+namespace ossm_b200 {
+namespace lti {
+constexpr long long kStaticSeries = 65536;  // largest B*P the allocation-free entry point accepts
+static __device__ __align__(256) float g_static_partials[kNumAcc * kStaticSeries];
+
+// The array's name is only a host-side handle; the kernels need its device
+// address, which differs per device.  Looked up once per device, with that device
+// current, and cached.
+static int static_partials_ptr(float** out) {
+  static float* cached[64] = {nullptr};
+  int dev = -1;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= 64) {
+    set_last_error("lti_scan_backward_static: device ordinal %d out of range", dev);
+    return kErrUnsupported;
+  }
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (int rc = check_cuda(cudaGetSymbolAddress(&ptr, g_static_partials), "cudaGetSymbolAddress(static scratch)"))
+      return rc;
+    cached[dev] = static_cast<float*>(ptr);
+  }
+  *out = cached[dev];
+  return kOk;
+}
+}  // namespace lti
+}  // namespace ossm_b200
+
+size_t ossm_b200_lti_scan_backward_static_max_series(void) { return (size_t)ossm_b200::lti::kStaticSeries; }
+
+int ossm_b200_lti_scan_backward_static(int variant, const float* a, const float* g, const float* step,
+                                       const void* bu, const void* carries, const void* grad_x, void* grad_bu,
+                                       float* grad_a, float* grad_g, float* grad_step, int64_t L, int64_t B,
+                                       int64_t P, cudaStream_t stream) {
+  if (B > 0 && P > 0 && (B > kStaticSeries || P > kStaticSeries || B * P > kStaticSeries)) {
+    set_last_error("lti_scan_backward_static: B*P = %lld series exceed the built-in scratch (%lld); use "
+                   "lti_scan_backward with a caller workspace",
+                   (long long)(B * P), (long long)kStaticSeries);
+    return kErrWorkspace;
+  }
+  float* scratch = nullptr;
+  if (int rc = static_partials_ptr(&scratch)) return rc;
+  return backward_common("lti_scan_backward_static", variant, a, g, step, bu, carries, 1, -1, grad_x, grad_bu,
+                         grad_a, grad_g, grad_step, scratch, sizeof(float) * kNumAcc * kStaticSeries, L, B, P,
+                         stream);
+}
+
 int ossm_b200_lti_scan_backward_states(int variant, const float* a, const float* g, const float* step,
                                        const void* bu, const void* states, const void* grad_x, void* grad_bu,
                                        float* grad_a, float* grad_g, float* grad_step, void* workspace,
