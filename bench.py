@@ -28,7 +28,6 @@ import os
 import statistics
 import subprocess
 import sys
-import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -39,13 +38,14 @@ METRIC = "dlinoss_scan_fwd_bwd_gelem_per_s"
 UNIT = "Gelem/s"
 FWD_BYTES = 16      # read bu 8 + write x 8                        (per scan element)
 BWD_BYTES = 24      # read grad_x 8 + read bu 8 + write grad_bu 8  (per scan element)
+BWD_DRAM_BYTES_PER_ELEM = 1.608e9 / (64 * 4096 * 256)   # measured DRAM traffic of one backward launch
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", default="imex1")
     ap.add_argument("--batch", type=int, default=64)
@@ -78,55 +78,82 @@ def make_params(P, device, seed):
 # clocks
 # ---------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs.
+
+    Uses NVML (read-only queries) from a background thread every ~2 ms, because the
+    timed region of this memory-bound benchmark lasts tens of milliseconds, shorter
+    than one `nvidia-smi -lms` period; falls back to `nvidia-smi` when NVML is not
+    importable.
+    """
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
     def __init__(self, index):
         self.index = index
-        self.proc = None
-        self.path = None
+        self.samples = []
+        self.mask = 0
+        self.max_mhz = None
+        self._stop = False
+        self._thread = None
+        self._nvml = None
+
+    def _loop(self):
+        nv, h = self._nvml
+        while not self._stop:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        import threading
+
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self._nvml = (nv, h)
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
         except Exception:
-            self.proc = None
+            self._nvml = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        time.sleep(0.15)
-        self.proc.terminate()
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": "nvml"}
+        if self._nvml is None:
+            return self._smi_once(out)
+        self._stop = True
+        self._thread.join(timeout=2)
+        if self.samples:
+            out.update(sm_mhz=statistics.median(self.samples), sm_max_mhz=self.max_mhz, samples=len(self.samples),
+                       reasons=[name for name, bit in self.REASONS if self.mask & bit])
+        return out
+
+    def _smi_once(self, out):
         try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        try:
-            for line in open(self.path):
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
-                    continue
-                try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
-                except ValueError:
-                    continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
-                                     parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
+            txt = subprocess.run(
+                ["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_power_cap", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                capture_output=True, text=True, timeout=20).stdout.strip().splitlines()[0]
+            parts = [p.strip() for p in txt.split(",")]
+            out.update(sm_mhz=float(parts[0]), sm_max_mhz=float(parts[1]), samples=1, source="nvidia-smi (one sample)",
+                       reasons=[n for (n, _), v in zip(self.REASONS, parts[2:6]) if v.lower().startswith("active")])
         except Exception:
             pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
 
 
@@ -241,15 +268,15 @@ def run_ours(args):
             record[2].record()
         return x, grads
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()             # sampled over warm-up + timed region (both run the same kernels back to back)
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     t_begin = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
@@ -340,15 +367,10 @@ def run_ours(args):
         "step": {"achieved": step_gbs, "frac": step_gbs / peak,
                  "algorithmic_bytes": elems * (FWD_BYTES + BWD_BYTES)},
     }
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    try:
-        tr = json.load(open(traffic_file))
-        per_elem = tr.get("lti_backward_kernel", {}).get("dram_bytes_per_elem")
-        if per_elem:
-            roofline["traffic"] = per_elem * elems
-            roofline["traffic_source"] = tr["lti_backward_kernel"].get("source")
-    except Exception:
-        pass
+    # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at config 1, from the ncu capture
+    # summarised in profiles/lti_scan_config1_dram_traffic.md (1.608 GB for 67.1 M elements), scaled by elements.
+    roofline["traffic"] = BWD_DRAM_BYTES_PER_ELEM * elems
+    roofline["traffic_source"] = "ncu dram__bytes_read.sum+dram__bytes_write.sum, profiles/lti_scan_config1_dram_traffic.md"
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
