@@ -312,18 +312,39 @@ def run_ours(args):
         d_bu = torch.empty_like(bu)
         d_gx = torch.empty_like(gx)
 
+        # Copies run on two side streams so that PCIe traffic in both directions overlaps
+        # with itself and with the kernels: grad_x goes up while the forward runs, x comes
+        # down while grad_x is still going up and the backward runs.
+        main = torch.cuda.current_stream()
+        up, down = torch.cuda.Stream(), torch.cuda.Stream()
+
         def e2e_step():
-            d_bu.copy_(h_bu, non_blocking=True)
-            d_gx.copy_(h_gx, non_blocking=True)
+            up.wait_stream(main)                       # previous step no longer reads the device inputs
+            with torch.cuda.stream(up):
+                d_bu.copy_(h_bu, non_blocking=True)
+                bu_ready = torch.cuda.Event()
+                bu_ready.record(up)
+                d_gx.copy_(h_gx, non_blocking=True)
+                gx_ready = torch.cuda.Event()
+                gx_ready.record(up)
             a_, g_, dt_ = (t.detach().requires_grad_(True) for t in (a, g, dt))
+            main.wait_event(bu_ready)
             bu_ = d_bu.detach().requires_grad_(True)
             x = run_dlinoss(variant, a_, g_, dt_, bu_)
+            down.wait_stream(main)
+            with torch.cuda.stream(down):
+                h_x.copy_(x.detach(), non_blocking=True)
+            main.wait_event(gx_ready)
             x.backward(d_gx)
-            h_x.copy_(x.detach(), non_blocking=True)
-            h_gbu.copy_(bu_.grad, non_blocking=True)
-            h_pg[0].copy_(a_.grad, non_blocking=True)
-            h_pg[1].copy_(g_.grad, non_blocking=True)
-            h_pg[2].copy_(dt_.grad, non_blocking=True)
+            down.wait_stream(main)
+            with torch.cuda.stream(down):
+                h_gbu.copy_(bu_.grad, non_blocking=True)
+                h_pg[0].copy_(a_.grad, non_blocking=True)
+                h_pg[1].copy_(g_.grad, non_blocking=True)
+                h_pg[2].copy_(dt_.grad, non_blocking=True)
+            main.wait_stream(down)                     # results are on the host when the step ends
+            x.record_stream(down)
+            bu_.grad.record_stream(down)
 
         e2e_step()
         torch.cuda.synchronize()
