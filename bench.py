@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba"],
+                    help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
+                         "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16)")
     ap.add_argument("--variant", default="imex1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--length", type=int, default=4096)
@@ -419,10 +422,88 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_secondary(args):
+    """Side workloads (single GPU, kernels only): BASELINE config 2 and config 3.  Same
+    timing rules as the headline; one JSON line with its own metric name."""
+    import torch
+
+    from ossm_b200 import _lib, kernels
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device")
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    if args.workload == "linoss":
+        L, B, P = (16384, 128, 128) if args.length == 4096 else (args.length, args.batch, args.ssm)
+        a = torch.relu(torch.randn(P, generator=gen, device=dev))
+        dt = torch.sigmoid(torch.randn(P, generator=gen, device=dev))
+        bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev) * 0.5)
+        gx = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev))
+        elems, fb, bb = L * B * P, FWD_BYTES, BWD_BYTES
+        name = f"LinOSS-IM scan fwd+bwd, B={B} L={L} P={P}, complex64 (BASELINE config 2)"
+        metric = "linoss_scan_fwd_bwd_gelem_per_s"
+
+        def fwd():
+            return kernels.lti_scan_forward("linoss_im", a, None, dt, bu)
+
+        def bwd(saved):
+            return kernels.lti_scan_backward("linoss_im", a, None, dt, bu, saved[2], gx)
+    else:
+        Bz, Dn, L, N = (32, 2048, 8192, 16) if args.length == 4096 else (args.batch, 2048, args.length, 16)
+        io = torch.bfloat16
+        u = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
+        z = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
+        delta = torch.nn.functional.softplus(torch.randn(Bz, Dn, L, generator=gen, device=dev) - 4)
+        A = -torch.arange(1, N + 1, device=dev, dtype=torch.float32).repeat(Dn, 1)
+        Bt = torch.randn(Bz, N, L, generator=gen, device=dev).to(io)      # given time-contiguous [B, N, L]
+        Ct = torch.randn(Bz, N, L, generator=gen, device=dev).to(io)
+        Dv = torch.ones(Dn, device=dev)
+        go = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
+        elems, fb, bb = Bz * Dn * L, 10, 18      # u 2 + delta 4 + z 2 -> out 2 ; + dout 2 -> du 2, ddelta 4, dz 2
+        name = f"Mamba selective scan fwd+bwd, B={Bz} D={Dn} L={L} N={N}, bf16 I/O, fp32 state (BASELINE config 3)"
+        metric = "selective_scan_fwd_bwd_gelem_per_s"
+
+        def fwd():
+            return kernels.selective_scan_fwd(u, delta, A, Bt.transpose(1, 2), Ct.transpose(1, 2), z, Dv)
+
+        def bwd(saved):
+            return kernels.selective_scan_bwd(go, u, delta, A, Bt.transpose(1, 2), Ct.transpose(1, 2), z, saved[1], Dv)
+
+    for _ in range(max(args.warmup, 3)):
+        bwd(fwd())
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    for e in evs:
+        e[0].record()
+        saved = fwd()
+        e[1].record()
+        bwd(saved)
+        e[2].record()
+    torch.cuda.synchronize()
+    if _lib.device_status() != 0:
+        raise SystemExit("bench.py: device status non-zero")
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    ms = evs[0][0].elapsed_time(evs[-1][2]) / args.steps
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        peak = 6650.0
+    gbs = elems * (fb + bb) / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": metric, "value": elems / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+        "config": {"workload": name}, "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "algorithmic_bytes_per_elem": fb + bb}}))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "dlinoss":
+        run_secondary(args)
     else:
         run_ours(args)
 
