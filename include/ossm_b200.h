@@ -61,8 +61,11 @@ int ossm_b200_lti_chunk(void);
 /* Bytes of the carry buffer written by forward and read by backward:
  * (ceil(L/chunk) - 1) * B * P * 16. */
 size_t ossm_b200_lti_carry_bytes(int64_t L, int64_t B, int64_t P);
-/* Bytes of scratch the backward needs (per-series partial sums, 6*B*P floats). */
+/* Bytes of scratch the backward needs: per-series partial sums (6*B*P floats) and, when a
+ * long sequence of few series is split into time segments, the segment summaries. */
 size_t ossm_b200_lti_backward_workspace_bytes(int64_t L, int64_t B, int64_t P);
+/* Bytes of scratch for ossm_b200_lti_scan_forward_ws (0 unless the sequence is split). */
+size_t ossm_b200_lti_forward_workspace_bytes(int64_t L, int64_t B, int64_t P);
 
 /* Forward.  Any of the three outputs may be NULL, but not both x and states:
  *   x       : complex64 [L, B, P]      position state x_t (the op's result)
@@ -73,6 +76,17 @@ size_t ossm_b200_lti_backward_workspace_bytes(int64_t L, int64_t B, int64_t P);
 int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, const float* step, const void* bu,
                                void* x, void* states, void* carries, int64_t L, int64_t B, int64_t P,
                                ossm_b200_stream_t stream);
+
+/* Forward with scratch (16-byte aligned).  With fewer than ~12k series the time axis is
+ * split into segments that run on different SMs: a summary pass finds every segment's
+ * end state, a stitching kernel turns them into entry states (segment transition by
+ * matrix power in double precision), and the scan proper starts each segment from its
+ * entry state.  Results are those of ossm_b200_lti_scan_forward up to rounding of the
+ * entry states.  The reference has one thread per series for any shape
+ * (dlinoss_imex1_cuda.cu:189-197). */
+int ossm_b200_lti_scan_forward_ws(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                  void* x, void* states, void* carries, void* workspace, size_t workspace_bytes,
+                                  int64_t L, int64_t B, int64_t P, ossm_b200_stream_t stream);
 
 /* Backward from the saved carries (recomputes the states chunk by chunk).
  *   grad_x : complex64 [L, B, P]  upstream gradient on x (contiguous)
@@ -113,8 +127,9 @@ int ossm_b200_lti_scan_backward_static(int variant, const float* a, const float*
                                        float* grad_a, float* grad_g, float* grad_step, int64_t L, int64_t B,
                                        int64_t P, ossm_b200_stream_t stream);
 
-/* Launch-shape knobs ("fwd_ring", "fwd_warps", "bwd_ring", "bwd_warps",
- * "force_plain"); process-wide, meant for benchmarking. */
+/* Launch-shape knobs ("fwd_ring", "fwd_warps", "bwd_ring", "bwd_warps", "force_plain",
+ * "segments" = forced number of time segments, 0 = automatic); process-wide, meant for
+ * benchmarking and tests. */
 int ossm_b200_lti_set_tuning(const char* key, int value);
 
 /* ---- generic LinOSS scan (complex 2x2 per channel, forcing per step) --------

@@ -23,6 +23,9 @@ SIGNATURES = {
     "ossm_b200_lti_chunk": (c_int, []),
     "ossm_b200_lti_carry_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "ossm_b200_lti_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "ossm_b200_lti_forward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "ossm_b200_lti_scan_forward_ws": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_size_t, c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_lti_scan_forward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_lti_scan_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

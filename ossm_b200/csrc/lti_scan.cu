@@ -120,6 +120,10 @@ struct FwdParams {
   float4* carries;       // [nchunks-1, N] or null
   long long L, N, P;
   int ring;              // stages per warp
+  // time segments (grid.y): segment s covers chunks [s*seg_chunks, (s+1)*seg_chunks)
+  long long seg_chunks;  // chunks per segment (>= nchunks when the sequence is not split)
+  const float4* seg_init;  // [S, N] state entering each segment, or null (zero)
+  float4* seg_end;         // [S, N] state leaving each segment (summary pass), or null
 };
 
 // Shared memory per warp: ring * kStageBytes, preceded (per CTA) by the barriers.
@@ -138,9 +142,16 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
   const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step[ch]);
 
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
+  const long long k0 = (long long)blockIdx.y * p.seg_chunks;            // this CTA's time segment
+  const long long k1 = (k0 + p.seg_chunks) < nchunks ? (k0 + p.seg_chunks) : nchunks;
   float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-  float2* xp = (kOut & 1) ? p.x + n : nullptr;
-  float4* sp = (kOut & 2) ? p.states + n : nullptr;
+  if (p.seg_init && valid) {
+    const float4 v = p.seg_init[(long long)blockIdx.y * p.N + n];
+    s0 = make_float2(v.x, v.y);
+    s1 = make_float2(v.z, v.w);
+  }
+  float2* xp = (kOut & 1) ? p.x + k0 * kChunk * p.N + n : nullptr;
+  float4* sp = (kOut & 2) ? p.states + k0 * kChunk * p.N + n : nullptr;
 
   if constexpr (kTma) {
     // All warps of the CTA consume the same stage (one TMA box of kChunk rows x
@@ -155,16 +166,17 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
       for (int s = 0; s < p.ring; ++s) mbar_init(&bars[s], 1);
       fence_barrier_init();
       fence_proxy_async();
-      const int pre = (int)(nchunks < p.ring ? nchunks : p.ring);
+      const int pre = (int)((k1 - k0) < p.ring ? (k1 - k0) : p.ring);
       for (int s = 0; s < pre; ++s) {
         mbar_expect_tx(&bars[s], stage_bytes);
-        tma_load_2d(ring_base + (size_t)s * stage_bytes, &tm_bu, &bars[s], (int32_t)(cta_col0 * 2), s * kChunk);
+        tma_load_2d(ring_base + (size_t)s * stage_bytes, &tm_bu, &bars[s], (int32_t)(cta_col0 * 2),
+                    (int32_t)((k0 + s) * kChunk));
       }
     }
     __syncthreads();
     int slot = 0;
     uint32_t parity = 0;
-    for (long long k = 0; k < nchunks; ++k) {
+    for (long long k = k0; k < k1; ++k) {
       if (!mbar_wait(&bars[slot], parity)) return;
       const float2* stage = reinterpret_cast<const float2*>(ring_base + (size_t)slot * stage_bytes) + threadIdx.x;
       const int rows = (int)((p.L - k * kChunk) < kChunk ? (p.L - k * kChunk) : kChunk);
@@ -193,7 +205,7 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
       }
       if (p.carries && valid && k + 1 < nchunks) p.carries[k * p.N + n] = make_float4(s0.x, s0.y, s1.x, s1.y);
       __syncthreads();  // every warp is done reading this slot
-      if (threadIdx.x == 0 && k + p.ring < nchunks) {
+      if (threadIdx.x == 0 && k + p.ring < k1) {
         fence_proxy_async();
         mbar_expect_tx(&bars[slot], stage_bytes);
         tma_load_2d(ring_base + (size_t)slot * stage_bytes, &tm_bu, &bars[slot], (int32_t)(cta_col0 * 2),
@@ -201,6 +213,7 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
       }
       if (++slot == p.ring) { slot = 0; parity ^= 1; }
     }
+    if (p.seg_end && valid) p.seg_end[(long long)blockIdx.y * p.N + n] = make_float4(s0.x, s0.y, s1.x, s1.y);
   } else {
     // Plain-load path for views TMA cannot describe (odd N, unaligned base):
     // register double-buffering of kBatch rows.
@@ -246,9 +259,11 @@ struct BwdParams {
   const float4* carry_src; // state at the end of row (c*carry_mul + carry_off), see below
   long long carry_mul, carry_off;
   float2* grad_bu;         // [L, N]
-  float* partials;         // [kNumAcc, N]
+  float* partials;         // [kNumAcc, S*N] (segment-major inside each accumulator)
   long long L, N, P;
   int ring;
+  long long seg_chunks;       // chunks per time segment (grid.y segments)
+  const float4* lam_init;     // [S, N] adjoint entering each segment from the right, or null (zero)
 };
 
 // Kahan-compensated add of a chunk-local sum into a running total.
@@ -313,7 +328,15 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
   float acc[kNumAcc], comp[kNumAcc];
 #pragma unroll
   for (int i = 0; i < kNumAcc; ++i) { acc[i] = 0.f; comp[i] = 0.f; }
+  const long long k0 = (long long)blockIdx.y * p.seg_chunks;            // this CTA's time segment [k0, k1)
+  const long long k1 = (k0 + p.seg_chunks) < nchunks ? (k0 + p.seg_chunks) : nchunks;
+  const long long nseg = k1 - k0;
   float2 l0 = make_float2(0.f, 0.f), l1 = make_float2(0.f, 0.f);  // adjoint carried to earlier times
+  if (p.lam_init && valid) {
+    const float4 v = p.lam_init[(long long)blockIdx.y * p.N + n];
+    l0 = make_float2(v.x, v.y);
+    l1 = make_float2(v.z, v.w);
+  }
 
   auto load_carry = [&](long long chunk) -> float4 {
     if (chunk <= 0 || !valid) return make_float4(0.f, 0.f, 0.f, 0.f);
@@ -333,9 +356,9 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
       for (int s = 0; s < p.ring; ++s) mbar_init(&bars[s], 1);
       fence_barrier_init();
       fence_proxy_async();
-      const int pre = (int)(nchunks < p.ring ? nchunks : p.ring);
+      const int pre = (int)(nseg < p.ring ? nseg : p.ring);
       for (int s = 0; s < pre; ++s) {
-        const int32_t row = (int32_t)((nchunks - 1 - s) * kChunk);
+        const int32_t row = (int32_t)((k1 - 1 - s) * kChunk);
         unsigned char* dst = ring_base + (size_t)s * pair_bytes;
         mbar_expect_tx(&bars[s], pair_bytes);
         tma_load_2d(dst, &tm_bu, &bars[s], (int32_t)(cta_col0 * 2), row);
@@ -347,9 +370,9 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
 
   int slot = 0;
   uint32_t parity = 0;
-  float4 carry = load_carry(nchunks - 1);
-  for (long long k = 0; k < nchunks; ++k) {
-    const long long chunk = nchunks - 1 - k;
+  float4 carry = load_carry(k1 - 1);
+  for (long long k = 0; k < nseg; ++k) {
+    const long long chunk = k1 - 1 - k;
     const long long t0 = chunk * kChunk;
     const float4 carry_next = load_carry(chunk - 1);  // prefetch for the next iteration
     const int rows = (int)((p.L - t0) < kChunk ? (p.L - t0) : kChunk);
@@ -418,7 +441,7 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
 
     if constexpr (kTma) {
       __syncthreads();  // every warp is done reading this slot
-      if (threadIdx.x == 0 && k + p.ring < nchunks) {
+      if (threadIdx.x == 0 && k + p.ring < nseg) {
         const int32_t row = (int32_t)((chunk - p.ring) * kChunk);
         unsigned char* dst = ring_base + (size_t)slot * pair_bytes;
         fence_proxy_async();
@@ -431,8 +454,139 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
     carry = carry_next;
   }
   if (valid) {
+    const long long SN = (long long)gridDim.y * p.N;
 #pragma unroll
-    for (int i = 0; i < kNumAcc; ++i) p.partials[(long long)i * p.N + n] = acc[i];
+    for (int i = 0; i < kNumAcc; ++i) p.partials[(long long)i * SN + (long long)blockIdx.y * p.N + n] = acc[i];
+  }
+}
+
+// Adjoint summary of a time segment: runs lam <- M^T (lam + e2 * g_t) right to left
+// over the segment from lam = 0 and writes lam at the segment's left end.  Reads
+// grad_x only (8 B/elem).  Same staging as the other kernels.
+template <int V>
+__global__ void __launch_bounds__(128)
+lti_adjoint_summary_kernel(const __grid_constant__ CUtensorMap tm_gx, BwdParams p, float4* seg_out) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const int warps = blockDim.x >> 5;
+  const int cta_cols = warps * kCols;
+  const long long cta_col0 = (long long)blockIdx.x * cta_cols;
+  const long long n = cta_col0 + threadIdx.x;
+  const bool valid = n < p.N;
+  const long long ch = valid ? (n % p.P) : 0;
+  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step[ch]);
+  const long long nchunks = (p.L + kChunk - 1) / kChunk;
+  const long long k0 = (long long)blockIdx.y * p.seg_chunks;
+  const long long k1 = (k0 + p.seg_chunks) < nchunks ? (k0 + p.seg_chunks) : nchunks;
+  const long long nseg = k1 - k0;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  unsigned char* ring_base = smem_raw + 1024;
+  const uint32_t stage_bytes = (uint32_t)warps * kStageBytes;
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm_gx);
+    for (int s = 0; s < p.ring; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    const int pre = (int)(nseg < p.ring ? nseg : p.ring);
+    for (int s = 0; s < pre; ++s) {
+      mbar_expect_tx(&bars[s], stage_bytes);
+      tma_load_2d(ring_base + (size_t)s * stage_bytes, &tm_gx, &bars[s], (int32_t)(cta_col0 * 2),
+                  (int32_t)((k1 - 1 - s) * kChunk));
+    }
+  }
+  __syncthreads();
+  float2 l0 = make_float2(0.f, 0.f), l1 = make_float2(0.f, 0.f);
+  int slot = 0;
+  uint32_t parity = 0;
+  for (long long k = 0; k < nseg; ++k) {
+    const long long chunk = k1 - 1 - k;
+    if (!mbar_wait(&bars[slot], parity)) return;
+    const float2* sgx = reinterpret_cast<const float2*>(ring_base + (size_t)slot * stage_bytes) + threadIdx.x;
+    // rows past the end of the sequence hold zeros and leave lam = 0 unchanged
+#pragma unroll
+    for (int r = kChunk - 1; r >= 0; --r) {
+      const float2 g1 = __fadd2_rn(l1, sgx[r * cta_cols]);
+      if constexpr (V == kImex1) {
+        const float2 gt = __fadd2_rn(l0, g1);
+        l0 = __fmul2_rn(gt, c.m11);
+        l1 = __ffma2_rn(gt, c.m12, g1);
+      } else {
+        const float2 g0 = l0;
+        l0 = __ffma2_rn(g1, c.m21, __fmul2_rn(g0, c.m11));
+        l1 = __ffma2_rn(g1, c.m22, __fmul2_rn(g0, c.m12));
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && k + p.ring < nseg) {
+      fence_proxy_async();
+      mbar_expect_tx(&bars[slot], stage_bytes);
+      tma_load_2d(ring_base + (size_t)slot * stage_bytes, &tm_gx, &bars[slot], (int32_t)(cta_col0 * 2),
+                  (int32_t)((chunk - p.ring) * kChunk));
+    }
+    if (++slot == p.ring) { slot = 0; parity ^= 1; }
+  }
+  if (valid) seg_out[(long long)blockIdx.y * p.N + n] = make_float4(l0.x, l0.y, l1.x, l1.y);
+}
+
+// Stitches the segment summaries together: with T = M^len (the transition over a
+// whole segment, by repeated squaring in double precision) the state entering
+// segment s+1 is  c_{s+1} = T c_s + e_s  (forward, kAdjoint = false; e_s = state
+// leaving segment s when started from zero), and the adjoint entering segment s
+// from the right is  lam_s = (M^T)^len_{s+1} lam_{s+1} + r_{s+1}  (kAdjoint = true).
+// One thread per series.
+template <int V, bool kAdjoint>
+__global__ void lti_segment_combine_kernel(const float* __restrict__ a, const float* __restrict__ g,
+                                           const float* __restrict__ step, const float4* __restrict__ summary,
+                                           float4* __restrict__ init, long long L, long long N, long long P,
+                                           long long seg_chunks, int S) {
+  const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const long long ch = n % P;
+  const Coef c = make_coef<V>(a[ch], g ? g[ch] : 0.0f, step[ch]);
+  // the map one step applies to the state (imex1: x' = w' + x makes the second row (m11, 1 + m12))
+  double m11 = c.m11.x, m12 = c.m12.x, m21, m22;
+  if constexpr (V == kImex1) { m21 = m11; m22 = 1.0 + m12; } else { m21 = c.m21.x; m22 = c.m22.x; }
+  if (kAdjoint) { const double t = m12; m12 = m21; m21 = t; }
+  auto power = [&](long long e, double (&T)[4]) {
+    double b0 = m11, b1 = m12, b2 = m21, b3 = m22;
+    T[0] = 1.0; T[1] = 0.0; T[2] = 0.0; T[3] = 1.0;
+    while (e > 0) {
+      if (e & 1) {
+        const double t0 = T[0] * b0 + T[1] * b2, t1 = T[0] * b1 + T[1] * b3;
+        const double t2 = T[2] * b0 + T[3] * b2, t3 = T[2] * b1 + T[3] * b3;
+        T[0] = t0; T[1] = t1; T[2] = t2; T[3] = t3;
+      }
+      const double q0 = b0 * b0 + b1 * b2, q1 = b0 * b1 + b1 * b3;
+      const double q2 = b2 * b0 + b3 * b2, q3 = b2 * b1 + b3 * b3;
+      b0 = q0; b1 = q1; b2 = q2; b3 = q3;
+      e >>= 1;
+    }
+  };
+  const long long full = seg_chunks * kChunk;
+  double T[4];
+  power(full, T);
+  double v[4] = {0.0, 0.0, 0.0, 0.0};   // (s0.re, s0.im, s1.re, s1.im)
+  if (!kAdjoint) {
+    init[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s + 1 < S; ++s) {
+      const float4 e = summary[(long long)s * N + n];
+      const double n0r = T[0] * v[0] + T[1] * v[2] + e.x, n0i = T[0] * v[1] + T[1] * v[3] + e.y;
+      const double n1r = T[2] * v[0] + T[3] * v[2] + e.z, n1i = T[2] * v[1] + T[3] * v[3] + e.w;
+      v[0] = n0r; v[1] = n0i; v[2] = n1r; v[3] = n1i;
+      init[(long long)(s + 1) * N + n] = make_float4((float)v[0], (float)v[1], (float)v[2], (float)v[3]);
+    }
+  } else {
+    init[(long long)(S - 1) * N + n] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long last = L - (long long)(S - 1) * full;   // steps in the rightmost segment
+    double Tl[4];
+    power(last, Tl);
+    for (int s = S - 2; s >= 0; --s) {
+      const double* U = (s == S - 2) ? Tl : T;              // transition over segment s+1
+      const float4 e = summary[(long long)(s + 1) * N + n];
+      const double n0r = U[0] * v[0] + U[1] * v[2] + e.x, n0i = U[0] * v[1] + U[1] * v[3] + e.y;
+      const double n1r = U[2] * v[0] + U[3] * v[2] + e.z, n1i = U[2] * v[1] + U[3] * v[3] + e.w;
+      v[0] = n0r; v[1] = n0i; v[2] = n1r; v[3] = n1i;
+      init[(long long)s * N + n] = make_float4((float)v[0], (float)v[1], (float)v[2], (float)v[3]);
+    }
   }
 }
 
@@ -534,6 +688,7 @@ struct Tuning {
   int bwd_ring = 2;
   int bwd_warps = 4;
   int force_plain = 0;
+  int segments = 0;   // 0 = automatic
 };
 static Tuning g_tuning;
 
@@ -543,8 +698,30 @@ static int set_smem(K kernel, size_t bytes) {
                     "cudaFuncSetAttribute(max dynamic smem)");
 }
 
+// Number of time segments.  A sequence is split only when the series alone cannot
+// occupy the GPU (few column tiles) and it is long enough; each segment then costs
+// one extra read of its input for the summary pass.
+static int pick_segments(long long L, long long N, int warps) {
+  if (g_tuning.segments > 0) {
+    const long long nchunks = (L + kChunk - 1) / kChunk;
+    return (int)(g_tuning.segments < nchunks ? g_tuning.segments : nchunks);
+  }
+  const long long tiles = (N + (long long)kCols * warps - 1) / ((long long)kCols * warps);
+  if (tiles >= 96) return 1;
+  const long long nchunks = (L + kChunk - 1) / kChunk;
+  long long S = sm_count() / tiles;
+  if (S > 16) S = 16;
+  if (S > nchunks / 16) S = nchunks / 16;   // at least 512 steps per segment
+  return S < 2 ? 1 : (int)S;
+}
+
+static size_t forward_ws_bytes(int S, long long N) { return S > 1 ? (size_t)2 * S * N * sizeof(float4) : 0; }
+static size_t backward_ws_bytes(int S, long long N) {
+  return (size_t)kNumAcc * S * N * sizeof(float) + (S > 1 ? (size_t)2 * S * N * sizeof(float4) : 0);
+}
+
 template <int V, int kOut>
-static int launch_forward_out(const FwdParams& p, cudaStream_t stream) {
+static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* workspace, size_t ws_bytes) {
   CUtensorMap tm;
   memset(&tm, 0, sizeof(tm));
   const int tw = g_tuning.fwd_warps;
@@ -558,12 +735,34 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream) {
     set_last_error("lti_scan_forward: B*P too large");
     return kErrInvalidArgument;
   }
+  const long long nchunks = (p.L + kChunk - 1) / kChunk;
   FwdParams q = p;
+  q.seg_chunks = nchunks;
+  q.seg_init = nullptr;
+  q.seg_end = nullptr;
   if (tma) {
     q.ring = g_tuning.fwd_ring;
     const size_t smem = 1024 + (size_t)warps * q.ring * kStageBytes;
+    int S = pick_segments(p.L, p.N, warps);
+    if (workspace == nullptr || ws_bytes < forward_ws_bytes(S, p.N)) S = 1;
+    if (S > 1) {
+      // pass 1: per-segment end states from zero; pass 2: stitch; pass 3: the scan proper
+      float4* seg_end = static_cast<float4*>(workspace);
+      float4* seg_init = seg_end + (size_t)S * p.N;
+      q.seg_chunks = (nchunks + S - 1) / S;
+      S = (int)((nchunks + q.seg_chunks - 1) / q.seg_chunks);
+      FwdParams sum = q;
+      sum.x = nullptr; sum.states = nullptr; sum.carries = nullptr; sum.seg_end = seg_end;
+      if (int rc = set_smem(lti_forward_kernel<V, true, 0>, smem)) return rc;
+      lti_forward_kernel<V, true, 0><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm, sum);
+      if (int rc = check_cuda(cudaGetLastError(), "lti_forward_kernel (summary) launch")) return rc;
+      lti_segment_combine_kernel<V, false><<<(unsigned)((p.N + 127) / 128), 128, 0, stream>>>(
+          p.a, p.g, p.step, seg_end, seg_init, p.L, p.N, p.P, q.seg_chunks, S);
+      if (int rc = check_cuda(cudaGetLastError(), "lti_segment_combine_kernel launch")) return rc;
+      q.seg_init = seg_init;
+    }
     if (int rc = set_smem(lti_forward_kernel<V, true, kOut>, smem)) return rc;
-    lti_forward_kernel<V, true, kOut><<<(unsigned)grid, warps * 32, smem, stream>>>(tm, q);
+    lti_forward_kernel<V, true, kOut><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm, q);
   } else {
     q.ring = 0;
     lti_forward_kernel<V, false, kOut><<<(unsigned)grid, warps * 32, 0, stream>>>(tm, q);
@@ -572,15 +771,15 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream) {
 }
 
 template <int V>
-static int launch_forward(const FwdParams& p, cudaStream_t stream) {
-  if (p.x && p.states) return launch_forward_out<V, 3>(p, stream);
-  if (p.states) return launch_forward_out<V, 2>(p, stream);
-  return launch_forward_out<V, 1>(p, stream);
+static int launch_forward(const FwdParams& p, cudaStream_t stream, void* workspace, size_t ws_bytes) {
+  if (p.x && p.states) return launch_forward_out<V, 3>(p, stream, workspace, ws_bytes);
+  if (p.states) return launch_forward_out<V, 2>(p, stream, workspace, ws_bytes);
+  return launch_forward_out<V, 1>(p, stream, workspace, ws_bytes);
 }
 
 template <int V>
 static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, float* grad_step, long long B,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, size_t ws_bytes) {
   CUtensorMap tm_bu, tm_gx;
   memset(&tm_bu, 0, sizeof(tm_bu));
   memset(&tm_gx, 0, sizeof(tm_gx));
@@ -597,12 +796,32 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
     set_last_error("lti_scan_backward: B*P too large");
     return kErrInvalidArgument;
   }
+  const long long nchunks = (p.L + kChunk - 1) / kChunk;
   BwdParams q = p;
+  q.seg_chunks = nchunks;
+  q.lam_init = nullptr;
+  int S = 1;
   if (tma) {
     q.ring = g_tuning.bwd_ring;
+    S = pick_segments(p.L, p.N, warps);
+    if (ws_bytes < backward_ws_bytes(S, p.N)) S = 1;
+    if (S > 1) {
+      q.seg_chunks = (nchunks + S - 1) / S;
+      S = (int)((nchunks + q.seg_chunks - 1) / q.seg_chunks);
+      float4* seg_sum = reinterpret_cast<float4*>(p.partials + (size_t)kNumAcc * S * p.N);
+      float4* seg_init = seg_sum + (size_t)S * p.N;
+      const size_t smem1 = 1024 + (size_t)warps * q.ring * kStageBytes;
+      if (int rc = set_smem(lti_adjoint_summary_kernel<V>, smem1)) return rc;
+      lti_adjoint_summary_kernel<V><<<dim3((unsigned)grid, S), warps * 32, smem1, stream>>>(tm_gx, q, seg_sum);
+      if (int rc = check_cuda(cudaGetLastError(), "lti_adjoint_summary_kernel launch")) return rc;
+      lti_segment_combine_kernel<V, true><<<(unsigned)((p.N + 127) / 128), 128, 0, stream>>>(
+          p.a, p.g, p.step, seg_sum, seg_init, p.L, p.N, p.P, q.seg_chunks, S);
+      if (int rc = check_cuda(cudaGetLastError(), "lti_segment_combine_kernel launch")) return rc;
+      q.lam_init = seg_init;
+    }
     const size_t smem = 1024 + (size_t)warps * q.ring * 2 * kStageBytes;
     if (int rc = set_smem(lti_backward_kernel<V, true>, smem)) return rc;
-    lti_backward_kernel<V, true><<<(unsigned)grid, warps * 32, smem, stream>>>(tm_bu, tm_gx, q);
+    lti_backward_kernel<V, true><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm_bu, tm_gx, q);
   } else {
     q.ring = 0;
     lti_backward_kernel<V, false><<<(unsigned)grid, warps * 32, 0, stream>>>(tm_bu, tm_gx, q);
@@ -610,8 +829,9 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   if (int rc = check_cuda(cudaGetLastError(), "lti_backward_kernel launch")) return rc;
   const int threads = kPgCh * kPgGroups;
   const unsigned blocks = (unsigned)((p.P + kPgCh - 1) / kPgCh);
+  // the segments of a series are summed like extra batch entries
   lti_param_grad_kernel<V><<<blocks, threads, 0, stream>>>(p.a, p.g, p.step, p.partials, grad_a, grad_g, grad_step,
-                                                           B, p.P);
+                                                           B * S, p.P);
   return check_cuda(cudaGetLastError(), "lti_param_grad_kernel launch");
 }
 
@@ -628,13 +848,13 @@ static bool needs_g(int v) { return v <= kEx; }
     default: { constexpr int V = kLinossImex; return CALL; }      \
   }
 
-static int forward_dispatch(int variant, const FwdParams& p, cudaStream_t stream) {
-  OSSM_DISPATCH_VARIANT(variant, launch_forward<V>(p, stream));
+static int forward_dispatch(int variant, const FwdParams& p, cudaStream_t stream, void* ws, size_t ws_bytes) {
+  OSSM_DISPATCH_VARIANT(variant, launch_forward<V>(p, stream, ws, ws_bytes));
 }
 
 static int backward_dispatch(int variant, const BwdParams& p, float* ga, float* gg, float* gs, long long B,
-                             cudaStream_t stream) {
-  OSSM_DISPATCH_VARIANT(variant, launch_backward<V>(p, ga, gg, gs, B, stream));
+                             cudaStream_t stream, size_t ws_bytes) {
+  OSSM_DISPATCH_VARIANT(variant, launch_backward<V>(p, ga, gg, gs, B, stream, ws_bytes));
 }
 
 }  // namespace lti
@@ -654,6 +874,7 @@ int ossm_b200_lti_set_tuning(const char* key, int value) {
   if (!strcmp(key, "bwd_ring") && value >= 1 && value <= 12) { g_tuning.bwd_ring = value; return kOk; }
   if (!strcmp(key, "bwd_warps") && value >= 1 && value <= 4) { g_tuning.bwd_warps = value; return kOk; }
   if (!strcmp(key, "force_plain")) { g_tuning.force_plain = value != 0; return kOk; }
+  if (!strcmp(key, "segments") && value >= 0 && value <= 64) { g_tuning.segments = value; return kOk; }
   set_last_error("lti_set_tuning: unknown key or value out of range: %s=%d", key, value);
   return kErrInvalidArgument;
 }
@@ -666,7 +887,14 @@ size_t ossm_b200_lti_carry_bytes(int64_t L, int64_t B, int64_t P) {
 
 size_t ossm_b200_lti_backward_workspace_bytes(int64_t L, int64_t B, int64_t P) {
   if (L <= 0 || B <= 0 || P <= 0) return 0;
-  return (size_t)kNumAcc * (size_t)B * (size_t)P * sizeof(float);
+  const int S = g_tuning.segments > 0 ? 64 : pick_segments(L, B * P, g_tuning.bwd_warps);
+  return backward_ws_bytes(S, B * P);
+}
+
+size_t ossm_b200_lti_forward_workspace_bytes(int64_t L, int64_t B, int64_t P) {
+  if (L <= 0 || B <= 0 || P <= 0) return 0;
+  const int S = g_tuning.segments > 0 ? 64 : pick_segments(L, B * P, g_tuning.fwd_warps);
+  return forward_ws_bytes(S, B * P);
 }
 
 static int check_common(const char* fn, int variant, const void* a, const void* g, const void* step, int64_t L,
@@ -681,9 +909,9 @@ static int check_common(const char* fn, int variant, const void* a, const void* 
   return kOk;
 }
 
-int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, const float* step, const void* bu,
-                               void* x, void* states, void* carries, int64_t L, int64_t B, int64_t P,
-                               cudaStream_t stream) {
+int ossm_b200_lti_scan_forward_ws(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                  void* x, void* states, void* carries, void* workspace, size_t workspace_bytes,
+                                  int64_t L, int64_t B, int64_t P, cudaStream_t stream) {
   if (int rc = check_common("lti_scan_forward", variant, a, g, step, L, B, P)) return rc;
   if (L == 0 || B == 0 || P == 0) return kOk;
   if (bu == nullptr || (x == nullptr && states == nullptr)) {
@@ -691,8 +919,9 @@ int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, cons
     return kErrInvalidArgument;
   }
   if ((reinterpret_cast<uintptr_t>(bu) & 7u) || (reinterpret_cast<uintptr_t>(x) & 7u) ||
-      (reinterpret_cast<uintptr_t>(states) & 15u) || (reinterpret_cast<uintptr_t>(carries) & 15u)) {
-    set_last_error("lti_scan_forward: misaligned buffer (bu/x need 8 B, states/carries 16 B)");
+      (reinterpret_cast<uintptr_t>(states) & 15u) || (reinterpret_cast<uintptr_t>(carries) & 15u) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
+    set_last_error("lti_scan_forward: misaligned buffer (bu/x need 8 B, states/carries/workspace 16 B)");
     return kErrInvalidArgument;
   }
   FwdParams p;
@@ -702,7 +931,15 @@ int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, cons
   p.states = static_cast<float4*>(states);
   p.carries = static_cast<float4*>(carries);
   p.L = L; p.N = B * P; p.P = P; p.ring = 0;
-  return forward_dispatch(variant, p, stream);
+  p.seg_chunks = 0; p.seg_init = nullptr; p.seg_end = nullptr;
+  return forward_dispatch(variant, p, stream, workspace, workspace_bytes);
+}
+
+int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, const float* step, const void* bu,
+                               void* x, void* states, void* carries, int64_t L, int64_t B, int64_t P,
+                               cudaStream_t stream) {
+  // without scratch the sequence is never split into time segments
+  return ossm_b200_lti_scan_forward_ws(variant, a, g, step, bu, x, states, carries, nullptr, 0, L, B, P, stream);
 }
 
 static int backward_common(const char* fn, int variant, const float* a, const float* g, const float* step,
@@ -731,13 +968,12 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
   }
   if ((reinterpret_cast<uintptr_t>(bu) & 7u) || (reinterpret_cast<uintptr_t>(grad_x) & 7u) ||
       (reinterpret_cast<uintptr_t>(grad_bu) & 7u) || (reinterpret_cast<uintptr_t>(carry_src) & 15u) ||
-      (reinterpret_cast<uintptr_t>(workspace) & 3u)) {
+      (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
     set_last_error("%s: misaligned buffer", fn);
     return kErrInvalidArgument;
   }
-  if (workspace == nullptr || workspace_bytes < ossm_b200_lti_backward_workspace_bytes(L, B, P)) {
-    set_last_error("%s: workspace too small (%zu < %zu bytes)", fn, workspace_bytes,
-                   ossm_b200_lti_backward_workspace_bytes(L, B, P));
+  if (workspace == nullptr || workspace_bytes < backward_ws_bytes(1, B * P)) {
+    set_last_error("%s: workspace too small (%zu < %zu bytes)", fn, workspace_bytes, backward_ws_bytes(1, B * P));
     return kErrWorkspace;
   }
   BwdParams p;
@@ -749,7 +985,9 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
   p.grad_bu = static_cast<float2*>(grad_bu);
   p.partials = static_cast<float*>(workspace);
   p.L = L; p.N = B * P; p.P = P; p.ring = 0;
-  return backward_dispatch(variant, p, grad_a, needs_g(variant) ? grad_g : nullptr, grad_step, B, stream);
+  p.seg_chunks = 0; p.lam_init = nullptr;
+  return backward_dispatch(variant, p, grad_a, needs_g(variant) ? grad_g : nullptr, grad_step, B, stream,
+                           workspace_bytes);
 }
 
 int ossm_b200_lti_scan_backward(int variant, const float* a, const float* g, const float* step, const void* bu,

@@ -82,10 +82,12 @@ def lti_scan_forward(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor,
         carries = torch.empty((rows, B, P, 2), dtype=torch.complex64, device=dev)
     if L == 0 or B == 0 or P == 0:
         return x, states, carries
+    ws_bytes = int(lib.ossm_b200_lti_forward_workspace_bytes(L, B, P))
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
     with torch.cuda.device(dev):
-        rc = lib.ossm_b200_lti_scan_forward(vid, _p(a), _p(g), _p(step), _p(bu), _p(x), _p(states),
-                                            _p(carries) if carries is not None and carries.numel() else None,
-                                            L, B, P, _stream(dev))
+        rc = lib.ossm_b200_lti_scan_forward_ws(vid, _p(a), _p(g), _p(step), _p(bu), _p(x), _p(states),
+                                               _p(carries) if carries is not None and carries.numel() else None,
+                                               _p(workspace), ws_bytes, L, B, P, _stream(dev))
     _lib.check(rc, "lti_scan_forward")
     return x, states, carries
 
