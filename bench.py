@@ -47,9 +47,11 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba"],
+    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba", "sharded_layer"],
                     help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
-                         "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16)")
+                         "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
+                         "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
+                         "L defaults to 32768, a quarter of the config, to bound memory)")
     ap.add_argument("--variant", default="imex1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--length", type=int, default=4096)
@@ -498,10 +500,86 @@ def run_secondary(args):
                      "algorithmic_bytes_per_elem": fb + bb}}))
 
 
+def run_sharded_layer(args):
+    """BASELINE config 4: D-LinOSS layer forward + backward with the oscillators split over
+    the ranks and the partial outputs summed over NVLink (ossm_b200.sharded_layer)."""
+    import torch
+    import torch.distributed as dist
+
+    from ossm_b200 import _lib
+    from ossm_b200.sharded_layer import sharded_dlinoss_layer
+    from ossm_b200.sharding import aggregate_throughput, shard_channels
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    Bz, H, P = 8, 512, 2048
+    L = 32768 if args.length == 4096 else args.length
+    per_rank_gb = Bz * L * (P // world) * 8 * 8 / 2**30 + Bz * L * H * 4 * 6 / 2**30
+    if per_rank_gb > 120:
+        raise SystemExit(f"bench.py: sharded_layer would need ~{per_rank_gb:.0f} GB per GPU; lower --length")
+    gen = torch.Generator().manual_seed(0)
+    a, g, dt = make_params(P, "cpu", 0)
+    bound = 1.0 / H ** 0.5
+    full = dict(a=a, g=g, step=dt,
+                B_re=torch.empty(P, H).uniform_(-bound, bound, generator=gen),
+                B_im=torch.empty(P, H).uniform_(-bound, bound, generator=gen),
+                C_re=torch.empty(H, P).uniform_(-bound, bound, generator=gen),
+                C_im=torch.empty(H, P).uniform_(-bound, bound, generator=gen))
+    dims = dict(a=0, g=0, step=0, B_re=0, B_im=0, C_re=1, C_im=1)
+    loc = {k: shard_channels(v, world, rank, dim=dims[k]).to(dev).requires_grad_(True) for k, v in full.items()}
+    Dv = torch.randn(H, generator=gen).to(dev).requires_grad_(True)
+    u = torch.randn(Bz, L, H, generator=gen).to(dev).requires_grad_(True)
+    dy = torch.randn(Bz, L, H, generator=gen).to(dev)
+
+    def step():
+        for t in list(loc.values()) + [Dv, u]:
+            t.grad = None
+        y = sharded_dlinoss_layer("imex1", loc["a"], loc["g"], loc["step"], loc["B_re"], loc["B_im"], loc["C_re"],
+                                  loc["C_im"], Dv, u, slices=4)
+        y.backward(dy)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    elems_local = Bz * L * loc["a"].numel()
+    total, ms = aggregate_throughput(elems_local, e0.elapsed_time(e1), dev)
+    if _lib.device_status() != 0:
+        raise SystemExit("bench.py: device status non-zero")
+    if rank == 0:
+        ms /= args.steps
+        print(json.dumps({
+            "metric": "dlinoss_layer_sharded_fwd_bwd_gelem_per_s", "value": total / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "data": "synthetic",
+            "config": {"workload": f"D-LinOSS imex1 layer fwd+bwd, B={Bz} L={L} H={H} P={P} split over {world} GPU(s), "
+                                   "partial outputs summed with NCCL (BASELINE config 4, reduced L)",
+                       "projections": "torch.matmul fp32 (library GEMM)"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "sharded_layer":
+        run_sharded_layer(args)
     elif args.workload != "dlinoss":
         run_secondary(args)
     else:
