@@ -40,7 +40,6 @@ namespace sscan {
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kCI = 8;                      // channels per warp
-constexpr int kChannelsPerCta = kWarps * kCI;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -283,6 +282,7 @@ struct Params {
   long long B, D, L, N;
   long long nstates;   // saved states per lane = ceil(L / state_interval)
   int state_interval;  // steps between saved states (= the backward's chunk)
+  int cpw;             // channels per warp (<= kCI); smaller for small problems so the grid fills the GPU
   bool vec_ok;
 };
 
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
   float2* carry = reinterpret_cast<float2*>(Cs + NP * T * 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
-  const long long d0 = (long long)blockIdx.x * kChannelsPerCta + warp * kCI;
+  const long long d0 = (long long)blockIdx.x * (kWarps * p.cpw) + warp * p.cpw;
   const long long nchunks = (p.L + T - 1) / T;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
     __syncthreads();
     const long long t0 = t_base + (long long)lane * kItems;
 #pragma unroll 1
-    for (int ci = 0; ci < kCI; ++ci) {
+    for (int ci = 0; ci < p.cpw; ++ci) {
       const long long d = d0 + ci;
       if (d >= p.D) break;  // warp-uniform
       const long long row = (b * p.D + d) * p.L;
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   float* dDacc = reinterpret_cast<float*>(dAacc + kWarps * kCI * NP);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
-  const long long d0 = (long long)blockIdx.x * kChannelsPerCta + warp * kCI;
+  const long long d0 = (long long)blockIdx.x * (kWarps * p.cpw) + warp * p.cpw;
   const long long nchunks = (p.L + T - 1) / T;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
@@ -434,7 +434,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
     float u[kItems], dt[kItems], go[kItems], zz[kItems];
     auto fetch = [&](int ci, float (&fu)[kItems], float (&fdt)[kItems], float (&fgo)[kItems], float (&fz)[kItems]) {
       const long long d = d0 + ci;
-      const bool ok = ci < kCI && d < p.D;
+      const bool ok = ci < p.cpw && d < p.D;
       const long long row = ok ? (b * p.D + d) * p.L : 0;
       const long long tl = ok ? p.L : 0;
       load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, tl, p.vec_ok, fu);
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
     };
     fetch(0, u, dt, go, zz);
 #pragma unroll 1
-    for (int ci = 0; ci < kCI; ++ci) {
+    for (int ci = 0; ci < p.cpw; ++ci) {
       const long long d = d0 + ci;
       if (d >= p.D) break;                                    // warp-uniform; no CTA barrier inside this loop
       const long long row = (b * p.D + d) * p.L;
@@ -581,16 +581,18 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   __syncthreads();
   for (int i = threadIdx.x; i < kWarps * kCI * N; i += kThreads) {
     const int wc = i / N, n = i - wc * N;
-    const long long d = (long long)blockIdx.x * kChannelsPerCta + wc;
-    if (d < p.D) {
+    const int w = wc / kCI, ci = wc - w * kCI;
+    const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
+    if (ci < p.cpw && d < p.D) {
       const float2 v = dAacc[wc * NP + (n >> 1)];
       p.dA_part[(b * p.D + d) * p.N + n] = (n & 1) ? v.y : v.x;
     }
   }
   if (p.dD_part) {
     for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) {
-      const long long d = (long long)blockIdx.x * kChannelsPerCta + i;
-      if (d < p.D) p.dD_part[b * p.D + d] = dDacc[i];
+      const int w = i / kCI, ci = i - w * kCI;
+      const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
+      if (ci < p.cpw && d < p.D) p.dD_part[b * p.D + d] = dDacc[i];
     }
   }
 }
@@ -634,7 +636,7 @@ static int launch_fwd(const Params& p, cudaStream_t stream) {
   const size_t smem = sizeof(float) * (2 * np2 * T + (size_t)kWarps * kCI * np2);
   if (smem > 200 * 1024) { set_last_error("selective_scan_forward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_forward_kernel<IO, kItems>, smem)) return rc;
-  dim3 grid((unsigned)((p.D + kChannelsPerCta - 1) / kChannelsPerCta), (unsigned)p.B);
+  dim3 grid((unsigned)((p.D + kWarps * p.cpw - 1) / (kWarps * p.cpw)), (unsigned)p.B);
   sscan_forward_kernel<IO, kItems><<<grid, kThreads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "sscan_forward_kernel launch");
 }
@@ -647,7 +649,7 @@ static int launch_bwd(const Params& p, cudaStream_t stream) {
                                        kWarps * kCI);
   if (smem > 220 * 1024) { set_last_error("selective_scan_backward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_backward_kernel<IO, kItems>, smem)) return rc;
-  dim3 grid((unsigned)((p.D + kChannelsPerCta - 1) / kChannelsPerCta), (unsigned)p.B);
+  dim3 grid((unsigned)((p.D + kWarps * p.cpw - 1) / (kWarps * p.cpw)), (unsigned)p.B);
   sscan_backward_kernel<IO, kItems><<<grid, kThreads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "sscan_backward_kernel launch");
 }
@@ -667,6 +669,13 @@ static int dispatch_items(bool backward, const Params& p, cudaStream_t stream) {
     case 2: return launch_fwd<IO, 2>(p, stream);
     default: return launch_fwd<IO, 1>(p, stream);
   }
+}
+
+// Channels per warp: the most that still gives one CTA per SM.
+static int pick_cpw(long long B, long long D) {
+  int cpw = kCI;
+  while (cpw > 1 && B * ((D + kWarps * cpw - 1) / (kWarps * cpw)) < (long long)sm_count()) cpw >>= 1;
+  return cpw;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -721,6 +730,7 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
   p.B = B; p.D = D; p.L = L; p.N = N;
   p.state_interval = 32 * sscan::items_bwd(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
+  p.cpw = sscan::pick_cpw(B, D);
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(out) && (!z || sscan::aligned16(z)) &&
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
@@ -760,6 +770,7 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.B = B; p.D = D; p.L = L; p.N = N;
   p.state_interval = 32 * sscan::items_bwd(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
+  p.cpw = sscan::pick_cpw(B, D);
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(dout) && sscan::aligned16(du) &&
              sscan::aligned16(ddt) && (!z || (sscan::aligned16(z) && sscan::aligned16(dz))) &&
