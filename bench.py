@@ -12,9 +12,9 @@ With N > 1 (launched by torchrun, one rank per GPU) every rank scans its own
 is no data-path collective (weak scaling).
 
 Prints ONE JSON line (rank 0).  ``value`` is scan elements (B*L*P) per second
-with inputs resident in HBM; ``e2e`` is the same metric through the public op
-(``ossm_b200.dlinoss.run_dlinoss`` + autograd) with pinned HOST buffers, the
-host->device and device->host copies inside the timed region.
+with inputs resident in HBM; ``e2e`` is the same metric through the public call
+for host-resident data (``ossm_b200.host_io.scan_from_host``) with pinned HOST
+buffers, the host->device and device->host copies inside the timed region.
 
 ``--impl reference`` times the reference's own compiled CPU kernels
 (``oracle/_ref``, built from the ossm checkout by ``oracle/build_ref.py``) on
@@ -237,7 +237,6 @@ def run_ours(args):
     import torch.distributed as dist
 
     from ossm_b200 import _lib, kernels
-    from ossm_b200.dlinoss import run_dlinoss
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -314,42 +313,14 @@ def run_ours(args):
         h_x = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
         h_gbu = torch.empty((L, B, P), dtype=torch.complex64, pin_memory=True)
         h_pg = torch.empty((3, P), dtype=torch.float32, pin_memory=True)
-        d_bu = torch.empty_like(bu)
-        d_gx = torch.empty_like(gx)
+        from ossm_b200.host_io import scan_from_host
 
-        # Copies run on two side streams so that PCIe traffic in both directions overlaps
-        # with itself and with the kernels: grad_x goes up while the forward runs, x comes
-        # down while grad_x is still going up and the backward runs.
-        main = torch.cuda.current_stream()
-        up, down = torch.cuda.Stream(), torch.cuda.Stream()
-
+        # The public call for host-resident data: batch slices are copied up, scanned and
+        # copied down in a pipeline so that both PCIe directions stay busy.
         def e2e_step():
-            up.wait_stream(main)                       # previous step no longer reads the device inputs
-            with torch.cuda.stream(up):
-                d_bu.copy_(h_bu, non_blocking=True)
-                bu_ready = torch.cuda.Event()
-                bu_ready.record(up)
-                d_gx.copy_(h_gx, non_blocking=True)
-                gx_ready = torch.cuda.Event()
-                gx_ready.record(up)
-            a_, g_, dt_ = (t.detach().requires_grad_(True) for t in (a, g, dt))
-            main.wait_event(bu_ready)
-            bu_ = d_bu.detach().requires_grad_(True)
-            x = run_dlinoss(variant, a_, g_, dt_, bu_)
-            down.wait_stream(main)
-            with torch.cuda.stream(down):
-                h_x.copy_(x.detach(), non_blocking=True)
-            main.wait_event(gx_ready)
-            x.backward(d_gx)
-            down.wait_stream(main)
-            with torch.cuda.stream(down):
-                h_gbu.copy_(bu_.grad, non_blocking=True)
-                h_pg[0].copy_(a_.grad, non_blocking=True)
-                h_pg[1].copy_(g_.grad, non_blocking=True)
-                h_pg[2].copy_(dt_.grad, non_blocking=True)
-            main.wait_stream(down)                     # results are on the host when the step ends
-            x.record_stream(down)
-            bu_.grad.record_stream(down)
+            grads = scan_from_host(variant, a, g, dt, h_bu, h_gx, h_x, h_gbu, slices=8)
+            for row, t in zip(h_pg, grads):
+                row.copy_(t, non_blocking=True)
 
         e2e_step()
         torch.cuda.synchronize()
@@ -366,7 +337,8 @@ def run_ours(args):
         _, e2e_ms = aggregate_throughput(elems, e2e_ms, dev)
         e2e = {"value": total_elems / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": 2 * elems * 8, "d2h_bytes_per_step": 2 * elems * 8 + 3 * P * 4,
-               "ms_per_step": e2e_ms, "api": "ossm_b200.dlinoss.run_dlinoss + autograd, pinned host buffers"}
+               "ms_per_step": e2e_ms,
+               "api": "ossm_b200.host_io.scan_from_host (forward + backward, pinned host buffers, 8 batch slices)"}
 
     if rank != 0:
         if world > 1:
