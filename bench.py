@@ -52,6 +52,8 @@ def parse_args():
                          "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
                          "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
                          "L defaults to 32768, a quarter of the config, to bound memory)")
+    ap.add_argument("--side-batch", type=int, default=0,
+                    help="batch of the side workloads (0 = the BASELINE config's own: 128 / 32 / 8)")
     ap.add_argument("--variant", default="imex1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--length", type=int, default=4096)
@@ -408,7 +410,7 @@ def run_secondary(args):
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(0)
     if args.workload == "linoss":
-        L, B, P = (16384, 128, 128) if args.length == 4096 else (args.length, args.batch, args.ssm)
+        L, B, P = 16384, (args.side_batch or 128), 128
         a = torch.relu(torch.randn(P, generator=gen, device=dev))
         dt = torch.sigmoid(torch.randn(P, generator=gen, device=dev))
         bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev) * 0.5)
@@ -423,7 +425,7 @@ def run_secondary(args):
         def bwd(saved):
             return kernels.lti_scan_backward("linoss_im", a, None, dt, bu, saved[2], gx)
     else:
-        Bz, Dn, L, N = (32, 2048, 8192, 16) if args.length == 4096 else (args.batch, 2048, args.length, 16)
+        Bz, Dn, L, N = (args.side_batch or 32), 2048, 8192, 16
         io = torch.bfloat16
         u = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
         z = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
