@@ -37,6 +37,10 @@ typedef struct CUstream_st* ossm_b200_stream_t; /* == cudaStream_t */
 #define OSSM_B200_VARIANT_EX 3          /* D-LinOSS ex     (_dlinoss_scan.py:85-91)  */
 #define OSSM_B200_VARIANT_LINOSS_IM 4   /* LinOSS IM       (linoss.py:244-251)       */
 #define OSSM_B200_VARIANT_LINOSS_IMEX 5 /* LinOSS IMEX     (linoss.py:253-258)       */
+/* Complex diagonal scan x_t = lambda x_{t-1} + b_t of the LRU / S5 layers (lru_scan.cpp:68-110,
+ * s5_scan.cpp): a = Re lambda, g = Im lambda, step unused (may be NULL); grad_a / grad_g receive
+ * Re / Im of sum_t G_t conj(x_{t-1}) (lru.py:69-78); only component 1 of states/carries is used. */
+#define OSSM_B200_VARIANT_DIAG 6
 
 /* ---- library ------------------------------------------------------------ */
 int ossm_b200_version(void);

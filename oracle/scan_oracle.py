@@ -380,3 +380,33 @@ def max_rel_err(got, want):
     if denom == 0.0:
         return float(np.max(np.abs(got))) if got.size else 0.0
     return float(np.max(np.abs(got.astype(want.dtype) - want)) / denom)
+
+
+# --------------------------------------------------------------------------
+# complex diagonal scan (LRU / S5)
+# --------------------------------------------------------------------------
+def diag_scan(lam, b_seq):
+    """``x_t = lam * x_{t-1} + b_t`` (``src/ossm/csrc/lru_scan.cpp:11-66``, identical in
+    ``s5_scan.cpp``); ``lam`` complex ``[P]``, ``b_seq`` complex ``[L,B,P]``."""
+    out = np.zeros_like(b_seq)
+    x = np.zeros(b_seq.shape[1:], dtype=b_seq.dtype)
+    for t in range(b_seq.shape[0]):
+        x = lam * x + b_seq[t]
+        out[t] = x
+    return out
+
+
+def diag_scan_backward(lam, states, grad_output):
+    """``_LRUScanFn.backward`` (``src/ossm/models/lru.py:53-80``): returns
+    ``(grad_lambda [P], grad_b [L,B,P])``."""
+    L = grad_output.shape[0]
+    gl = np.zeros_like(lam)
+    gb = np.zeros_like(grad_output)
+    nxt = np.zeros(grad_output.shape[1:], dtype=grad_output.dtype)
+    for t in range(L - 1, -1, -1):
+        G = grad_output[t] + nxt
+        gb[t] = G
+        prev = states[t - 1] if t > 0 else np.zeros_like(nxt)
+        gl += (G * np.conj(prev)).sum(axis=0)
+        nxt = G * np.conj(lam)
+    return gl, gb

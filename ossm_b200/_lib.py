@@ -57,9 +57,16 @@ def load():
     if _lib is not None:
         return _lib
     if not os.path.exists(LIB_PATH):
-        raise RuntimeError(
-            f"ossm_b200: {LIB_PATH} is missing -- build it with `python -m ossm_b200.build` "
-            "(there is no CPU or PyTorch fallback)")
+        # a source checkout without the built library: compile it once (needs nvcc); anything
+        # else is an error -- there is no CPU or PyTorch fallback to take instead
+        try:
+            from . import build as _build
+
+            _build.build()
+        except Exception as exc:
+            raise RuntimeError(
+                f"ossm_b200: {LIB_PATH} is missing and could not be built ({exc}); build it with "
+                "`python -m ossm_b200.build` (there is no CPU or PyTorch fallback)") from exc
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)

@@ -5,7 +5,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "../../include/ossm_b200.h"
 
@@ -87,6 +89,21 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> granted;
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& have = granted[std::make_pair(kernel, dev)];
+  if (bytes <= have) return kOk;
+  if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
+                          "cudaFuncSetAttribute(max dynamic smem)"))
+    return rc;
+  have = bytes;
+  return kOk;
 }
 
 }  // namespace ossm_b200

@@ -45,6 +45,9 @@ bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, u
                             bool swizzle128);
 
 int sm_count();
+// Raises a kernel's dynamic shared-memory limit to `bytes`; remembered per (kernel, device) so the
+// attribute call is made only when a launch needs more than any earlier one.
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 // ---- device helpers --------------------------------------------------------
 #ifdef __CUDACC__

@@ -49,6 +49,7 @@ enum Variant : int {
   kEx = OSSM_B200_VARIANT_EX,
   kLinossIm = OSSM_B200_VARIANT_LINOSS_IM,
   kLinossImex = OSSM_B200_VARIANT_LINOSS_IMEX,
+  kDiag = OSSM_B200_VARIANT_DIAG,   // x_t = lambda * x_{t-1} + b_t, complex lambda = (a, g) per channel
 };
 
 // Coefficients as (v, v) pairs: the real and imaginary parts of a state evolve
@@ -87,8 +88,10 @@ __device__ __forceinline__ Coef make_coef(float al, float ga, float si) {
     const float schur = 1.0f / (1.0f + s2a);
     m11 = 1.0f - s2a * schur; m12 = -si * al * schur; m21 = si * schur; m22 = schur;
     f1 = m11 * si; f2 = m21 * si;
-  } else {  // kLinossImex
+  } else if constexpr (V == kLinossImex) {
     m11 = 1.0f; m12 = -si * al; m21 = si; m22 = 1.0f - si * si * al; f1 = si; f2 = si * si;
+  } else {  // kDiag: (m11, m12) = (Re lambda, Im lambda), the other entries are unused
+    m11 = al; m12 = ga; m21 = 0.0f; m22 = 0.0f; f1 = 1.0f; f2 = 0.0f;
   }
   Coef c;
   c.m11 = bcast(m11); c.m12 = bcast(m12); c.m21 = bcast(m21); c.m22 = bcast(m22);
@@ -101,6 +104,12 @@ __device__ __forceinline__ Coef make_coef(float al, float ga, float si) {
 // has determinant exactly `inv`; the other variants use the plain 2x2 form.
 template <int V>
 __device__ __forceinline__ void fwd_step(const Coef& c, float2& s0, float2& s1, float2 b) {
+  if constexpr (V == kDiag) {
+    // complex multiply-add on the (re, im) pair: x' = lambda * x + b  (lru_scan.cpp:11-66, s5_scan.cpp)
+    const float2 rot = make_float2(-s1.y, s1.x);
+    s1 = __ffma2_rn(s1, c.m11, __ffma2_rn(rot, c.m12, b));
+    return;
+  }
   const float2 n0 = __ffma2_rn(s1, c.m12, __ffma2_rn(s0, c.m11, __fmul2_rn(b, c.f1)));
   if constexpr (V == kImex1) {
     s1 = __fadd2_rn(n0, s1);
@@ -139,7 +148,7 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
   const bool valid = n < p.N;
   if (!kTma && cta_col0 + (long long)warp * kCols >= p.N) return;
   const long long ch = valid ? (n % p.P) : 0;
-  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step[ch]);
+  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step ? p.step[ch] : 0.0f);
 
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
   const long long k0 = (long long)blockIdx.y * p.seg_chunks;            // this CTA's time segment
@@ -283,6 +292,14 @@ template <int V>
 __device__ __forceinline__ float2 bwd_step(const Coef& c, float2& l0, float2& l1, float2 gx, float2 p0, float2 p1,
                                            float2 b, float2 (&loc)[kNumAcc]) {
   const float2 g1 = __fadd2_rn(l1, gx);
+  if constexpr (V == kDiag) {
+    // G = g_t + lam ; dlambda += G * conj(x_{t-1}) ; lam <- G * conj(lambda) ; grad_b = G   (lru.py:69-78)
+    const float2 rot = make_float2(g1.y, -g1.x);
+    loc[0] = __ffma2_rn(g1, p1, loc[0]);     // Re: Gr*pr + Gi*pi
+    loc[1] = __ffma2_rn(rot, p1, loc[1]);    // Im: Gi*pr - Gr*pi
+    l1 = __ffma2_rn(rot, c.m12, __fmul2_rn(g1, c.m11));
+    return g1;
+  }
   if constexpr (V == kImex1) {
     const float2 gt = __fadd2_rn(l0, g1);
     loc[0] = __ffma2_rn(gt, p0, loc[0]);
@@ -322,7 +339,7 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
   const bool valid = n < p.N;
   if (!kTma && cta_col0 + (long long)warp * kCols >= p.N) return;
   const long long ch = valid ? (n % p.P) : 0;
-  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step[ch]);
+  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step ? p.step[ch] : 0.0f);
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
 
   float acc[kNumAcc], comp[kNumAcc];
@@ -473,7 +490,7 @@ lti_adjoint_summary_kernel(const __grid_constant__ CUtensorMap tm_gx, BwdParams 
   const long long n = cta_col0 + threadIdx.x;
   const bool valid = n < p.N;
   const long long ch = valid ? (n % p.P) : 0;
-  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step[ch]);
+  const Coef c = make_coef<V>(p.a[ch], p.g ? p.g[ch] : 0.0f, p.step ? p.step[ch] : 0.0f);
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
   const long long k0 = (long long)blockIdx.y * p.seg_chunks;
   const long long k1 = (k0 + p.seg_chunks) < nchunks ? (k0 + p.seg_chunks) : nchunks;
@@ -541,7 +558,7 @@ __global__ void lti_segment_combine_kernel(const float* __restrict__ a, const fl
   const long long n = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   const long long ch = n % P;
-  const Coef c = make_coef<V>(a[ch], g ? g[ch] : 0.0f, step[ch]);
+  const Coef c = make_coef<V>(a[ch], g ? g[ch] : 0.0f, step ? step[ch] : 0.0f);
   // the map one step applies to the state (imex1: x' = w' + x makes the second row (m11, 1 + m12))
   double m11 = c.m11.x, m12 = c.m12.x, m21, m22;
   if constexpr (V == kImex1) { m21 = m11; m22 = 1.0 + m12; } else { m21 = c.m21.x; m22 = c.m22.x; }
@@ -611,7 +628,7 @@ lti_param_grad_kernel(const float* __restrict__ a, const float* __restrict__ g, 
   const int gy = threadIdx.x / kPgCh;
   const long long pch = (long long)blockIdx.x * kPgCh + cx;
   const long long N = B * P;
-  constexpr int kUsed = (V == kImex1) ? 3 : kNumAcc;  // imex1 accumulates three sums only
+  constexpr int kUsed = (V == kImex1) ? 3 : (V == kDiag ? 2 : kNumAcc);  // sums actually accumulated
   double s[kNumAcc];
 #pragma unroll
   for (int i = 0; i < kNumAcc; ++i) s[i] = 0.0;
@@ -632,9 +649,12 @@ lti_param_grad_kernel(const float* __restrict__ a, const float* __restrict__ g, 
     for (int k = 1; k < kPgGroups; ++k) t += red[i][k][cx];
     s[i] = t;
   }
-  const double al = a[pch], ga = g ? g[pch] : 0.0, si = step[pch];
+  const double al = a[pch], ga = g ? g[pch] : 0.0, si = step ? step[pch] : 0.0;
   double da = 0.0, dg = 0.0, ds = 0.0;
-  if constexpr (V == kImex1) {
+  if constexpr (V == kDiag) {
+    da = s[0];   // Re sum G conj(x_{t-1})
+    dg = s[1];   // Im
+  } else if constexpr (V == kImex1) {
     // s = { <gt,p0>, <gt,p1>, <gt,bu> }
     const double inv = 1.0 / (1.0 + si * ga);
     const double s2i = si * si * inv;
@@ -676,7 +696,7 @@ lti_param_grad_kernel(const float* __restrict__ a, const float* __restrict__ g, 
   }
   grad_a[pch] = (float)da;
   if (grad_g) grad_g[pch] = (float)dg;
-  grad_step[pch] = (float)ds;
+  if (grad_step) grad_step[pch] = (float)ds;
 }
 
 // ---------------------------------------------------------------------------
@@ -694,13 +714,15 @@ static Tuning g_tuning;
 
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
-  return check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
-                    "cudaFuncSetAttribute(max dynamic smem)");
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 // Number of time segments.  A sequence is split only when the series alone cannot
 // occupy the GPU (few column tiles) and it is long enough; each segment then costs
 // one extra read of its input for the summary pass.
+template <int V>
+static int pick_segments_for(long long L, long long N, int warps);
+
 static int pick_segments(long long L, long long N, int warps) {
   if (g_tuning.segments > 0) {
     const long long nchunks = (L + kChunk - 1) / kChunk;
@@ -713,6 +735,13 @@ static int pick_segments(long long L, long long N, int warps) {
   if (S > 16) S = 16;
   if (S > nchunks / 16) S = nchunks / 16;   // at least 512 steps per segment
   return S < 2 ? 1 : (int)S;
+}
+
+// The stitching kernel assumes a real transition shared by the real and imaginary parts;
+// the complex diagonal scan is therefore never split.
+template <int V>
+static int pick_segments_for(long long L, long long N, int warps) {
+  return V == kDiag ? 1 : pick_segments(L, N, warps);
 }
 
 static size_t forward_ws_bytes(int S, long long N) { return S > 1 ? (size_t)2 * S * N * sizeof(float4) : 0; }
@@ -743,7 +772,7 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
   if (tma) {
     q.ring = g_tuning.fwd_ring;
     const size_t smem = 1024 + (size_t)warps * q.ring * kStageBytes;
-    int S = pick_segments(p.L, p.N, warps);
+    int S = pick_segments_for<V>(p.L, p.N, warps);
     if (workspace == nullptr || ws_bytes < forward_ws_bytes(S, p.N)) S = 1;
     if (S > 1) {
       // pass 1: per-segment end states from zero; pass 2: stitch; pass 3: the scan proper
@@ -803,7 +832,7 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   int S = 1;
   if (tma) {
     q.ring = g_tuning.bwd_ring;
-    S = pick_segments(p.L, p.N, warps);
+    S = pick_segments_for<V>(p.L, p.N, warps);
     if (ws_bytes < backward_ws_bytes(S, p.N)) S = 1;
     if (S > 1) {
       q.seg_chunks = (nchunks + S - 1) / S;
@@ -835,8 +864,9 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   return check_cuda(cudaGetLastError(), "lti_param_grad_kernel launch");
 }
 
-static bool variant_ok(int v) { return v >= kImex1 && v <= kLinossImex; }
-static bool needs_g(int v) { return v <= kEx; }
+static bool variant_ok(int v) { return v >= kImex1 && v <= kDiag; }
+static bool needs_g(int v) { return v <= kEx || v == kDiag; }
+static bool needs_step(int v) { return v != kDiag; }
 
 #define OSSM_DISPATCH_VARIANT(v, CALL)                  \
   switch (v) {                                          \
@@ -845,6 +875,7 @@ static bool needs_g(int v) { return v <= kEx; }
     case kIm: { constexpr int V = kIm; return CALL; }             \
     case kEx: { constexpr int V = kEx; return CALL; }             \
     case kLinossIm: { constexpr int V = kLinossIm; return CALL; } \
+    case kDiag: { constexpr int V = kDiag; return CALL; }         \
     default: { constexpr int V = kLinossImex; return CALL; }      \
   }
 
@@ -901,7 +932,7 @@ static int check_common(const char* fn, int variant, const void* a, const void* 
                         int64_t B, int64_t P) {
   if (!variant_ok(variant)) { set_last_error("%s: unknown variant %d", fn, variant); return kErrInvalidArgument; }
   if (L < 0 || B < 0 || P < 0) { set_last_error("%s: negative extent", fn); return kErrInvalidArgument; }
-  if (a == nullptr || step == nullptr || (needs_g(variant) && g == nullptr)) {
+  if (a == nullptr || (needs_step(variant) && step == nullptr) || (needs_g(variant) && g == nullptr)) {
     set_last_error("%s: null coefficient pointer", fn);
     return kErrInvalidArgument;
   }
@@ -925,7 +956,7 @@ int ossm_b200_lti_scan_forward_ws(int variant, const float* a, const float* g, c
     return kErrInvalidArgument;
   }
   FwdParams p;
-  p.a = a; p.g = needs_g(variant) ? g : nullptr; p.step = step;
+  p.a = a; p.g = needs_g(variant) ? g : nullptr; p.step = needs_step(variant) ? step : nullptr;
   p.bu = static_cast<const float2*>(bu);
   p.x = static_cast<float2*>(x);
   p.states = static_cast<float4*>(states);
@@ -947,7 +978,7 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
                            void* grad_bu, float* grad_a, float* grad_g, float* grad_step, void* workspace,
                            size_t workspace_bytes, int64_t L, int64_t B, int64_t P, cudaStream_t stream) {
   if (int rc = check_common(fn, variant, a, g, step, L, B, P)) return rc;
-  if (grad_a == nullptr || grad_step == nullptr || (needs_g(variant) && grad_g == nullptr)) {
+  if (grad_a == nullptr || (needs_step(variant) && grad_step == nullptr) || (needs_g(variant) && grad_g == nullptr)) {
     set_last_error("%s: null coefficient-gradient pointer", fn);
     return kErrInvalidArgument;
   }
@@ -955,6 +986,7 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
   if (L == 0 || B == 0) {
     if (int rc = check_cuda(cudaMemsetAsync(grad_a, 0, P * sizeof(float), stream), fn)) return rc;
     if (grad_g) if (int rc = check_cuda(cudaMemsetAsync(grad_g, 0, P * sizeof(float), stream), fn)) return rc;
+    if (grad_step == nullptr) return kOk;
     return check_cuda(cudaMemsetAsync(grad_step, 0, P * sizeof(float), stream), fn);
   }
   if (bu == nullptr || grad_x == nullptr || grad_bu == nullptr) {
@@ -977,7 +1009,7 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
     return kErrWorkspace;
   }
   BwdParams p;
-  p.a = a; p.g = needs_g(variant) ? g : nullptr; p.step = step;
+  p.a = a; p.g = needs_g(variant) ? g : nullptr; p.step = needs_step(variant) ? step : nullptr;
   p.bu = static_cast<const float2*>(bu);
   p.grad_x = static_cast<const float2*>(grad_x);
   p.carry_src = static_cast<const float4*>(carry_src);
@@ -986,7 +1018,8 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
   p.partials = static_cast<float*>(workspace);
   p.L = L; p.N = B * P; p.P = P; p.ring = 0;
   p.seg_chunks = 0; p.lam_init = nullptr;
-  return backward_dispatch(variant, p, grad_a, needs_g(variant) ? grad_g : nullptr, grad_step, B, stream,
+  return backward_dispatch(variant, p, grad_a, needs_g(variant) ? grad_g : nullptr,
+                           needs_step(variant) ? grad_step : nullptr, B, stream,
                            workspace_bytes);
 }
 

@@ -653,8 +653,7 @@ static int items_fwd(long long N) {
 
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
-  return check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
-                    "cudaFuncSetAttribute(max dynamic smem)");
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 template <typename IO, int kItems>

@@ -29,10 +29,10 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
     except ImportError:
         return
     setattr(ossm, "_kernels", kernels)
-    from . import dlinoss, linoss, selective_scan
+    from . import diag, dlinoss, linoss, selective_scan
 
     mods = {}
-    for name in ("_dlinoss_scan", "dlinoss", "_linoss_scan", "linoss", "_selective_scan", "mambarec"):
+    for name in ("_dlinoss_scan", "dlinoss", "_linoss_scan", "linoss", "_selective_scan", "mambarec", "lru", "s5"):
         try:
             mods[name] = importlib.import_module(f"ossm.models.{name}")
         except ImportError:
@@ -45,6 +45,11 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
         mods["linoss"].try_run_scan = linoss.try_run_scan
     if "_linoss_scan" in mods:
         mods["_linoss_scan"].try_run_scan = linoss.try_run_scan
+    # LRU / S5: the layers call ``_LRUScanFn.apply`` / ``_S5ScanFn.apply`` (lru.py:176, s5.py:294)
+    if "lru" in mods:
+        mods["lru"]._LRUScanFn = diag.DiagScanFn
+    if "s5" in mods:
+        mods["s5"]._S5ScanFn = diag.DiagScanFn
     if "_selective_scan" in mods:
         mods["_selective_scan"].try_selective_scan = selective_scan.try_selective_scan
     if "mambarec" in mods:

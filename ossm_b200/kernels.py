@@ -20,7 +20,7 @@ from torch import Tensor
 from . import _lib
 
 VARIANT_IDS = {
-    "imex1": 0, "imex2": 1, "im": 2, "ex": 3, "linoss_im": 4, "linoss_imex": 5,
+    "imex1": 0, "imex2": 1, "im": 2, "ex": 3, "linoss_im": 4, "linoss_imex": 5, "diag": 6,
 }
 
 
@@ -42,9 +42,9 @@ def lti_chunk() -> int:
     return int(_lib.load().ossm_b200_lti_chunk())
 
 
-def _check_lti_inputs(a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor) -> Tuple[int, int, int]:
+def _check_lti_inputs(a: Tensor, g: Optional[Tensor], step: Optional[Tensor], bu: Tensor) -> Tuple[int, int, int]:
     # same checks and messages as dlinoss_imex1.cpp:321-341
-    coeffs = [a, step] + ([g] if g is not None else [])
+    coeffs = [t for t in (a, step, g) if t is not None]
     if any(c.dim() != 1 for c in coeffs):
         raise RuntimeError("Coefficient diagonals must be 1-D tensors")
     if bu.dim() != 3:
@@ -101,11 +101,12 @@ def _lti_backward(fn_name: str, variant: str, a: Tensor, g: Optional[Tensor], st
     dev = bu.device
     grad_a = torch.empty_like(a)
     grad_g = torch.empty_like(g) if g is not None else None
-    grad_step = torch.empty_like(step)
+    grad_step = torch.empty_like(step) if step is not None else None
     grad_bu = torch.empty_like(bu)
     if L == 0 or B == 0 or P == 0:
         grad_a.zero_()
-        grad_step.zero_()
+        if grad_step is not None:
+            grad_step.zero_()
         if grad_g is not None:
             grad_g.zero_()
         return grad_a, grad_g, grad_step, grad_bu
@@ -379,6 +380,52 @@ def selective_scan_backward(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: 
     return selective_scan_cuda_backward(grad_output, inputs, dt, A, B, C, gate, states, inputs.new_empty(0), 0)
 
 
+# ---- complex diagonal scan of the LRU / S5 layers ------------------------------
+def diag_scan_forward(lambda_real: Tensor, lambda_imag: Tensor, b_seq: Tensor, want_carries: bool = True):
+    """``x_t = lambda * x_{t-1} + b_t`` with ``b_seq`` complex64 ``[L,B,P]``; returns ``(x, carries)``."""
+    x, _, carries = lti_scan_forward("diag", lambda_real, lambda_imag, None, b_seq, want_carries=want_carries)
+    return x, carries
+
+
+def diag_scan_backward(lambda_real: Tensor, lambda_imag: Tensor, b_seq: Tensor, carries: Optional[Tensor],
+                       grad_x: Tensor):
+    """Returns ``(grad_lambda complex64 [P], grad_b complex64 [L,B,P])`` as ``_LRUScanFn.backward``
+    computes them in a Python loop (lru.py:53-80)."""
+    gre, gim, _, gb = lti_scan_backward("diag", lambda_real, lambda_imag, None, b_seq, carries, grad_x)
+    return torch.complex(gre, gim), gb
+
+
+def _diag_compat(name: str):
+    def scan(lambda_real: Tensor, lambda_imag: Tensor, b_seq: Tensor) -> Tensor:
+        # same checks as lru_scan.cpp:75-88; b_seq is the real view [L, B, P, 2]
+        if lambda_real.dim() != 1:
+            raise RuntimeError("lambda_real must be 1-D")
+        if lambda_imag.dim() != 1:
+            raise RuntimeError("lambda_imag must be 1-D")
+        if b_seq.dim() != 4 or b_seq.size(-1) != 2:
+            raise RuntimeError("b_seq must have shape (length, batch, state, 2)")
+        if lambda_real.size(0) != b_seq.size(2):
+            raise RuntimeError("lambda_real must match state dimension")
+        if lambda_imag.size(0) != b_seq.size(2):
+            raise RuntimeError("lambda_imag must match state dimension")
+        _require_cuda("b_seq", b_seq)
+        if b_seq.dtype != torch.float32:
+            raise RuntimeError(f"ossm_b200: {name} runs in float32 only")
+        if b_seq.numel() == 0:
+            return torch.empty_like(b_seq)
+        x, _ = diag_scan_forward(lambda_real.contiguous(), lambda_imag.contiguous(),
+                                 torch.view_as_complex(b_seq.contiguous()), want_carries=False)
+        return torch.view_as_real(x)
+
+    scan.__name__ = name
+    scan.__doc__ = f"``ossm._kernels.{name}(lambda_real, lambda_imag, b_seq)`` (bindings.cpp:177-179)."
+    return scan
+
+
+lru_scan = _diag_compat("lru_scan")
+s5_scan = _diag_compat("s5_scan")
+
+
 # ---- names ossm calls unconditionally but that are outside this library ------
 def _out_of_scope(name: str):
     def stub(*_args, **_kwargs):
@@ -390,6 +437,4 @@ def _out_of_scope(name: str):
     return stub
 
 
-lru_scan = _out_of_scope("lru_scan")
-s5_scan = _out_of_scope("s5_scan")
 linear_rnn_scan = _out_of_scope("linear_rnn_scan")

@@ -13,7 +13,7 @@ Sources of the vectors:
   ``tests/test_dlinoss_parity.py:73-138``), re-encoded as arrays.
 * ``linoss_im_snapshot.npz``       -- the inline LinOSS-IM snapshot of
   ``tests/test_linoss_parity.py:74-204``.
-* ``dlinoss_generated.npz``, ``linoss_generated.npz``,
+* ``dlinoss_generated.npz``, ``linoss_generated.npz``, ``diag_generated.npz``,
   ``selective_scan_generated.npz`` -- outputs of the reference itself run here
   on seeded inputs: its pure-PyTorch recurrences (float64 and float32, grads by
   autograd) and its compiled CPU kernels (float32).
@@ -219,6 +219,31 @@ def main():
         o3 = kernels.selective_scan(u, dt, A, Bm, Cm, None)
         out[pre + "cpp_out_nogate"] = _np(o3)
     np.savez_compressed(os.path.join(HERE, "selective_scan_generated.npz"), **out)
+    # ---- F. complex diagonal scan (LRU / S5) ------------------------------
+    from ossm.models.lru import _LRUScanFn
+    from ossm.models.s5 import _S5ScanFn
+
+    out = {}
+    gen = torch.Generator().manual_seed(2024)
+    for tag, (L, B, P) in (("d1", (9, 2, 5)), ("d2", (70, 3, 33))):
+        mag = torch.rand(P, generator=gen) * 0.5 + 0.45
+        ph = torch.rand(P, generator=gen) * 6.28
+        lam = torch.polar(mag, ph).to(torch.complex64)
+        b = torch.complex(torch.randn(L, B, P, generator=gen), torch.randn(L, B, P, generator=gen)).to(torch.complex64)
+        go = torch.complex(torch.randn(L, B, P, generator=gen), torch.randn(L, B, P, generator=gen)).to(torch.complex64)
+        pre = f"{tag}/"
+        out[pre + "lambda"], out[pre + "b_seq"], out[pre + "grad_out"] = _np(lam), _np(b), _np(go)
+        for name, fn in (("lru", _LRUScanFn), ("s5", _S5ScanFn)):
+            lm = lam.clone().requires_grad_(True)
+            bb = b.clone().requires_grad_(True)
+            st = fn.apply(lm, bb)
+            ((st.real * go.real).sum() + (st.imag * go.imag).sum()).backward()
+            out[pre + name + "_states"] = _np(st)
+            out[pre + name + "_grad_lambda"], out[pre + name + "_grad_b"] = _np(lm.grad), _np(bb.grad)
+        raw = kernels.lru_scan(lam.real.contiguous(), lam.imag.contiguous(), torch.view_as_real(b).contiguous())
+        out[pre + "cpp_states"] = _np(torch.view_as_complex(raw.contiguous()))
+    np.savez_compressed(os.path.join(HERE, "diag_generated.npz"), **out)
+
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

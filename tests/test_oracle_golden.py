@@ -163,3 +163,21 @@ def test_selective_scan_generated(tag):
             assert so.max_rel_err(want, got) < 1e-4, (src, name)
     np.testing.assert_allclose(SGEN[p + "cpp_out_nogate"], so.selective_scan(u, dt, A, Bm, Cm, None),
                                rtol=1e-4, atol=5e-5)
+
+
+@pytest.mark.parametrize("tag", ["d1", "d2"])
+def test_diag_scan_generated(tag):
+    """Complex diagonal scan of the LRU / S5 layers against the reference's two autograd
+    functions (Python-loop backward) and its compiled forward kernel."""
+    G = _load("diag_generated.npz")
+    p = f"{tag}/"
+    lam = G[p + "lambda"].astype(np.complex128)
+    b = G[p + "b_seq"].astype(np.complex128)
+    go = G[p + "grad_out"].astype(np.complex128)
+    st = so.diag_scan(lam, b)
+    gl, gb = so.diag_scan_backward(lam, st, go)
+    for name in ("lru", "s5"):
+        assert so.max_rel_err(G[p + name + "_states"], st) < 5e-6
+        assert so.max_rel_err(G[p + name + "_grad_lambda"], gl) < 5e-5
+        assert so.max_rel_err(G[p + name + "_grad_b"], gb) < 5e-5
+    assert so.max_rel_err(G[p + "cpp_states"], st) < 5e-6
