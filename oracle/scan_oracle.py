@@ -410,3 +410,127 @@ def diag_scan_backward(lam, states, grad_output):
         gl += (G * np.conj(prev)).sum(axis=0)
         nxt = G * np.conj(lam)
     return gl, gb
+
+
+# --------------------------------------------------------------------------
+# selective D-LinOSS: per-step, per-series coefficients
+# --------------------------------------------------------------------------
+SDLINOSS_VARIANTS = ("imex1", "imex2", "im", "ex")
+
+
+def sdlinoss_param_view(param, L, B, M):
+    """Broadcast view ``[L|1, B|1, M]`` of a parameter given as ``(M,)``, ``(L,M)``, ``(B,M)``
+    or ``(L|1,B|1,M)`` -- the rule of ``_normalize_param``
+    (``src/ossm/models/_sdlinoss_scan.py:105-141``): a 2-D parameter whose first extent equals
+    the length is time-varying, else per-batch."""
+    p = np.asarray(param)
+    if p.ndim == 1 and p.shape[0] == M:
+        return p.reshape(1, 1, M)
+    if p.ndim == 2 and p.shape[1] == M:
+        if p.shape[0] == L:
+            return p.reshape(L, 1, M)
+        if p.shape[0] == B:
+            return p.reshape(1, B, M)
+    if p.ndim == 3 and p.shape[2] == M and p.shape[0] in (1, L) and p.shape[1] in (1, B):
+        return p
+    raise ValueError(f"parameter must be shaped (M,), (L,M), (B,M) or (L,B,M); got {p.shape}")
+
+
+def _sdlinoss_step_terms(variant, a, g, step_raw):
+    """dt, dt^2, alpha, S_raw, 1/S, clamp mask and the partials of S_raw for one time step
+    (``src/ossm/csrc/sdlinoss_imex1.cpp:60-71`` and the same lines of the three siblings)."""
+    real = a.dtype.type
+    dt = np.minimum(np.maximum(step_raw, real(1e-6)), real(1.0))
+    dt2 = dt * dt
+    one = np.ones_like(dt)
+    zero = np.zeros_like(dt)
+    if variant == "imex1":
+        alpha, s_raw, ds_ddt, ds_dg, ds_da = one, 1 + dt * g, g + zero, dt, zero
+    elif variant == "imex2":
+        alpha, s_raw, ds_ddt, ds_dg, ds_da = 1 - dt * g, 1 + dt2 * a, 2 * dt * a, zero, dt2
+    elif variant == "im":
+        alpha, s_raw, ds_ddt, ds_dg, ds_da = one, 1 + dt * g + dt2 * a, g + 2 * dt * a, dt, dt2
+    elif variant == "ex":
+        alpha, s_raw, ds_ddt, ds_dg, ds_da = 1 - dt * g, one, zero, zero, zero
+    else:
+        raise ValueError(variant)
+    if variant == "ex":
+        inv_s, mask = one, zero
+    else:
+        inv_s = 1 / np.maximum(s_raw, real(1e-6))
+        mask = (s_raw > real(1e-6)).astype(a.dtype)
+    return dt, dt2, alpha, inv_s, mask, ds_ddt, ds_dg, ds_da
+
+
+def sdlinoss_scan(variant, A, G, step, bu):
+    """States ``[L,B,M,2]`` (``[...,0]`` = w, ``[...,1]`` = x) of
+    ``w' = (alpha w + dt^2 (-a x + bu)) / S,  x' = x + w'`` with per-step ``a, g, dt``
+    (``sdlinoss_imex1.cpp:33-97``, ``sdlinoss_imex2.cpp:33-100``, ``sdlinoss_im.cpp:33-98``,
+    ``sdlinoss_ex.cpp:25-80``)."""
+    L, B, M = bu.shape
+    real = bu.real.dtype
+    Av, Gv, Sv = (sdlinoss_param_view(np.asarray(p, dtype=real), L, B, M) for p in (A, G, step))
+    out = np.zeros((L, B, M, 2), dtype=bu.dtype)
+    w = np.zeros((B, M), dtype=bu.dtype)
+    x = np.zeros((B, M), dtype=bu.dtype)
+    for t in range(L):
+        a, g, s = (np.broadcast_to(v[t if v.shape[0] > 1 else 0], (B, M)) for v in (Av, Gv, Sv))
+        dt, dt2, alpha, inv_s, _m, _1, _2, _3 = _sdlinoss_step_terms(variant, a, g, s)
+        comb = -a * x + bu[t]
+        w = (alpha * w + dt2 * comb) * inv_s
+        x = x + w
+        out[t, :, :, 0] = w
+        out[t, :, :, 1] = x
+    return out
+
+
+def sdlinoss_scan_backward(variant, A, G, step, bu, states, grad_out):
+    """``(grad_A, grad_G, grad_step, grad_bu)`` of ``sum(Re(conj(grad_out) * x))``, the
+    parameter gradients in the shapes the parameters were given in (broadcast axes summed;
+    ``sdlinoss_imex1.cpp:99-243`` and siblings, reduction as ``reduce_broadcast_grad``)."""
+    L, B, M = bu.shape
+    real = bu.real.dtype
+    shapes = [np.asarray(p).shape for p in (A, G, step)]
+    Av, Gv, Sv = (sdlinoss_param_view(np.asarray(p, dtype=real), L, B, M) for p in (A, G, step))
+    gA = np.zeros((L, B, M), dtype=real)
+    gG = np.zeros((L, B, M), dtype=real)
+    gS = np.zeros((L, B, M), dtype=real)
+    gbu = np.zeros_like(bu)
+    gw_next = np.zeros((B, M), dtype=bu.dtype)
+    gx_next = np.zeros((B, M), dtype=bu.dtype)
+
+    def dot(p, q):
+        return p.real * q.real + p.imag * q.imag
+
+    for t in range(L - 1, -1, -1):
+        a, g, s = (np.broadcast_to(v[t if v.shape[0] > 1 else 0], (B, M)) for v in (Av, Gv, Sv))
+        dt, dt2, alpha, inv_s, mask, ds_ddt, ds_dg, ds_da = _sdlinoss_step_terms(variant, a, g, s)
+        step_mask = ((s > real.type(1e-6)) & (s < real.type(1.0))).astype(real)
+        w_prev = states[t - 1, :, :, 0] if t > 0 else np.zeros((B, M), dtype=bu.dtype)
+        x_prev = states[t - 1, :, :, 1] if t > 0 else np.zeros((B, M), dtype=bu.dtype)
+        gx = grad_out[t] + gx_next
+        gw = gw_next + gx
+        comb = -a * x_prev + bu[t]
+        tmpw = alpha * w_prev + dt2 * comb
+        gt = gw * inv_s
+        gs_raw = -dot(gw, tmpw) * inv_s * inv_s * mask
+        g_step = gs_raw * ds_ddt + dot(gt, 2 * dt * comb)
+        g_a = gs_raw * ds_da - dt2 * dot(gt, x_prev)
+        g_g = gs_raw * ds_dg
+        if variant in ("imex2", "ex"):
+            g_step = g_step - g * dot(gt, w_prev)
+            g_g = g_g - dt * dot(gt, w_prev)
+        gA[t], gG[t], gS[t] = g_a, g_g, g_step * step_mask
+        gbu[t] = gt * dt2
+        gx_next = gx - (dt2 * a) * gt
+        gw_next = gt * alpha
+
+    def reduce(full, view_shape, orig_shape):
+        r = full
+        if view_shape[0] == 1 and L > 1:
+            r = r.sum(axis=0, keepdims=True)
+        if view_shape[1] == 1 and B > 1:
+            r = r.sum(axis=1, keepdims=True)
+        return r.reshape(orig_shape)
+
+    return (reduce(gA, Av.shape, shapes[0]), reduce(gG, Gv.shape, shapes[1]), reduce(gS, Sv.shape, shapes[2]), gbu)

@@ -14,7 +14,7 @@ Sources of the vectors:
 * ``linoss_im_snapshot.npz``       -- the inline LinOSS-IM snapshot of
   ``tests/test_linoss_parity.py:74-204``.
 * ``dlinoss_generated.npz``, ``linoss_generated.npz``, ``diag_generated.npz``,
-  ``selective_scan_generated.npz`` -- outputs of the reference itself run here
+  ``sdlinoss_generated.npz``, ``selective_scan_generated.npz`` -- outputs of the reference itself run here
   on seeded inputs: its pure-PyTorch recurrences (float64 and float32, grads by
   autograd) and its compiled CPU kernels (float32).
 """
@@ -243,6 +243,69 @@ def main():
         raw = kernels.lru_scan(lam.real.contiguous(), lam.imag.contiguous(), torch.view_as_real(b).contiguous())
         out[pre + "cpp_states"] = _np(torch.view_as_complex(raw.contiguous()))
     np.savez_compressed(os.path.join(HERE, "diag_generated.npz"), **out)
+    # ---- G. selective D-LinOSS (per-step coefficients) --------------------
+    from ossm.models import _sdlinoss_scan as sd
+
+    def sel_params(variant, L, B, M, gen):
+        """(A, G, step) from a pole radius / angle field, the layer's own map
+        (``src/ossm/models/sdlinoss.py:186-204``); a few raw steps lie above 1 so that the
+        step clamp and its gradient mask are exercised."""
+        r = torch.rand(L, B, M, generator=gen) * 0.7 + 0.25
+        th = (torch.rand(L, B, M, generator=gen) * 2 - 1) * 3.0
+        raw = torch.sigmoid(torch.randn(L, B, M, generator=gen)) * 0.9 + 0.05
+        dtc = raw.clone()
+        raw = torch.where(torch.rand(L, B, M, generator=gen) < 0.05, raw + 1.0, raw)
+        dtc = torch.clamp(torch.minimum(raw, torch.ones(())), min=1e-6)
+        r2 = r * r
+        cos_t = torch.cos(th)
+        if variant == "imex1":
+            A = (r2 - 2.0 * r * cos_t + 1.0) / (dtc * dtc * r2)
+            G = (1.0 - r2) / (dtc * r2)
+        elif variant == "imex2":
+            A = (r2 - 2.0 * r * cos_t + 1.0) / (dtc * dtc)
+            G = (1.0 - r2) / dtc
+        elif variant == "im":
+            A = (r2 - 2.0 * r * cos_t + 1.0) / (dtc * dtc * r2)
+            G = (-2.0 * r2 + 2.0 * r * cos_t) / (dtc * r2)
+        else:
+            A = (r2 - 2.0 * r * cos_t + 1.0) / (dtc * dtc)
+            G = (2.0 - 2.0 * r * cos_t) / dtc
+        return A.float(), G.float(), raw.float()
+
+    out = {}
+    gen = torch.Generator().manual_seed(777)
+    pick = {"M": lambda t: t[0, 0].contiguous(), "LM": lambda t: t[:, 0].contiguous(),
+            "BM": lambda t: t[0].contiguous(), "LBM": lambda t: t.contiguous()}
+    for variant in ("imex1", "imex2", "im", "ex"):
+        for kind, (L, B, M) in (("LBM", (37, 3, 11)), ("LM", (24, 2, 5)), ("BM", (24, 2, 5)), ("M", (24, 2, 5)),
+                                ("clamp", (6, 2, 3))):
+            A, G, raw = sel_params(variant, L, B, M, gen)
+            if kind == "clamp":      # one strongly negative damping entry drives S below its floor
+                G[2, 1, 1] = -3.0 / torch.clamp(raw[2, 1, 1], max=1.0)
+                a, g, s = A, G, raw
+            else:
+                a, g, s = (pick[kind](t) for t in (A, G, raw))
+            bu = torch.complex(torch.randn(L, B, M, generator=gen), torch.randn(L, B, M, generator=gen))
+            go = torch.complex(torch.randn(L, B, M, generator=gen), torch.randn(L, B, M, generator=gen))
+            pre = f"{variant}/{kind}/"
+            for k, v in (("A", a), ("G", g), ("step", s), ("bu", bu), ("grad_out", go)):
+                out[pre + k] = _np(v)
+            st = getattr(kernels, f"sdlinoss_{variant}_forward")(a, g, s, bu)
+            gr = getattr(kernels, f"sdlinoss_{variant}_backward")(a, g, s, bu, st, go)
+            out[pre + "cpp_states"] = _np(st)
+            for name, t in zip(("grad_A", "grad_G", "grad_step", "grad_bu"), gr):
+                out[pre + "cpp_" + name] = _np(t)
+            # the pure-PyTorch recurrence in float64, gradients by autograd
+            leaves = [t.double().clone().requires_grad_(True) for t in (a, g, s)]
+            bl = bu.to(torch.complex128).clone().requires_grad_(True)
+            st64 = sd._reference_sdlinoss_states(variant, leaves[0], leaves[1], leaves[2], bl)
+            x64 = st64[..., 1]
+            ((x64.real * go.real.double()).sum() + (x64.imag * go.imag.double()).sum()).backward()
+            out[pre + "py64_states"] = _np(st64)
+            for name, leaf in zip(("grad_A", "grad_G", "grad_step"), leaves):
+                out[pre + "py64_" + name] = _np(leaf.grad)
+            out[pre + "py64_grad_bu"] = _np(bl.grad)
+    np.savez_compressed(os.path.join(HERE, "sdlinoss_generated.npz"), **out)
 
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
