@@ -154,6 +154,46 @@ int ossm_b200_linoss_scan_backward(const void* m11, const void* m12, const void*
                                    void* workspace, size_t workspace_bytes, int64_t L, int64_t B, int64_t P,
                                    ossm_b200_stream_t stream);
 
+/* ---- selective D-LinOSS (per-step coefficients) ---------------------------------
+ * Replaces ossm::sdlinoss_<v>_forward / sdlinoss_<v>_backward for v = imex1, imex2, im, ex
+ * (src/ossm/csrc/sdlinoss_imex1.cpp:331-427 and the same entries of sdlinoss_imex2.cpp,
+ * sdlinoss_im.cpp, sdlinoss_ex.cpp; CUDA bodies sdlinoss_<v>_cuda.cu; bindings.cpp).
+ * `variant` is OSSM_B200_VARIANT_IMEX1 .. OSSM_B200_VARIANT_EX.
+ *
+ *   A, G, step : float32 fields over (L, B, M).  `*_strides` points at three element
+ *                strides {L, B, M} in host memory; a stride of 0 marks a broadcast axis
+ *                (the forms (M,), (L,M), (B,M), (L,B,M) of the reference's Strided3,
+ *                dlinoss_common.h:25-41).  The raw step is clamped to [1e-6, 1] inside.
+ *   bu, x, grad_x, grad_bu : complex64 [L, B, M], contiguous
+ *   states     : complex64 [L, B, M, 2] = (w, x) per step, the reference's forward output
+ *   carries    : the state after every ossm_b200_sdlinoss_carry_interval() steps,
+ *                ossm_b200_sdlinoss_carry_bytes() bytes; what the backward needs instead of
+ *                `states`
+ *
+ * Forward writes `x` and / or `states` (either may be NULL, not both) and `carries` when
+ * given.  Backward takes `states` or `carries` (states wins; neither is needed for
+ * L <= ossm_b200_lti_chunk()) and writes grad_bu and grad_A / grad_G / grad_step, each laid
+ * out with the strides of its parameter.  A gradient whose parameter is broadcast along
+ * the batch or state axis is accumulated with atomic adds and must be zero on entry (the
+ * reference allocates it with at::zeros_like); every other gradient is overwritten.
+ * The TMA-staged kernels run when A, G, step are all dense [L, B, M] with 16-byte aligned
+ * bases and B*M a multiple of 4; other views take plain-load kernels.
+ */
+int ossm_b200_sdlinoss_carry_interval(void);
+size_t ossm_b200_sdlinoss_carry_bytes(int64_t L, int64_t B, int64_t M);
+int ossm_b200_sdlinoss_forward(int variant, const float* A, const int64_t* A_strides, const float* G,
+                               const int64_t* G_strides, const float* step, const int64_t* step_strides,
+                               const void* bu, void* x, void* states, void* carries, int64_t L, int64_t B,
+                               int64_t M, ossm_b200_stream_t stream);
+int ossm_b200_sdlinoss_backward(int variant, const float* A, const int64_t* A_strides, const float* G,
+                                const int64_t* G_strides, const float* step, const int64_t* step_strides,
+                                const void* bu, const void* carries, const void* states, const void* grad_x,
+                                float* grad_A, float* grad_G, float* grad_step, void* grad_bu, int64_t L,
+                                int64_t B, int64_t M, ossm_b200_stream_t stream);
+/* Launch-shape knobs of the two kernels above (keys fwd_ring, fwd_warps, bwd_ring, bwd_warps,
+ * force_plain); for experiments, the defaults are the measured best. */
+int ossm_b200_sdlinoss_set_tuning(const char* key, int value);
+
 /* ---- Mamba selective scan ------------------------------------------------------
  * Replaces ossm::selective_scan_cuda_forward / selective_scan_cuda_backward
  * (src/ossm/csrc/selective_scan_cuda.cu:253-393; bindings.cpp:199-222) and the CPU

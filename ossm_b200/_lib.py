@@ -48,6 +48,15 @@ SIGNATURES = {
     "ossm_b200_linoss_scan_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_size_t, c_int64, c_int64, c_int64,
                                                c_void_p]),
+    "ossm_b200_sdlinoss_forward": (c_int, [c_int, c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p,
+                                           POINTER(c_int64), c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                           c_int64, c_int64, c_void_p]),
+    "ossm_b200_sdlinoss_backward": (c_int, [c_int, c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p,
+                                            POINTER(c_int64), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "ossm_b200_sdlinoss_set_tuning": (c_int, [c_char_p, c_int]),
+    "ossm_b200_sdlinoss_carry_interval": (c_int, []),
+    "ossm_b200_sdlinoss_carry_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
 }
 
 

@@ -5,4 +5,5 @@
 #include "common.cu"
 #include "lti_scan.cu"
 #include "linoss_generic.cu"
+#include "sdlinoss_scan.cu"
 #include "selective_scan.cu"

@@ -426,6 +426,161 @@ lru_scan = _diag_compat("lru_scan")
 s5_scan = _diag_compat("s5_scan")
 
 
+# ---- selective D-LinOSS (per-step coefficients) -------------------------------
+SDLINOSS_VARIANTS = ("imex1", "imex2", "im", "ex")
+
+
+def _sd_field(t: Tensor, name: str, L: int, B: int, M: int):
+    """(tensor, element strides over (L, B, M)) of a parameter given with 1, 2 or 3 dimensions; an
+    axis of extent 1 is a broadcast axis (stride 0).  Axis assignment and messages follow
+    ``make_strided3`` (dlinoss_common.h:86-185): a 2-D parameter's first axis is time when its
+    extent is the length (or 1), else batch."""
+    if t.dim() < 1 or t.dim() > 3:
+        raise RuntimeError(f"Selective D-LinOSS expects parameters with 1, 2, or 3 dimensions; got {t.dim()}")
+    sizes, strides = [1, 1, 1], [0, 0, 0]
+
+    def put(axis: int, dim: int, expected: int, what: str):
+        size = int(t.shape[dim])
+        if size != expected and size != 1:
+            raise RuntimeError(f"Expected size {expected} or 1 along {what} axis but got {size}")
+        sizes[axis] = size
+        strides[axis] = 0 if size == 1 else int(t.stride(dim))
+
+    if t.dim() == 1:
+        put(2, 0, M, "M")
+    elif t.dim() == 2:
+        size0 = int(t.shape[0])
+        if size0 == L or size0 == 1:
+            put(0, 0, L, "length")
+        elif size0 == B:
+            put(1, 0, B, "batch")
+        else:
+            raise RuntimeError(f"First dimension must match length or batch (or be 1), got {size0}")
+        put(2, 1, M, "last")
+    else:
+        put(0, 0, L, "length")
+        put(1, 1, B, "batch")
+        put(2, 2, M, "state")
+    return t, strides
+
+
+def _sd_prepare(A: Tensor, G: Tensor, step: Tensor, bu: Tensor):
+    if bu.dim() != 3:
+        raise RuntimeError("bu must have shape (length, batch, ssm_size)")
+    _require_cuda("bu", bu)
+    if any(t.device != bu.device for t in (A, G, step)):
+        raise RuntimeError("All tensors must live on the same device")
+    if bu.dtype != torch.complex64 or any(t.dtype != torch.float32 for t in (A, G, step)):
+        raise RuntimeError("ossm_b200: the selective scan runs in float32 / complex64 only")
+    L, B, M = (int(v) for v in bu.shape)
+    fields = []
+    for name, t in (("A", A), ("G", G), ("step", step)):
+        t = t if t.is_contiguous() else t.contiguous()
+        fields.append(_sd_field(t, name, L, B, M))
+    return L, B, M, fields
+
+
+def _sd_carry_rows(L: int) -> int:
+    step = int(_lib.load().ossm_b200_sdlinoss_carry_interval())
+    return max((L + step - 1) // step - 1, 0)
+
+
+def _i64x3(strides):
+    return (ctypes.c_int64 * 3)(*strides)
+
+
+def sdlinoss_scan_forward(variant: str, A: Tensor, G: Tensor, step: Tensor, bu: Tensor, *, want_x: bool = True,
+                          want_states: bool = False, want_carries: bool = True):
+    """Selective D-LinOSS scan; returns ``(x [L,B,M], states [L,B,M,2], carries)`` (entries not asked
+    for are ``None``).  ``A, G, step`` may be ``(M,)``, ``(L,M)``, ``(B,M)`` or ``(L|1,B|1,M)``."""
+    vid = VARIANT_IDS[variant]
+    L, B, M, fields = _sd_prepare(A, G, step, bu)
+    dev = bu.device
+    x = torch.empty((L, B, M), dtype=torch.complex64, device=dev) if want_x else None
+    states = torch.empty((L, B, M, 2), dtype=torch.complex64, device=dev) if want_states else None
+    carries = None
+    if want_carries:
+        carries = torch.empty((_sd_carry_rows(L), B, M, 2), dtype=torch.complex64, device=dev)
+    if L == 0 or B == 0 or M == 0:
+        return x, states, carries
+    if not bu.is_contiguous():
+        raise RuntimeError("bu must be contiguous")
+    (a, sa), (g, sg), (s, ss) = fields
+    with torch.cuda.device(dev):
+        rc = _lib.load().ossm_b200_sdlinoss_forward(
+            vid, _p(a), _i64x3(sa), _p(g), _i64x3(sg), _p(s), _i64x3(ss), _p(bu), _p(x), _p(states),
+            _p(carries) if carries is not None and carries.numel() else None, L, B, M, _stream(dev))
+    _lib.check(rc, "sdlinoss_forward")
+    return x, states, carries
+
+
+def sdlinoss_scan_backward(variant: str, A: Tensor, G: Tensor, step: Tensor, bu: Tensor, grad_x: Tensor, *,
+                           carries: Optional[Tensor] = None, states: Optional[Tensor] = None):
+    """``(grad_A, grad_G, grad_step, grad_bu)``, the parameter gradients in the shapes of the
+    parameters (broadcast axes summed).  Needs ``carries`` (from :func:`sdlinoss_scan_forward`) or
+    the full ``states``."""
+    vid = VARIANT_IDS[variant]
+    L, B, M, fields = _sd_prepare(A, G, step, bu)
+    if grad_x.shape != bu.shape:
+        raise RuntimeError("grad_output must match bu shape")
+    dev = bu.device
+    grads = []
+    for (t, strides), orig in zip(fields, (A, G, step)):
+        dense = strides == [B * M, M, 1] or L * B * M == 0
+        grads.append(torch.empty_like(t) if dense and t.numel() == L * B * M else torch.zeros_like(t))
+    grad_bu = torch.empty_like(bu)
+    if L == 0 or B == 0 or M == 0:
+        return (*[gr.zero_().view(o.shape) for gr, o in zip(grads, (A, G, step))], grad_bu)
+    if grad_x.dtype != torch.complex64 or grad_x.device != dev:
+        raise RuntimeError("ossm_b200: grad_output must be complex64 on the device of bu")
+    if not (bu.is_contiguous() and grad_x.is_contiguous()):
+        raise RuntimeError("states and grad_output must be contiguous on CUDA")
+    for name, t, shape in (("carries", carries, (_sd_carry_rows(L), B, M, 2)),
+                           ("states", states, (L, B, M, 2))):
+        if t is not None and (t.dtype != torch.complex64 or not t.is_contiguous() or tuple(t.shape) != shape):
+            raise RuntimeError(f"ossm_b200: {name} must be a contiguous complex64 tensor of shape {shape}")
+    (a, sa), (g, sg), (s, ss) = fields
+    with torch.cuda.device(dev):
+        rc = _lib.load().ossm_b200_sdlinoss_backward(
+            vid, _p(a), _i64x3(sa), _p(g), _i64x3(sg), _p(s), _i64x3(ss), _p(bu),
+            _p(carries) if carries is not None and carries.numel() else None,
+            _p(states) if states is not None and states.numel() else None,
+            _p(grad_x), _p(grads[0]), _p(grads[1]), _p(grads[2]), _p(grad_bu), L, B, M, _stream(dev))
+    _lib.check(rc, "sdlinoss_backward")
+    return grads[0], grads[1], grads[2], grad_bu
+
+
+def _make_sdlinoss(variant: str):
+    def forward(A: Tensor, G: Tensor, step: Tensor, bu: Tensor) -> Tensor:
+        _, states, _ = sdlinoss_scan_forward(variant, A, G, step, bu, want_x=False, want_states=True,
+                                             want_carries=False)
+        return states
+
+    def backward(A: Tensor, G: Tensor, step: Tensor, bu: Tensor, states: Tensor, grad_output: Tensor):
+        if states.dim() != 4 or states.size(3) != 2:
+            raise RuntimeError("states must have shape (length, batch, ssm_size, 2)")
+        if bu.dim() != 3:
+            raise RuntimeError("bu must have shape (length, batch, ssm_size)")
+        return sdlinoss_scan_backward(variant, A, G, step, bu, grad_output, states=states)
+
+    forward.__name__ = f"sdlinoss_{variant}_forward"
+    backward.__name__ = f"sdlinoss_{variant}_backward"
+    forward.__doc__ = (f"``ossm._kernels.sdlinoss_{variant}_forward(A, G, step, bu)`` (sdlinoss_{variant}.cpp): "
+                       "the state trajectory ``[L,B,M,2]`` complex64.")
+    backward.__doc__ = (f"``ossm._kernels.sdlinoss_{variant}_backward``: ``(grad_A, grad_G, grad_step, grad_bu)``.")
+    return forward, backward
+
+
+sdlinoss_imex1_forward, sdlinoss_imex1_backward = _make_sdlinoss("imex1")
+sdlinoss_imex2_forward, sdlinoss_imex2_backward = _make_sdlinoss("imex2")
+sdlinoss_im_forward, sdlinoss_im_backward = _make_sdlinoss("im")
+sdlinoss_ex_forward, sdlinoss_ex_backward = _make_sdlinoss("ex")
+
+
+def set_sdlinoss_tuning(key: str, value: int) -> None:
+    _lib.check(_lib.load().ossm_b200_sdlinoss_set_tuning(key.encode(), int(value)), "sdlinoss_set_tuning")
+
+
 # ---- names ossm calls unconditionally but that are outside this library ------
 def _out_of_scope(name: str):
     def stub(*_args, **_kwargs):
