@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba", "sharded_layer"],
+    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba", "sdlinoss", "sharded_layer"],
                     help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
                          "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
                          "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
@@ -431,6 +431,32 @@ def run_secondary(args):
 
         def bwd(saved):
             return kernels.lti_scan_backward("linoss_im", a, None, dt, bu, saved[2], gx)
+    elif args.workload == "sdlinoss":
+        # selective D-LinOSS at the headline shape: per-step a, g, dt fields [L,B,M] from a slowly varying pole
+        # field (the layer's map, sdlinoss.py:186-204)
+        L, B, P = 4096, (args.side_batch or 64), 256
+        r = (torch.rand(1, B, P, generator=gen, device=dev) * 0.6 + 0.3
+             + 0.03 * torch.randn(L, B, P, generator=gen, device=dev)).clamp_(0.25, 0.95)
+        th = (torch.rand(1, B, P, generator=gen, device=dev) * 2 - 1) * 2.5 + 0.05 * torch.randn(
+            L, B, P, generator=gen, device=dev)
+        dtf = (torch.sigmoid(torch.randn(1, B, P, generator=gen, device=dev)) * 0.9 + 0.05) * (
+            1 + 0.03 * torch.randn(L, B, P, generator=gen, device=dev))
+        dtc = dtf.clamp(1e-6, 1.0)
+        Af = (r * r - 2 * r * torch.cos(th) + 1) / (dtc * dtc * r * r)
+        Gf = (1 - r * r) / (dtc * r * r)
+        del r, th, dtc
+        bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev) * 0.5)
+        gx = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev))
+        # forward: a, g, dt 12 B + bu 8 -> x 8 ; backward: 12 + bu 8 + grad_x 8 -> grad_bu 8 + three gradients 12
+        elems, fb, bb = L * B * P, 28, 48
+        name = f"selective D-LinOSS imex1 scan fwd+bwd, B={B} L={L} M={P}, dense per-step coefficients, complex64"
+        metric = "sdlinoss_scan_fwd_bwd_gelem_per_s"
+
+        def fwd():
+            return kernels.sdlinoss_scan_forward("imex1", Af, Gf, dtf, bu)
+
+        def bwd(saved):
+            return kernels.sdlinoss_scan_backward("imex1", Af, Gf, dtf, bu, gx, carries=saved[2])
     else:
         Bz, Dn, L, N = (args.side_batch or 32), 2048, 8192, 16
         io = torch.bfloat16

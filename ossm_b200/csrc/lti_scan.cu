@@ -137,11 +137,13 @@ struct FwdParams {
 
 // Shared memory per warp: ring * kStageBytes, preceded (per CTA) by the barriers.
 // kOut: 1 = write x, 2 = write full states, 3 = both.
-template <int V, bool kTma, int kOut>
+// kW: warps per CTA when known at compile time (0 = read from the launch); a constant makes every
+// shared-memory offset of the unrolled time loop an immediate.
+template <int V, bool kTma, int kOut, int kW = 0>
 __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant__ CUtensorMap tm_bu, FwdParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5;
-  const int warps = blockDim.x >> 5;
+  const int warps = kW > 0 ? kW : (int)(blockDim.x >> 5);
   const int cta_cols = warps * kCols;                      // columns of one shared stage
   const long long cta_col0 = (long long)blockIdx.x * cta_cols;
   const long long n = cta_col0 + threadIdx.x;              // this lane's series
@@ -326,13 +328,13 @@ __device__ __forceinline__ float2 bwd_step(const Coef& c, float2& l0, float2& l1
 //   generic variants: acc = { <g0,p0>, <g0,p1>, <g1,p0>, <g1,p1>, <g0,bu>, <g1,bu> }
 //   imex1           : acc = { <gt,p0>, <gt,p1>, <gt,bu>, 0, 0, 0 }  with gt = g0 + g1
 // (g0,g1) = adjoint after adding the upstream gradient, (p0,p1) = previous state.
-template <int V, bool kTma>
+template <int V, bool kTma, int kW = 0>
 __global__ void __launch_bounds__(128, 1)
 lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_constant__ CUtensorMap tm_gx,
                     BwdParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5;
-  const int warps = blockDim.x >> 5;
+  const int warps = kW > 0 ? kW : (int)(blockDim.x >> 5);
   const int cta_cols = warps * kCols;
   const long long cta_col0 = (long long)blockIdx.x * cta_cols;
   const long long n = cta_col0 + threadIdx.x;
@@ -790,8 +792,13 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
       if (int rc = check_cuda(cudaGetLastError(), "lti_segment_combine_kernel launch")) return rc;
       q.seg_init = seg_init;
     }
-    if (int rc = set_smem(lti_forward_kernel<V, true, kOut>, smem)) return rc;
-    lti_forward_kernel<V, true, kOut><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm, q);
+    if (warps == 4) {
+      if (int rc = set_smem(lti_forward_kernel<V, true, kOut, 4>, smem)) return rc;
+      lti_forward_kernel<V, true, kOut, 4><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm, q);
+    } else {
+      if (int rc = set_smem(lti_forward_kernel<V, true, kOut>, smem)) return rc;
+      lti_forward_kernel<V, true, kOut><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm, q);
+    }
   } else {
     q.ring = 0;
     lti_forward_kernel<V, false, kOut><<<(unsigned)grid, warps * 32, 0, stream>>>(tm, q);
@@ -849,8 +856,13 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
       q.lam_init = seg_init;
     }
     const size_t smem = 1024 + (size_t)warps * q.ring * 2 * kStageBytes;
-    if (int rc = set_smem(lti_backward_kernel<V, true>, smem)) return rc;
-    lti_backward_kernel<V, true><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm_bu, tm_gx, q);
+    if (warps == 4) {
+      if (int rc = set_smem(lti_backward_kernel<V, true, 4>, smem)) return rc;
+      lti_backward_kernel<V, true, 4><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm_bu, tm_gx, q);
+    } else {
+      if (int rc = set_smem(lti_backward_kernel<V, true>, smem)) return rc;
+      lti_backward_kernel<V, true><<<dim3((unsigned)grid, S), warps * 32, smem, stream>>>(tm_bu, tm_gx, q);
+    }
   } else {
     q.ring = 0;
     lti_backward_kernel<V, false><<<(unsigned)grid, warps * 32, 0, stream>>>(tm_bu, tm_gx, q);

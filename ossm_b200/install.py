@@ -6,7 +6,7 @@ Seeding ``sys.modules["ossm._kernels"]`` with :mod:`ossm_b200.kernels` *before*
 ``import ossm`` makes every shim (and the ``torch.ops.ossm.*`` library it
 registers) call into ``libossm_b200.so``.  ``patch_ops=True`` additionally swaps
 ossm's op functions for the leaner ones of this package (no full-state
-materialisation, CUDA backward for LinOSS, bf16 selective scan).
+materialisation, CUDA backward for LinOSS, bf16 selective scan, selective D-LinOSS from chunk carries).
 """
 from __future__ import annotations
 
@@ -29,10 +29,11 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
     except ImportError:
         return
     setattr(ossm, "_kernels", kernels)
-    from . import diag, dlinoss, linoss, selective_scan
+    from . import diag, dlinoss, linoss, sdlinoss, selective_scan
 
     mods = {}
-    for name in ("_dlinoss_scan", "dlinoss", "_linoss_scan", "linoss", "_selective_scan", "mambarec", "lru", "s5"):
+    for name in ("_dlinoss_scan", "dlinoss", "_sdlinoss_scan", "sdlinoss", "_linoss_scan", "linoss", "_selective_scan",
+                 "mambarec", "lru", "s5"):
         try:
             mods[name] = importlib.import_module(f"ossm.models.{name}")
         except ImportError:
@@ -40,6 +41,10 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
     for name in ("_dlinoss_scan", "dlinoss"):
         if name in mods:
             mods[name].run_dlinoss = dlinoss.run_dlinoss
+    # selective D-LinOSS: the layer imports run_sdlinoss by name (sdlinoss.py:13)
+    for name in ("_sdlinoss_scan", "sdlinoss"):
+        if name in mods:
+            mods[name].run_sdlinoss = sdlinoss.run_sdlinoss
     if "linoss" in mods:
         mods["linoss"]._run_associative_scan = linoss.run_associative_scan
         mods["linoss"].try_run_scan = linoss.try_run_scan
