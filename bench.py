@@ -434,7 +434,7 @@ def run_secondary(args):
     elif args.workload == "sdlinoss":
         # selective D-LinOSS at the headline shape: per-step a, g, dt fields [L,B,M] from a slowly varying pole
         # field (the layer's map, sdlinoss.py:186-204)
-        L, B, P = 4096, (args.side_batch or 64), 256
+        L, B, P = args.length, (args.side_batch or 64), args.ssm
         r = (torch.rand(1, B, P, generator=gen, device=dev) * 0.6 + 0.3
              + 0.03 * torch.randn(L, B, P, generator=gen, device=dev)).clamp_(0.25, 0.95)
         th = (torch.rand(1, B, P, generator=gen, device=dev) * 2 - 1) * 2.5 + 0.05 * torch.randn(
