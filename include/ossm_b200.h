@@ -215,6 +215,10 @@ int ossm_b200_sdlinoss_set_tuning(const char* key, int value);
 
 /* Time steps per chunk for a given state size N (256 for N<=16, 128 for N<=32, ...). */
 int ossm_b200_selective_scan_chunk(int64_t N);
+/* Kernel choice for experiments: key "serial" = 1 (default) runs the serial-in-time kernels for the
+ * state sizes they cover, 0 the time-parallel kernels for every size.  Changes the value of
+ * ossm_b200_selective_scan_chunk(); forward and backward of one scan must run under the same setting. */
+int ossm_b200_selective_scan_set_tuning(const char* key, int value);
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 

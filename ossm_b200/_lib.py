@@ -55,6 +55,7 @@ SIGNATURES = {
                                             POINTER(c_int64), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_sdlinoss_set_tuning": (c_int, [c_char_p, c_int]),
+    "ossm_b200_selective_scan_set_tuning": (c_int, [c_char_p, c_int]),
     "ossm_b200_sdlinoss_carry_interval": (c_int, []),
     "ossm_b200_sdlinoss_carry_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
 }

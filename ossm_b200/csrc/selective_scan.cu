@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
         y2[j] = make_float2(0.f, 0.f);
       }
       const int slot = (warp * kCI + ci) * NP;
-      const float* cs_in = p.chunk_states + ((b * p.D + d) * nchunks + c) * p.N;
+      const float* cs_in = p.chunk_states + ((b * p.D + d) * p.nstates + c * (T / p.state_interval)) * p.N;
 #pragma unroll 1
       for (int pr = 0; pr < NP; ++pr) {
         const float2 Ap = load_A_pair(p.A, d, N, pr, true);
@@ -698,6 +698,20 @@ static int dispatch_items(bool backward, const Params& p, cudaStream_t stream) {
   }
 }
 
+}  // namespace sscan
+}  // namespace ossm_b200
+
+#include "selective_scan_serial.cuh"
+
+namespace ossm_b200 {
+namespace sscan {
+
+// Serial-in-time kernels (selective_scan_serial.cuh) are used for the state sizes they are built for.
+static int g_use_serial = 1;
+static bool serial_ok(long long N) { return g_use_serial && N == 16; }
+// Steps between the states the forward saves for the backward.
+static int state_interval_for(long long N) { return serial_ok(N) ? kSerialInterval : 32 * items_bwd(N); }
+
 // Channels per warp: the most that still gives one CTA per SM.
 static int pick_cpw(long long B, long long D) {
   int cpw = kCI;
@@ -714,11 +728,17 @@ extern "C" {
 
 using namespace ossm_b200;
 
-int ossm_b200_selective_scan_chunk(int64_t N) { return 32 * sscan::items_bwd(N); }
+int ossm_b200_selective_scan_chunk(int64_t N) { return sscan::state_interval_for(N); }
+
+int ossm_b200_selective_scan_set_tuning(const char* key, int value) {
+  if (key != nullptr && !strcmp(key, "serial")) { sscan::g_use_serial = value != 0; return kOk; }
+  set_last_error("selective_scan_set_tuning: unknown key %s", key ? key : "(null)");
+  return kErrInvalidArgument;
+}
 
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N) {
   if (B <= 0 || D <= 0 || L <= 0 || N <= 0) return 0;
-  const int64_t T = 32 * sscan::items_bwd(N);
+  const int64_t T = sscan::state_interval_for(N);
   return (size_t)B * D * ((L + T - 1) / T) * N * sizeof(float);
 }
 
@@ -755,12 +775,18 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
   p.u = u; p.dt = dt; p.A = A; p.Bm = Bm; p.Cm = Cm; p.z = z; p.Dskip = Dskip; p.out = out;
   p.chunk_states = chunk_states;
   p.B = B; p.D = D; p.L = L; p.N = N;
-  p.state_interval = 32 * sscan::items_bwd(N);
+  p.state_interval = sscan::state_interval_for(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
   p.cpw = sscan::pick_cpw(B, D);
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(out) && (!z || sscan::aligned16(z)) &&
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
+  if (sscan::serial_ok(N)) {
+    // the B/C tiles are also read with 16-byte loads
+    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm);
+    return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_serial<float>(p, stream)
+                                           : sscan::launch_fwd_serial<__nv_bfloat16>(p, stream);
+  }
   return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::dispatch_items<float>(false, p, stream)
                                          : sscan::dispatch_items<__nv_bfloat16>(false, p, stream);
 }
@@ -795,7 +821,7 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.dA_part = static_cast<float*>(workspace);
   p.dD_part = Dskip ? p.dA_part + (size_t)B * D * N : nullptr;
   p.B = B; p.D = D; p.L = L; p.N = N;
-  p.state_interval = 32 * sscan::items_bwd(N);
+  p.state_interval = sscan::state_interval_for(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
   p.cpw = sscan::pick_cpw(B, D);
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
