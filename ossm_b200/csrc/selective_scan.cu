@@ -828,8 +828,17 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(dout) && sscan::aligned16(du) &&
              sscan::aligned16(ddt) && (!z || (sscan::aligned16(z) && sscan::aligned16(dz))) &&
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
-  int rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::dispatch_items<float>(true, p, stream)
-                                           : sscan::dispatch_items<__nv_bfloat16>(true, p, stream);
+  int rc;
+  if (sscan::serial_ok(N)) {
+    // B/C tiles, saved states, dB and dC are also accessed with 16-byte operations
+    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(chunk_states) &&
+               sscan::aligned16(dB) && sscan::aligned16(dC);
+    rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_serial<float>(p, stream)
+                                         : sscan::launch_bwd_serial<__nv_bfloat16>(p, stream);
+  } else {
+    rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::dispatch_items<float>(true, p, stream)
+                                         : sscan::dispatch_items<__nv_bfloat16>(true, p, stream);
+  }
   if (rc) return rc;
   const long long M = D * N;
   sscan::sscan_reduce_batch_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(p.dA_part, dA, B, M);

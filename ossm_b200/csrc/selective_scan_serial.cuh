@@ -293,6 +293,337 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------
+// Lane pairs: lanes l and l + 16 of a warp own the low and high 8 states of channel
+// (warp base + l % 16), so a thread keeps, for one window of kSerialInterval steps, the
+// decays a_t[n] and the states h_{t-1}[n] of its 8 states in registers (128 registers).
+// Windows are walked right to left.  Per window: re-run the forward recurrence from the
+// state saved by the forward pass, then the adjoint
+//     g_t = C_t * gy_t + a_{t+1} g_{t+1}
+// right to left, forming du, ddt, dz (sums over the 16 states: one shuffle between the
+// two lanes of a pair), dA, dD (register accumulators over the whole sequence) and the
+// per-step dB_t[n] = g_t dt_t u_t, dC_t[n] = gy_t h_t, which are sums over channels:
+// within a warp through a padded shared-memory transpose (lane c of a half ends up with
+// value c summed over the 16 channels), across the CTA's warps through a per-window
+// partial tile, and across CTAs with one 16-byte vector atomic per (n, 4 steps).
+constexpr int kBwdWarps = 4;
+constexpr int kBwdThreads = kBwdWarps * 32;
+constexpr int kBwdChPerWarp = 16;
+constexpr int kBwdSpan = kBwdWarps * kBwdChPerWarp;   // channels per CTA
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+template <typename IO, int N>
+struct BwdSmem {
+  static constexpr int G = kSerialInterval;
+  static constexpr int kVecIO = G * (int)sizeof(IO) / 16;
+  static constexpr int kChVecs = 3 * kVecIO + 2;
+  static constexpr int kPad = 20;
+  IO tile[2][kStage * 2 * N];                         // B | C per step, two stages
+  uint4 raw[TileLoader<IO, N, kBwdThreads>::kItemsTotal];
+  uint4 slab[2][kBwdWarps][kChVecs][kBwdChPerWarp];   // per-channel operands of a window, two windows
+  uint4 snap[2][kBwdWarps][2][32];                    // saved state of each lane's 8 states
+  float xpose[kBwdWarps][32 * kPad];                  // per-warp transpose buffer
+  float part[2][kBwdWarps][G][32];                    // per-warp channel sums of dB / dC of a window
+};
+
+template <typename IO, int N>
+__global__ void __launch_bounds__(kBwdThreads, 2) sscan_backward_serial_kernel(Params p) {
+  constexpr int G = kSerialInterval;
+  constexpr int NH = N / 2;          // states per thread
+  constexpr int NQ = NH / 2;         // state pairs per thread
+  constexpr int kWinPerStage = kStage / G;
+  constexpr int kVecIO = G * (int)sizeof(IO) / 16;
+  constexpr int kChVecs = 3 * kVecIO + 2;      // u | dt dt | z | dout  (16-byte vectors per channel and window)
+  constexpr int kPad = 20;                     // floats per lane in the transpose buffer (16 used)
+  using Loader = TileLoader<IO, N, kBwdThreads>;
+  using Smem = BwdSmem<IO, N>;
+  extern __shared__ __align__(16) unsigned char bwd_smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(bwd_smem_raw);
+  auto& tile = sm.tile;
+  auto& raw = sm.raw;
+  auto& slab = sm.slab;
+  auto& snap = sm.snap;
+  auto& xpose = sm.xpose;
+  auto& part = sm.part;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = lane >> 4, c = lane & 15;
+  const long long b = blockIdx.y;
+  const long long dch = (long long)blockIdx.x * kBwdSpan + warp * kBwdChPerWarp + c;
+  const bool active = dch < p.D;
+  const long long d = active ? dch : 0;          // idle lanes shadow channel 0 and store nothing
+  const long long row = (b * p.D + d) * p.L;
+  const IO* u_row = static_cast<const IO*>(p.u) + row;
+  const float* dt_row = p.dt + row;
+  const IO* z_row = p.z ? static_cast<const IO*>(p.z) + row : nullptr;
+  const IO* go_row = static_cast<const IO*>(p.dout) + row;
+  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * N * p.L;
+  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * N * p.L;
+  const float* snaps = p.chunk_states + (b * p.D + d) * p.nstates * N + half * NH;
+
+  float2 A2[NQ], ag[NQ], dAacc[NQ];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const int n = half * NH + 2 * q;
+    A2[q] = make_float2(__ldg(p.A + d * N + n) * kLog2e, __ldg(p.A + d * N + n + 1) * kLog2e);
+    ag[q] = make_float2(0.f, 0.f);
+    dAacc[q] = make_float2(0.f, 0.f);
+  }
+  const float dskip = p.Dskip ? __ldg(p.Dskip + d) : 0.0f;
+  float dDacc = 0.0f;
+
+  const long long nwin = (p.L + G - 1) / G;
+  const long long nstages = (p.L + kStage - 1) / kStage;
+
+  // 16-byte vectors of one row segment -> slab (lanes of the low half only) ------------------------
+  auto issue_vecs = [&](uint4* dst0, const void* rowp, int elem_bytes, long long t0, int nvec) {
+    // dst0 + v * kBwdChPerWarp is this channel's v-th vector
+    const char* src = static_cast<const char*>(rowp) + t0 * elem_bytes;
+    if (p.vec_ok && t0 + G <= p.L) {
+      for (int v = 0; v < nvec; ++v)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst0 + v * kBwdChPerWarp)),
+                     "l"(src + 16 * v) : "memory");
+    } else {
+      const int per = 16 / elem_bytes;
+      for (int v = 0; v < nvec; ++v) {
+        uint4 tmp = make_uint4(0u, 0u, 0u, 0u);
+        char* tb = reinterpret_cast<char*>(&tmp);
+        for (int j = 0; j < per; ++j)
+          if (t0 + v * per + j < p.L)
+            for (int k = 0; k < elem_bytes; ++k) tb[j * elem_bytes + k] = src[(v * per + j) * elem_bytes + k];
+        dst0[v * kBwdChPerWarp] = tmp;
+      }
+    }
+  };
+  auto issue_window = [&](int buf, long long w) {
+    if (w >= 0) {
+      const long long t0 = w * G;
+      if (half == 0) {
+        uint4* base = &slab[buf][warp][0][c];
+        issue_vecs(base, u_row, (int)sizeof(IO), t0, kVecIO);
+        issue_vecs(base + kVecIO * kBwdChPerWarp, dt_row, 4, t0, 2);
+        if (z_row) issue_vecs(base + (kVecIO + 2) * kBwdChPerWarp, z_row, (int)sizeof(IO), t0, kVecIO);
+        issue_vecs(base + (2 * kVecIO + 2) * kBwdChPerWarp, go_row, (int)sizeof(IO), t0, kVecIO);
+      }
+      const float* sp = snaps + w * N;
+#pragma unroll
+      for (int v = 0; v < 2; ++v)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&snap[buf][warp][v][lane])),
+                     "l"(sp + 4 * v) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto read_vecs = [&](const uint4* src0, int elem_bytes, float (&out)[G]) {
+    if (elem_bytes == 4) {
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        const uint4 r = src0[v * kBwdChPerWarp];
+        out[4 * v] = __uint_as_float(r.x); out[4 * v + 1] = __uint_as_float(r.y);
+        out[4 * v + 2] = __uint_as_float(r.z); out[4 * v + 3] = __uint_as_float(r.w);
+      }
+    } else {
+      const uint4 r = src0[0];
+      const uint32_t wv[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        out[2 * j] = __uint_as_float(wv[j] << 16);
+        out[2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+      }
+    }
+  };
+  // (state pairs of this lane's half) of B and C of one tile step
+  auto load_bc_half = [&](const IO* step, float2 (&Bp)[NQ], float2 (&Cp)[NQ]) {
+    if constexpr (sizeof(IO) == 4) {
+      const float4* bv = reinterpret_cast<const float4*>(step + half * NH);
+      const float4* cv = reinterpret_cast<const float4*>(step + N + half * NH);
+#pragma unroll
+      for (int q = 0; q < NQ / 2; ++q) {
+        const float4 x = bv[q], y = cv[q];
+        Bp[2 * q] = make_float2(x.x, x.y); Bp[2 * q + 1] = make_float2(x.z, x.w);
+        Cp[2 * q] = make_float2(y.x, y.y); Cp[2 * q + 1] = make_float2(y.z, y.w);
+      }
+    } else {
+      const uint4 x = *reinterpret_cast<const uint4*>(step + half * NH);
+      const uint4 y = *reinterpret_cast<const uint4*>(step + N + half * NH);
+      const uint32_t bw[4] = {x.x, x.y, x.z, x.w}, cw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        Bp[q] = make_float2(__uint_as_float(bw[q] << 16), __uint_as_float(bw[q] & 0xffff0000u));
+        Cp[q] = make_float2(__uint_as_float(cw[q] << 16), __uint_as_float(cw[q] & 0xffff0000u));
+      }
+    }
+  };
+
+  // prologue: last stage's tiles and the last window's operands
+  Loader::issue(raw, Bm_b, Cm_b, (nstages - 1) * kStage, p.L, p.vec_ok);
+  issue_window((int)((nwin - 1) & 1), nwin - 1);
+  Loader::finish(raw, tile[(nstages - 1) & 1]);
+  __syncthreads();
+
+  for (long long w = nwin - 1; w >= 0; --w) {
+    const long long t0 = w * G;
+    const long long s = w / kWinPerStage;
+    const int tb = (int)(s & 1), wb = (int)(w & 1);
+    const int tl = (int)(w % kWinPerStage) * G;          // first step of the window inside the tile
+    const bool stage_head = (w % kWinPerStage) == kWinPerStage - 1 || w == nwin - 1;   // first window of a stage we process
+    issue_window(wb ^ 1, w - 1);
+    if (stage_head && s > 0) {
+      Loader::issue(raw, Bm_b, Cm_b, (s - 1) * kStage, p.L, p.vec_ok);
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    }
+    __syncwarp();   // the low half's copies are read by both halves
+
+    float u_c[G], dt_c[G], z_c[G], go_c[G];
+    {
+      const uint4* base = &slab[wb][warp][0][c];
+      read_vecs(base, (int)sizeof(IO), u_c);
+      read_vecs(base + kVecIO * kBwdChPerWarp, 4, dt_c);
+      if (z_row) read_vecs(base + (kVecIO + 2) * kBwdChPerWarp, (int)sizeof(IO), z_c);
+      read_vecs(base + (2 * kVecIO + 2) * kBwdChPerWarp, (int)sizeof(IO), go_c);
+      if (!active) {   // a shadow lane must not add to the sums over channels
+#pragma unroll
+        for (int j = 0; j < G; ++j) go_c[j] = 0.0f;
+      }
+    }
+    float2 h[NQ];
+    {
+      const uint4 s0 = snap[wb][warp][0][lane], s1 = snap[wb][warp][1][lane];
+      h[0] = make_float2(__uint_as_float(s0.x), __uint_as_float(s0.y));
+      h[1] = make_float2(__uint_as_float(s0.z), __uint_as_float(s0.w));
+      h[2] = make_float2(__uint_as_float(s1.x), __uint_as_float(s1.y));
+      h[3] = make_float2(__uint_as_float(s1.z), __uint_as_float(s1.w));
+    }
+    const IO* steps = tile[tb] + tl * 2 * N;
+
+    // forward re-run of the window
+    float2 a[G][NQ], hw[G][NQ];
+    float yv[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      float2 Bp[NQ], Cp[NQ];
+      load_bc_half(steps + j * 2 * N, Bp, Cp);
+      const float2 dtv = splat(dt_c[j]);
+      const float2 dtu = splat(dt_c[j] * u_c[j]);
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        const float2 x = p2mul(dtv, A2[q]);
+        a[j][q] = make_float2(ex2(x.x), ex2(x.y));
+        hw[j][q] = h[q];
+        h[q] = p2fma(a[j][q], h[q], p2mul(dtu, Bp[q]));
+        acc = p2fma(Cp[q], h[q], acc);
+      }
+      yv[j] = acc.x + acc.y;
+    }
+    if (z_row) {
+#pragma unroll
+      for (int j = 0; j < G; ++j) yv[j] = fmaf(dskip, u_c[j], yv[j] + __shfl_xor_sync(0xffffffffu, yv[j], 16));
+    }
+
+    // adjoint, right to left
+    float du_v[G], ddt_v[G], dz_v[G];
+    float* xp = xpose[warp];
+#pragma unroll
+    for (int j = G - 1; j >= 0; --j) {
+      float2 Bp[NQ], Cp[NQ];
+      load_bc_half(steps + j * 2 * N, Bp, Cp);
+      float gy = go_c[j];
+      if (z_row) {
+        const float zv = z_c[j];
+        const float sg = __fdividef(1.0f, 1.0f + ex2(-zv * kLog2e));
+        gy = go_c[j] * zv * sg;
+        dz_v[j] = go_c[j] * yv[j] * (sg * fmaf(zv, 1.0f - sg, 1.0f));
+      }
+      const float2 gy2 = splat(gy), dtv = splat(dt_c[j]), dtu = splat(dt_c[j] * u_c[j]);
+      float2 gb = make_float2(0.f, 0.f), dd = make_float2(0.f, 0.f);
+      float2 dBv[NQ], dCv[NQ];
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        const float2 h_after = (j == G - 1) ? h[q] : hw[(j + 1) % G][q];
+        const float2 g = p2fma(Cp[q], gy2, ag[q]);
+        dCv[q] = p2mul(gy2, h_after);
+        const float2 t1 = p2mul(p2mul(g, hw[j][q]), a[j][q]);   // g * a_t * h_{t-1}
+        dd = p2fma(t1, A2[q], dd);
+        dAacc[q] = p2fma(t1, dtv, dAacc[q]);
+        gb = p2fma(g, Bp[q], gb);
+        dBv[q] = p2mul(g, dtu);
+        ag[q] = p2mul(a[j][q], g);
+      }
+      float sgb = gb.x + gb.y, sdd = (dd.x + dd.y) * kLn2;      // A2 carries log2(e)
+      sgb += __shfl_xor_sync(0xffffffffu, sgb, 16);
+      sdd += __shfl_xor_sync(0xffffffffu, sdd, 16);
+      du_v[j] = fmaf(dt_c[j], sgb, gy * dskip);
+      ddt_v[j] = fmaf(u_c[j], sgb, sdd);
+      dDacc = fmaf(gy, u_c[j], dDacc);
+      // sum dB, dC over the 16 channels of this warp: lane (half, c) ends with value c of its half
+      float4* xo = reinterpret_cast<float4*>(xp + lane * kPad);
+      xo[0] = make_float4(dBv[0].x, dBv[0].y, dBv[1].x, dBv[1].y);
+      xo[1] = make_float4(dBv[2].x, dBv[2].y, dBv[3].x, dBv[3].y);
+      xo[2] = make_float4(dCv[0].x, dCv[0].y, dCv[1].x, dCv[1].y);
+      xo[3] = make_float4(dCv[2].x, dCv[2].y, dCv[3].x, dCv[3].y);
+      __syncwarp();
+      float sum = 0.0f;
+      const float* xi = xp + (half * 16) * kPad + c;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) sum += xi[k * kPad];
+      part[wb][warp][j][lane] = sum;
+      __syncwarp();
+    }
+
+    // per-channel outputs: the low half writes du and dz, the high half ddt
+    if (active) {
+      if (half == 0) {
+        store_items<IO, G>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, du_v);
+        if (z_row) store_items<IO, G>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dz_v);
+      } else {
+        store_items<float, G>(p.ddt + row, t0, p.L, p.vec_ok, ddt_v);
+      }
+    }
+    if (stage_head && s > 0) Loader::finish(raw, tile[tb ^ 1]);
+    __syncthreads();   // partials of this window and (at a stage head) the next tile are visible
+    if (threadIdx.x < 64) {
+      // value id l = (half, c): c < 8 -> dB[half*8 + c], else dC[half*8 + c - 8]; four steps per thread
+      const int l = threadIdx.x & 31, jg = threadIdx.x >> 5;
+      float4 sum4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int wq = 0; wq < kBwdWarps; ++wq) {
+        sum4.x += part[wb][wq][4 * jg][l];
+        sum4.y += part[wb][wq][4 * jg + 1][l];
+        sum4.z += part[wb][wq][4 * jg + 2][l];
+        sum4.w += part[wb][wq][4 * jg + 3][l];
+      }
+      const int lc = l & 15, n = (l >> 4) * NH + (lc & 7);
+      float* dst = ((lc & 8) ? p.dC : p.dB) + (b * N + n) * p.L + t0 + 4 * jg;
+      if (p.vec_ok && t0 + G <= p.L) {
+        red_add_v4(dst, sum4);
+      } else {
+        const float vals[4] = {sum4.x, sum4.y, sum4.z, sum4.w};
+        for (int k = 0; k < 4; ++k)
+          if (t0 + 4 * jg + k < p.L) atomicAdd(dst + k, vals[k]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (active) {
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      const int n = half * NH + 2 * q;
+      p.dA_part[(b * p.D + d) * N + n] = dAacc[q].x;
+      p.dA_part[(b * p.D + d) * N + n + 1] = dAacc[q].y;
+    }
+    if (p.dD_part && half == 0) p.dD_part[b * p.D + d] = dDacc;
+  }
+}
+
 template <typename IO>
 static int launch_fwd_serial(const Params& p, cudaStream_t stream) {
   dim3 grid((unsigned)((p.D + kSerialSpan - 1) / kSerialSpan), (unsigned)p.B);
@@ -300,5 +631,18 @@ static int launch_fwd_serial(const Params& p, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "sscan_forward_serial_kernel launch");
 }
 
+}  // namespace sscan
+}  // namespace ossm_b200
+
+namespace ossm_b200 {
+namespace sscan {
+template <typename IO>
+static int launch_bwd_serial(const Params& p, cudaStream_t stream) {
+  dim3 grid((unsigned)((p.D + kBwdSpan - 1) / kBwdSpan), (unsigned)p.B);
+  const size_t smem = sizeof(BwdSmem<IO, 16>);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sscan_backward_serial_kernel<IO, 16>), smem)) return rc;
+  sscan_backward_serial_kernel<IO, 16><<<grid, kBwdThreads, smem, stream>>>(p);
+  return check_cuda(cudaGetLastError(), "sscan_backward_serial_kernel launch");
+}
 }  // namespace sscan
 }  // namespace ossm_b200

@@ -236,6 +236,12 @@ def linoss_scan_backward(m11: Tensor, m12: Tensor, m21: Tensor, m22: Tensor, sta
 _IO_DTYPES = {torch.float32: 0, torch.bfloat16: 1}
 
 
+def set_selective_scan_tuning(key: str, value: int) -> None:
+    """``"serial"``: 1 (default) = serial-in-time kernels for the state sizes they cover, 0 = the
+    time-parallel kernels for every size.  Forward and backward of one scan must agree."""
+    _lib.check(_lib.load().ossm_b200_selective_scan_set_tuning(key.encode(), int(value)), "selective_scan_set_tuning")
+
+
 def selective_scan_chunk(d_state: int) -> int:
     return int(_lib.load().ossm_b200_selective_scan_chunk(int(d_state)))
 
