@@ -213,11 +213,12 @@ int ossm_b200_sdlinoss_set_tuning(const char* key, int value);
 #define OSSM_B200_DTYPE_F32 0
 #define OSSM_B200_DTYPE_BF16 1
 
-/* Time steps per chunk for a given state size N (256 for N<=16, 128 for N<=32, ...). */
+/* Time steps between the states the forward saves for the backward, for a state size N. */
 int ossm_b200_selective_scan_chunk(int64_t N);
 /* Kernel choice for experiments: key "serial" = 1 (default) runs the serial-in-time kernels for the
- * state sizes they cover, 0 the time-parallel kernels for every size.  Changes the value of
- * ossm_b200_selective_scan_chunk(); forward and backward of one scan must run under the same setting. */
+ * state sizes they cover (d_state 16), 0 the time-parallel kernels for every size; it changes the
+ * value of ossm_b200_selective_scan_chunk(), so forward and backward of one scan must run under the
+ * same setting.  Key "bwd_split" = 2 (default) or 4: lanes per channel in the serial backward. */
 int ossm_b200_selective_scan_set_tuning(const char* key, int value);
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N);

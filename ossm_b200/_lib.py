@@ -10,7 +10,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p, POINTER
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libossm_b200.so")
+LIB_PATH = os.environ.get("OSSM_B200_LIB") or os.path.join(_PKG, "libossm_b200.so")
 
 _lib = None
 

@@ -13,7 +13,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
-LIB = os.path.join(PKG, "libossm_b200.so")
+LIB = os.environ.get("OSSM_B200_LIB") or os.path.join(PKG, "libossm_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -42,6 +42,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found; cannot build libossm_b200.so")
     cmd = [nvcc, *NVCC_FLAGS]
+    cmd += os.environ.get("OSSM_B200_NVCC_FLAGS", "").split()   # extra flags for experiments (e.g. -DNAME)
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", LIB, os.path.join(CSRC, "ossm_b200_all.cu")]
