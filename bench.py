@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--length", type=int, default=4096)
     ap.add_argument("--ssm", type=int, default=256, help="oscillators per GPU")
+    ap.add_argument("--side-length", type=int, default=0,
+                    help="sequence length of the linoss / mamba side workloads (0 = the BASELINE config's own)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -417,7 +419,7 @@ def run_secondary(args):
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(0)
     if args.workload == "linoss":
-        L, B, P = 16384, (args.side_batch or 128), 128
+        L, B, P = (args.side_length or 16384), (args.side_batch or 128), 128
         a = torch.relu(torch.randn(P, generator=gen, device=dev))
         dt = torch.sigmoid(torch.randn(P, generator=gen, device=dev))
         bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev) * 0.5)
@@ -458,7 +460,7 @@ def run_secondary(args):
         def bwd(saved):
             return kernels.sdlinoss_scan_backward("imex1", Af, Gf, dtf, bu, gx, carries=saved[2])
     else:
-        Bz, Dn, L, N = (args.side_batch or 32), 2048, 8192, 16
+        Bz, Dn, L, N = (args.side_batch or 32), 2048, (args.side_length or 8192), 16
         io = torch.bfloat16
         u = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
         z = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
