@@ -206,9 +206,10 @@ int ossm_b200_sdlinoss_set_tuning(const char* key, int value);
  *                             transpose of ossm's [B, L, N] argument)
  *   dB, dC                  : [B, N, L]  float32 (zeroed by the call)
  *   z / dz, Dskip / dD      : optional (NULL): SiLU gate and skip term Dskip[d]*u
- *   chunk_states            : float32 [B, D, ceil(L/chunk), N], the state entering each
- *                             chunk; written by forward (may be NULL when no backward
- *                             will follow), read by backward.
+ *   chunk_states            : float32, B * D * ceil(L/chunk) * N values: the state entering
+ *                             each chunk, in a layout private to the kernel pair; written by
+ *                             forward (may be NULL when no backward will follow), read by
+ *                             backward.
  */
 #define OSSM_B200_DTYPE_F32 0
 #define OSSM_B200_DTYPE_BF16 1

@@ -20,7 +20,8 @@
 // group ahead.
 //
 // The forward also saves the state entering every kSerialInterval-step window
-// (float32 [B, D, ceil(L/interval), N]): the backward recomputes inside a window only.
+// (float32 [B, ceil(L/interval), D, N], channels contiguous so that a warp's states of one
+// window are one 2 KB block): the backward recomputes inside a window only.
 #include "common.cuh"
 
 #include <cuda_bf16.h>
@@ -69,18 +70,20 @@ struct TileLoader {
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
 
-  static __device__ __forceinline__ void finish(const uint4* raw, IO* tile) {
+  // TT: element type of the tile, the I/O type or float (converted here, once per CTA, instead of at every use)
+  template <typename TT>
+  static __device__ __forceinline__ void finish(const uint4* raw, TT* tile) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
     for (int q = 0; q < kPerThread; ++q) {
       const int i = threadIdx.x + q * kThreads;
       if (i >= kItemsTotal) continue;
       const int r = i % (2 * N), c = i / (2 * N);
-      IO* o = tile + (c * kVec) * (2 * N) + r;
+      TT* o = tile + (c * kVec) * (2 * N) + r;
       const uint4 v = raw[i];
       const IO* e = reinterpret_cast<const IO*>(&v);
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) o[j * 2 * N] = e[j];
+      for (int j = 0; j < kVec; ++j) o[j * 2 * N] = static_cast<TT>(e[j]);
     }
   }
 };
@@ -190,9 +193,14 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
   constexpr int CH = kSerialCh;
   using Loader = TileLoader<IO, N, kSerialLanes>;
   using Stream = GroupStream<IO, kSerialLanes>;
-  __shared__ __align__(16) IO tile[2][kStage * 2 * N];
+  __shared__ __align__(16) float tile[2][kStage * 2 * N];   // fp32: no unpacking in the time loop
   __shared__ uint4 raw[Loader::kItemsTotal];
   __shared__ uint4 slab[2 * CH * Stream::kVecs * kSerialLanes];
+  // outputs of one stage, [channel of the CTA][16-byte vector of the stage's steps]: written by the owning lane per
+  // group, stored at the end of the stage with consecutive lanes covering consecutive bytes of a row
+  constexpr int kOutVecs = kStage * (int)sizeof(IO) / 16;   // per channel and stage (4 or 8)
+  static_assert(kOutVecs == 4 || kOutVecs == 8, "swizzle below");
+  __shared__ uint4 ostage[kSerialSpan * kOutVecs];
   const long long b = blockIdx.y;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * N * p.L;
@@ -217,7 +225,8 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
       h[ch][q] = make_float2(0.f, 0.f);
     }
     dskip[ch] = p.Dskip ? __ldg(p.Dskip + d) : 0.0f;
-    cs_out[ch] = (p.chunk_states && active[ch]) ? p.chunk_states + (b * p.D + d) * p.nstates * N : nullptr;
+    // saved states are laid out [B, window, D, N]: the 32 channels of a warp store 2 KB contiguous per window
+    cs_out[ch] = (p.chunk_states && active[ch]) ? p.chunk_states + (b * p.nstates * p.D + d) * N : nullptr;
   }
 
   const long long nstages = (p.L + kStage - 1) / kStage;
@@ -228,6 +237,7 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
 
   for (long long s = 0; s < nstages; ++s) {
     const int buf = (int)(s & 1);
+    const bool staged = p.vec_ok && (s + 1) * kStage <= p.L;   // whole stage inside the sequence, rows 16-byte aligned
 #pragma unroll 1
     for (int g = 0; g < kGroupsPerStage; ++g) {
       const long long t0 = s * kStage + (long long)g * G;
@@ -249,17 +259,17 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
         stream.template read<float>(gb, ch, Stream::kVecIO, dt_c[ch]);
         if (z_all) stream.template read<IO>(gb, ch, Stream::kVecIO + 2, z_c[ch]);
         if (cs_out[ch]) {   // state entering this window
-          float4* o = reinterpret_cast<float4*>(cs_out[ch] + (t0 / G) * N);
+          float4* o = reinterpret_cast<float4*>(cs_out[ch] + (t0 / G) * p.D * N);
 #pragma unroll
           for (int q = 0; q < NP / 2; ++q)
             o[q] = make_float4(h[ch][2 * q].x, h[ch][2 * q].y, h[ch][2 * q + 1].x, h[ch][2 * q + 1].y);
         }
       }
-      const IO* steps = tile[buf] + g * G * 2 * N;
+      const float* steps = tile[buf] + g * G * 2 * N;
 #pragma unroll
       for (int j = 0; j < G; ++j) {
         float2 Bp[NP], Cp[NP];
-        load_bc_step<IO, N>(steps + j * 2 * N, Bp, Cp);
+        load_bc_step<float, N>(steps + j * 2 * N, Bp, Cp);
 #pragma unroll
         for (int ch = 0; ch < CH; ++ch) {
           const float2 dtv = splat(dt_c[ch][j]);
@@ -283,9 +293,50 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
           y[ch][j] = yv;
         }
       }
+      if (staged) {
+        constexpr int kV = Stream::kVecIO;   // vectors per group
 #pragma unroll
-      for (int ch = 0; ch < CH; ++ch)
-        if (active[ch]) store_items<IO, G>(static_cast<IO*>(p.out) + off[ch], t0, p.L, p.vec_ok, y[ch]);
+        for (int ch = 0; ch < CH; ++ch) {
+          // vector v of channel chn sits at chn * kOutVecs + (v ^ swizzle(chn)): 8 lanes hit 8 different bank groups
+          const int chn = ch * kSerialLanes + threadIdx.x;
+          const int sw = kOutVecs == 4 ? ((chn >> 1) & 3) : (chn & 7);
+          uint4* ob = ostage + chn * kOutVecs;
+          if constexpr (sizeof(IO) == 4) {
+            ob[(g * kV) ^ sw] = make_uint4(__float_as_uint(y[ch][0]), __float_as_uint(y[ch][1]),
+                                           __float_as_uint(y[ch][2]), __float_as_uint(y[ch][3]));
+            ob[(g * kV + 1) ^ sw] = make_uint4(__float_as_uint(y[ch][4]), __float_as_uint(y[ch][5]),
+                                               __float_as_uint(y[ch][6]), __float_as_uint(y[ch][7]));
+          } else {
+            uint32_t wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __nv_bfloat162 hv = __floats2bfloat162_rn(y[ch][2 * i], y[ch][2 * i + 1]);
+              wv[i] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            ob[(g * kV) ^ sw] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch)
+          if (active[ch]) store_items<IO, G>(static_cast<IO*>(p.out) + off[ch], t0, p.L, p.vec_ok, y[ch]);
+      }
+    }
+    if (staged) {
+      __syncwarp();
+      // kOutVecs consecutive lanes write one channel's stage (kStage elements, contiguous in memory)
+#pragma unroll
+      for (int it = 0; it < kSerialSpan * kOutVecs / kSerialLanes; ++it) {
+        const int i = it * kSerialLanes + threadIdx.x;
+        const int chn = i / kOutVecs, v = i % kOutVecs;
+        const long long dd = (long long)blockIdx.x * kSerialSpan + chn;
+        if (dd < p.D) {
+          IO* dst = static_cast<IO*>(p.out) + (b * p.D + dd) * p.L + s * kStage;
+          const int sw = kOutVecs == 4 ? ((chn >> 1) & 3) : (chn & 7);
+          reinterpret_cast<uint4*>(dst)[v] = ostage[chn * kOutVecs + (v ^ sw)];
+        }
+      }
+      __syncwarp();
     }
     if (s + 1 < nstages) Loader::finish(raw, tile[buf ^ 1]);
     __syncwarp();
@@ -371,7 +422,7 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
   const IO* go_row = static_cast<const IO*>(p.dout) + row;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * N * p.L;
-  const float* snaps = p.chunk_states + (b * p.D + d) * p.nstates * N + grp * NH;
+  const float* snaps = p.chunk_states + (b * p.nstates * p.D + d) * N + grp * NH;   // [B, window, D, N]
 
   float2 A2[NQ], ag[NQ], dAacc[NQ];
 #pragma unroll
@@ -417,7 +468,7 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
         if (z_row) issue_vecs(base + (kVecIO + 2) * CW, z_row, (int)sizeof(IO), t0, kVecIO);
         issue_vecs(base + (2 * kVecIO + 2) * CW, go_row, (int)sizeof(IO), t0, kVecIO);
       }
-      const float* sp = snaps + w * N;
+      const float* sp = snaps + w * p.D * N;
 #pragma unroll
       for (int v = 0; v < Smem::kSnapVecs; ++v)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&snap[buf][warp][v][lane])),
@@ -608,7 +659,8 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
       __syncwarp();
     }
 
-    // per-channel outputs, spread over the lanes of the channel: du | ddt | dz
+    // per-channel outputs, spread over the lanes of the channel: du | ddt | dz.  (Staging them in shared memory
+    // for row-contiguous stores, as the forward does with its output, cost more in barriers than it saved.)
     if (active) {
       if (grp == 0) store_items<IO, G>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, du_v);
       if (grp == 1) store_items<float, G>(p.ddt + row, t0, p.L, p.vec_ok, ddt_v);
