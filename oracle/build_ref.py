@@ -80,7 +80,9 @@ def build(reference: str, verbose: bool = False) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("OSSM_REFERENCE", "/root/reference"))
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ap.add_argument("--reference", default=os.environ.get("OSSM_REFERENCE") or os.path.join(os.path.dirname(here), "reference"),
+                    help="ossm checkout (default: $OSSM_REFERENCE, else a directory 'reference' beside this repository)")
     ap.add_argument("-v", "--verbose", action="store_true")
     args = ap.parse_args()
     print(build(args.reference, args.verbose))

@@ -56,7 +56,8 @@ def stable_params(P, gen):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("OSSM_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("OSSM_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="ossm checkout (default: $OSSM_REFERENCE, else a directory 'reference' beside this repository)")
     args = ap.parse_args()
     ref = args.reference
 
