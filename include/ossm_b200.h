@@ -224,16 +224,24 @@ int ossm_b200_selective_scan_set_tuning(const char* key, int value);
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 
+/* delta_bias (float32 [D], may be NULL) and delta_softplus (0 / 1) fold the step-size transform of the
+ * Mamba mixer into the scan: the kernels use dt = raw + delta_bias[d], passed through softplus when
+ * delta_softplus is set (identity above 20) -- the switches of the vendored kernel
+ * (csrc/mamba/selective_scan_fwd_kernel.cuh:123-161) that ossm's wrapper leaves off
+ * (selective_scan_cuda.cu:133-140) while the mixer applies F.softplus(dt_proj(.)) as a separate pass
+ * (mambarec.py:155).  With either of them `ddt` is the gradient of the raw step, and ddelta_bias
+ * (float32 [D], required when delta_bias is given) receives the gradient of the bias. */
 int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float* A, const void* Bm, const void* Cm,
-                                     const void* z, const float* Dskip, void* out, float* chunk_states, int64_t B,
-                                     int64_t D, int64_t L, int64_t N, int io_dtype, ossm_b200_stream_t stream);
+                                     const void* z, const float* Dskip, const float* delta_bias, int delta_softplus,
+                                     void* out, float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
+                                     int io_dtype, ossm_b200_stream_t stream);
 
 int ossm_b200_selective_scan_backward(const void* u, const float* dt, const float* A, const void* Bm,
-                                      const void* Cm, const void* z, const float* Dskip, const void* dout,
-                                      const float* chunk_states, void* du, float* ddt, float* dA, float* dB,
-                                      float* dC, void* dz, float* dD, void* workspace, size_t workspace_bytes,
-                                      int64_t B, int64_t D, int64_t L, int64_t N, int io_dtype,
-                                      ossm_b200_stream_t stream);
+                                      const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
+                                      int delta_softplus, const void* dout, const float* chunk_states, void* du,
+                                      float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
+                                      float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
+                                      int64_t D, int64_t L, int64_t N, int io_dtype, ossm_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -303,14 +303,36 @@ def _sigmoid(x):
     return 1.0 / (1.0 + np.exp(-x))
 
 
-def selective_scan(u, dt, A, Bm, Cm, gate=None, D=None, return_states=False):
+def delta_transform(dt_raw, delta_bias=None, delta_softplus=False):
+    """The step size the scan uses: ``dt_raw + delta_bias[d]`` passed through softplus when asked
+    (identity above 20), the ``delta_bias`` / ``delta_softplus`` switches of the vendored Mamba kernel
+    (``src/ossm/csrc/mamba/selective_scan_fwd_kernel.cuh:123-161``; ossm's wrapper leaves them off and
+    applies ``F.softplus(dt_proj(.))`` in the mixer, ``mambarec.py:155``)."""
+    x = dt_raw if delta_bias is None else dt_raw + delta_bias[None, :, None]
+    if delta_softplus:
+        x = np.where(x <= 20.0, np.log1p(np.exp(np.minimum(x, 20.0))), x)
+    return x
+
+
+def delta_transform_backward(ddt, dt_raw, delta_bias=None, delta_softplus=False):
+    """``(d dt_raw, d delta_bias or None)`` from the gradient with respect to the transformed step."""
+    x = dt_raw if delta_bias is None else dt_raw + delta_bias[None, :, None]
+    g = ddt * np.where(x <= 20.0, _sigmoid(x), 1.0) if delta_softplus else ddt
+    return g, (None if delta_bias is None else g.sum(axis=(0, 2)))
+
+
+def selective_scan(u, dt, A, Bm, Cm, gate=None, D=None, return_states=False, delta_bias=None,
+                   delta_softplus=False):
     """Fused selective scan: ``h = exp(dt*A) h + dt*B*u ; y = <C,h> (+ D*u) ; out = y*silu(gate)``.
 
     Shapes: ``u, dt, gate [B,D,L]``; ``A [D,N]``; ``Bm, Cm [B,L,N]``; ``D [D]``.
     Restates ``src/ossm/csrc/selective_scan_cpu.cpp:78-166`` (ossm itself
     passes no ``D``; the skip term follows the Mamba convention and is added
-    before the gate).
+    before the gate).  With ``delta_bias`` / ``delta_softplus`` the given ``dt`` is the raw
+    step, see :func:`delta_transform`.
     """
+    if delta_bias is not None or delta_softplus:
+        dt = delta_transform(dt, delta_bias, delta_softplus)
     Bsz, Dn, L = u.shape
     N = A.shape[1]
     h = np.zeros((Bsz, Dn, N), dtype=u.dtype)
@@ -330,13 +352,19 @@ def selective_scan(u, dt, A, Bm, Cm, gate=None, D=None, return_states=False):
     return out
 
 
-def selective_scan_backward(grad_out, u, dt, A, Bm, Cm, gate=None, D=None):
+def selective_scan_backward(grad_out, u, dt, A, Bm, Cm, gate=None, D=None, delta_bias=None, delta_softplus=False):
     """Gradients ``(du, ddt, dA, dB, dC, dgate, dD)`` of :func:`selective_scan`.
 
     Restates ``src/ossm/csrc/selective_scan_cpu.cpp:168-360`` (recompute all
     states, then the reverse loop of lines 287-351).  ``dgate``/``dD`` are
-    ``None`` when the corresponding input is ``None``.
+    ``None`` when the corresponding input is ``None``.  With ``delta_bias`` / ``delta_softplus``
+    ``ddt`` is the gradient of the raw step and the gradient of ``delta_bias`` (or ``None``) is
+    appended as an eighth entry.
     """
+    if delta_bias is not None or delta_softplus:
+        res = selective_scan_backward(grad_out, u, delta_transform(dt, delta_bias, delta_softplus), A, Bm, Cm, gate, D)
+        g_raw, g_bias = delta_transform_backward(res[1], dt, delta_bias, delta_softplus)
+        return (res[0], g_raw) + tuple(res[2:]) + (g_bias,)
     Bsz, Dn, L = u.shape
     _, y, hs = selective_scan(u, dt, A, Bm, Cm, gate=None, D=D, return_states=True)
     if gate is not None:

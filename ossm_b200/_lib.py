@@ -40,8 +40,10 @@ SIGNATURES = {
     "ossm_b200_selective_scan_chunk": (c_int, [c_int64]),
     "ossm_b200_selective_scan_state_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
     "ossm_b200_selective_scan_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
-    "ossm_b200_selective_scan_forward": (c_int, [c_void_p] * 9 + [c_int64] * 4 + [c_int, c_void_p]),
-    "ossm_b200_selective_scan_backward": (c_int, [c_void_p] * 17 + [c_size_t] + [c_int64] * 4 + [c_int, c_void_p]),
+    "ossm_b200_selective_scan_forward": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 2 + [c_int64] * 4
+                                         + [c_int, c_void_p]),
+    "ossm_b200_selective_scan_backward": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 11 + [c_size_t]
+                                          + [c_int64] * 4 + [c_int, c_void_p]),
     "ossm_b200_linoss_scan_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_linoss_scan_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

@@ -50,6 +50,29 @@ __device__ __forceinline__ float ex2(float x) {
 
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + ex2(-x * kLog2e)); }
 
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Step size used by the scan from the raw one: raw + bias, through softplus when asked (identity above
+// 20, as in the vendored Mamba kernel, selective_scan_fwd_kernel.cuh:123-161).  Small arguments use
+// log1p(e) = e - e^2/2 so that tiny steps keep their relative accuracy.
+__device__ __forceinline__ float step_transform(float raw, float bias, bool softplus) {
+  float x = raw + bias;
+  if (softplus && x <= 20.0f) {
+    const float e = ex2(x * kLog2e);
+    x = e < 1e-4f ? e * fmaf(-0.5f, e, 1.0f) : 0.6931471805599453f * lg2(1.0f + e);
+  }
+  return x;
+}
+// d(step)/d(raw) expressed through the transformed step: sigmoid(x) = 1 - exp(-softplus(x)).
+__device__ __forceinline__ float step_transform_grad(float dt, bool softplus) {
+  if (!softplus) return 1.0f;
+  return dt < 1e-3f ? dt * fmaf(-0.5f, dt, 1.0f) : 1.0f - ex2(-dt * kLog2e);
+}
+
 
 // Pair arithmetic on (state 2p, state 2p+1): packed f32x2 instructions (measured 13 %
 // faster in the backward than the scalar forms, which remain selectable for comparison).
@@ -307,6 +330,9 @@ struct Params {
   float* dC;
   float* dA_part;  // [B, D, N]
   float* dD_part;  // [B, D] (nullable)
+  const float* delta_bias;  // [D] (nullable): dt = raw + delta_bias[d]
+  int delta_softplus;       // dt = softplus(raw + bias)
+  float* dbias_part;        // [B, D] (nullable), backward only
   long long B, D, L, N;
   long long nstates;   // saved states per lane = ceil(L / state_interval)
   int state_interval;  // steps between saved states (= the backward's chunk)
@@ -358,6 +384,11 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
       float2 y2[kItems], dtu2[kItems];
       load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, p.L, p.vec_ok, u);
       load_items<float, kItems>(p.dt + row, t0, p.L, p.vec_ok, dt);
+      if (p.delta_bias || p.delta_softplus) {   // steps past the end of the sequence stay zero (no-ops)
+        const float bias = p.delta_bias ? __ldg(p.delta_bias + d) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < kItems; ++j) dt[j] = (t0 + j < p.L) ? step_transform(dt[j], bias, p.delta_softplus != 0) : 0.0f;
+      }
 #pragma unroll
       for (int j = 0; j < kItems; ++j) { dtu2[j] = splat(dt[j] * u[j]); y2[j] = make_float2(0.f, 0.f); }
       float2* cw = carry + (warp * kCI + ci) * NP;
@@ -418,7 +449,7 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
 
 // Shared memory (floats), NP = ceil(N/2), tile = NP*T*2:
 //   Bs | Cs (one tile each) | acc[kWarps][2 (dB,dC)][tile] | lam[kWarps*kCI*NP*2] | dAacc[kWarps*kCI*NP*2]
-//   | dDacc[kWarps*kCI]
+//   | dDacc[kWarps*kCI] | dBiasacc[kWarps*kCI]
 // Every warp owns a private dB/dC accumulator tile, so the warps of a CTA run
 // independently between the three barriers of a chunk (tile staging, flush).
 template <typename IO, int kItems>
@@ -434,6 +465,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   float2* lam = reinterpret_cast<float2*>(acc + kWarps * 2 * tile);   // adjoint carried from the later chunk
   float2* dAacc = lam + kWarps * kCI * NP;
   float* dDacc = reinterpret_cast<float*>(dAacc + kWarps * kCI * NP);
+  float* dBiasacc = dDacc + kWarps * kCI;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
   const long long d0 = (long long)blockIdx.x * (kWarps * p.cpw) + warp * p.cpw;
@@ -447,7 +479,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
     lam[i] = make_float2(0.f, 0.f);
     dAacc[i] = make_float2(0.f, 0.f);
   }
-  for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) dDacc[i] = 0.0f;
+  for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) { dDacc[i] = 0.0f; dBiasacc[i] = 0.0f; }
 
   for (long long c = nchunks - 1; c >= 0; --c) {
     const long long t_base = c * T;
@@ -467,6 +499,11 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
       const long long tl = ok ? p.L : 0;
       load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, tl, p.vec_ok, fu);
       load_items<float, kItems>(p.dt + row, t0, tl, p.vec_ok, fdt);
+      if (p.delta_bias || p.delta_softplus) {
+        const float bias = (ok && p.delta_bias) ? __ldg(p.delta_bias + d) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < kItems; ++j) fdt[j] = (t0 + j < tl) ? step_transform(fdt[j], bias, p.delta_softplus != 0) : 0.0f;
+      }
       load_items<IO, kItems>(static_cast<const IO*>(p.dout) + row, t0, tl, p.vec_ok, fgo);
       if (p.z) load_items<IO, kItems>(static_cast<const IO*>(p.z) + row, t0, tl, p.vec_ok, fz);
     };
@@ -567,6 +604,14 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
         ddv[j] = fmaf(u[j], gb, ddts2[j].x + ddts2[j].y);
         dD_t = fmaf(gy[j], u[j], dD_t);
       }
+      float dbias_t = 0.0f;
+      if (p.delta_bias || p.delta_softplus) {   // gradient with respect to the raw step
+#pragma unroll
+        for (int j = 0; j < kItems; ++j) {
+          ddv[j] = (t0 + j < p.L) ? ddv[j] * step_transform_grad(dt[j], p.delta_softplus != 0) : 0.0f;
+          dbias_t += ddv[j];
+        }
+      }
       store_items<IO, kItems>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, duv);
       store_items<float, kItems>(p.ddt + row, t0, p.L, p.vec_ok, ddv);
       if (p.z) {
@@ -583,6 +628,11 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dD_t += __shfl_xor_sync(0xffffffffu, dD_t, off);
         if (lane == 0) dDacc[warp * kCI + ci] += dD_t;
+      }
+      if (p.dbias_part) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dbias_t += __shfl_xor_sync(0xffffffffu, dbias_t, off);
+        if (lane == 0) dBiasacc[warp * kCI + ci] += dbias_t;
       }
 #pragma unroll
       for (int j = 0; j < kItems; ++j) { u[j] = nu[j]; dt[j] = ndt[j]; go[j] = ngo[j]; zz[j] = nz[j]; }
@@ -621,6 +671,13 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
       const int w = i / kCI, ci = i - w * kCI;
       const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
       if (ci < p.cpw && d < p.D) p.dD_part[b * p.D + d] = dDacc[i];
+    }
+  }
+  if (p.dbias_part) {
+    for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) {
+      const int w = i / kCI, ci = i - w * kCI;
+      const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
+      if (ci < p.cpw && d < p.D) p.dbias_part[b * p.D + d] = dBiasacc[i];
     }
   }
 }
@@ -673,7 +730,7 @@ static int launch_bwd(const Params& p, cudaStream_t stream) {
   const int T = 32 * kItems;
   const size_t np2 = 2 * (size_t)((p.N + 1) / 2);
   const size_t smem = sizeof(float) * ((2 + 2 * (size_t)kWarps) * np2 * T + 2 * (size_t)kWarps * kCI * np2 +
-                                       kWarps * kCI);
+                                       2 * kWarps * kCI);
   if (smem > 220 * 1024) { set_last_error("selective_scan_backward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_backward_kernel<IO, kItems>, smem)) return rc;
   dim3 grid((unsigned)((p.D + kWarps * p.cpw - 1) / (kWarps * p.cpw)), (unsigned)p.B);
@@ -745,7 +802,7 @@ size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int
 
 size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N) {
   if (B <= 0 || D <= 0 || L <= 0 || N <= 0) return 0;
-  return (size_t)B * D * (N + 1) * sizeof(float);
+  return (size_t)B * D * (N + 2) * sizeof(float);   // batch partials of dA, dD and d(delta_bias)
 }
 
 static int sscan_check(const char* fn, const void* u, const float* dt, const float* A, const void* Bm,
@@ -763,8 +820,9 @@ static int sscan_check(const char* fn, const void* u, const float* dt, const flo
 }
 
 int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float* A, const void* Bm, const void* Cm,
-                                     const void* z, const float* Dskip, void* out, float* chunk_states, int64_t B,
-                                     int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
+                                     const void* z, const float* Dskip, const float* delta_bias, int delta_softplus,
+                                     void* out, float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
+                                     int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_forward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
   if (B == 0 || D == 0 || L == 0) return kOk;
   if (!out) { set_last_error("selective_scan_forward: null out"); return kErrInvalidArgument; }
@@ -774,6 +832,7 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
   }
   sscan::Params p{};
   p.u = u; p.dt = dt; p.A = A; p.Bm = Bm; p.Cm = Cm; p.z = z; p.Dskip = Dskip; p.out = out;
+  p.delta_bias = delta_bias; p.delta_softplus = delta_softplus != 0;
   p.chunk_states = chunk_states;
   p.B = B; p.D = D; p.L = L; p.N = N;
   p.state_interval = sscan::state_interval_for(N);
@@ -793,19 +852,23 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
 }
 
 int ossm_b200_selective_scan_backward(const void* u, const float* dt, const float* A, const void* Bm,
-                                      const void* Cm, const void* z, const float* Dskip, const void* dout,
-                                      const float* chunk_states, void* du, float* ddt, float* dA, float* dB,
-                                      float* dC, void* dz, float* dD, void* workspace, size_t workspace_bytes,
-                                      int64_t B, int64_t D, int64_t L, int64_t N, int io_dtype,
-                                      cudaStream_t stream) {
+                                      const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
+                                      int delta_softplus, const void* dout, const float* chunk_states, void* du,
+                                      float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
+                                      float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
+                                      int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_backward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
   if (D == 0 || N == 0) return kOk;
   if (!dA) { set_last_error("selective_scan_backward: null dA"); return kErrInvalidArgument; }
   if (int rc = check_cuda(cudaMemsetAsync(dA, 0, (size_t)D * N * sizeof(float), stream), "memset dA")) return rc;
   if (dD) if (int rc = check_cuda(cudaMemsetAsync(dD, 0, (size_t)D * sizeof(float), stream), "memset dD")) return rc;
+  if (ddelta_bias)
+    if (int rc = check_cuda(cudaMemsetAsync(ddelta_bias, 0, (size_t)D * sizeof(float), stream), "memset ddelta_bias"))
+      return rc;
   if (B == 0 || L == 0) return kOk;
-  if (!dout || !chunk_states || !du || !ddt || !dB || !dC || (z && !dz) || (Dskip && !dD)) {
-    set_last_error("selective_scan_backward: null pointer among dout/chunk_states/du/ddt/dB/dC/dz/dD");
+  if (!dout || !chunk_states || !du || !ddt || !dB || !dC || (z && !dz) || (Dskip && !dD) ||
+      (delta_bias && !ddelta_bias)) {
+    set_last_error("selective_scan_backward: null pointer among dout/chunk_states/du/ddt/dB/dC/dz/dD/ddelta_bias");
     return kErrInvalidArgument;
   }
   if (!workspace || workspace_bytes < ossm_b200_selective_scan_backward_workspace_bytes(B, D, L, N)) {
@@ -821,6 +884,8 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.dout = dout; p.du = du; p.ddt = ddt; p.dz = dz; p.dB = dB; p.dC = dC;
   p.dA_part = static_cast<float*>(workspace);
   p.dD_part = Dskip ? p.dA_part + (size_t)B * D * N : nullptr;
+  p.dbias_part = delta_bias ? p.dA_part + (size_t)B * D * (N + 1) : nullptr;
+  p.delta_bias = delta_bias; p.delta_softplus = delta_softplus != 0;
   p.B = B; p.D = D; p.L = L; p.N = N;
   p.state_interval = sscan::state_interval_for(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
@@ -846,6 +911,10 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   if (int rc2 = check_cuda(cudaGetLastError(), "sscan_reduce_batch_kernel launch")) return rc2;
   if (p.dD_part) {
     sscan::sscan_reduce_batch_kernel<<<(unsigned)((D + 255) / 256), 256, 0, stream>>>(p.dD_part, dD, B, D);
+    if (int rc2 = check_cuda(cudaGetLastError(), "sscan_reduce_batch_kernel launch")) return rc2;
+  }
+  if (p.dbias_part) {
+    sscan::sscan_reduce_batch_kernel<<<(unsigned)((D + 255) / 256), 256, 0, stream>>>(p.dbias_part, ddelta_bias, B, D);
     if (int rc2 = check_cuda(cudaGetLastError(), "sscan_reduce_batch_kernel launch")) return rc2;
   }
   return kOk;

@@ -185,7 +185,9 @@ struct GroupStream {
   }
 };
 
-template <typename IO, int N>
+// kStep: the given dt is a raw step to be biased / passed through softplus (a template parameter so that the
+// plain case keeps its register allocation)
+template <typename IO, int N, bool kStep>
 __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Params p) {
   constexpr int NP = N / 2;
   constexpr int G = kSerialInterval;
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
   long long dch[CH], off[CH];
   bool active[CH];
   float2 A2[CH][NP], h[CH][NP];
-  float dskip[CH];
+  float dskip[CH], dbias[CH];
   float* cs_out[CH];
 #pragma unroll
   for (int ch = 0; ch < CH; ++ch) {
@@ -225,6 +227,7 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
       h[ch][q] = make_float2(0.f, 0.f);
     }
     dskip[ch] = p.Dskip ? __ldg(p.Dskip + d) : 0.0f;
+    dbias[ch] = (kStep && p.delta_bias) ? __ldg(p.delta_bias + d) : 0.0f;
     // saved states are laid out [B, window, D, N]: the 32 channels of a warp store 2 KB contiguous per window
     cs_out[ch] = (p.chunk_states && active[ch]) ? p.chunk_states + (b * p.nstates * p.D + d) * N : nullptr;
   }
@@ -257,6 +260,11 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
       for (int ch = 0; ch < CH; ++ch) {
         stream.template read<IO>(gb, ch, 0, u_c[ch]);
         stream.template read<float>(gb, ch, Stream::kVecIO, dt_c[ch]);
+        if constexpr (kStep) {   // steps past the end of the sequence stay zero (no-ops)
+#pragma unroll
+          for (int j = 0; j < G; ++j)
+            dt_c[ch][j] = (t0 + j < p.L) ? step_transform(dt_c[ch][j], dbias[ch], p.delta_softplus != 0) : 0.0f;
+        }
         if (z_all) stream.template read<IO>(gb, ch, Stream::kVecIO + 2, z_c[ch]);
         if (cs_out[ch]) {   // state entering this window
           float4* o = reinterpret_cast<float4*>(cs_out[ch] + (t0 / G) * p.D * N);
@@ -387,7 +395,7 @@ struct BwdSmem {
   float part[2][kBwdWarps][G][32];                     // per-warp channel sums of dB / dC of a window
 };
 
-template <typename IO, int N, int kSplit>
+template <typename IO, int N, int kSplit, bool kStep>
 __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backward_serial_kernel(Params p) {
   using Smem = BwdSmem<IO, N, kSplit>;
   constexpr int G = kSerialInterval;
@@ -433,7 +441,9 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
     dAacc[q] = make_float2(0.f, 0.f);
   }
   const float dskip = p.Dskip ? __ldg(p.Dskip + d) : 0.0f;
-  float dDacc = 0.0f;
+  const float dbias = (kStep && p.delta_bias) ? __ldg(p.delta_bias + d) : 0.0f;
+  constexpr bool raw_step = kStep;   // the given dt is a raw step to be biased / passed through softplus
+  float dDacc = 0.0f, dBiasAcc = 0.0f;
 
   const long long nwin = (p.L + G - 1) / G;
   const long long nstages = (p.L + kStage - 1) / kStage;
@@ -563,6 +573,10 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
       const uint4* base = &slab[wb][warp][0][c];
       read_vecs(base, (int)sizeof(IO), u_c);
       read_vecs(base + kVecIO * CW, 4, dt_c);
+      if constexpr (raw_step) {   // steps past the end of the sequence stay zero (no-ops)
+#pragma unroll
+        for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
+      }
       if (z_row) read_vecs(base + (kVecIO + 2) * CW, (int)sizeof(IO), z_c);
       read_vecs(base + (2 * kVecIO + 2) * CW, (int)sizeof(IO), go_c);
       if (!active) {   // a shadow lane must not add to the sums over channels
@@ -637,6 +651,10 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
       const float sdd = channel_sum((dd.x + dd.y) * kLn2);      // A2 carries log2(e)
       du_v[j] = fmaf(dt_c[j], sgb, gy * dskip);
       ddt_v[j] = fmaf(u_c[j], sgb, sdd);
+      if constexpr (raw_step) {   // gradient with respect to the raw step
+        ddt_v[j] = (t0 + j < p.L) ? ddt_v[j] * step_transform_grad(dt_c[j], p.delta_softplus != 0) : 0.0f;
+        dBiasAcc += ddt_v[j];
+      }
       dDacc = fmaf(gy, u_c[j], dDacc);
       // sum dB, dC over the CW channels of this warp: lane (grp, c) ends with value c of its group
       float2* xo = reinterpret_cast<float2*>(xp + lane * kPad + grp * CW);
@@ -700,13 +718,15 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
       p.dA_part[(b * p.D + d) * N + n + 1] = dAacc[q].y;
     }
     if (p.dD_part && grp == 0) p.dD_part[b * p.D + d] = dDacc;
+    if (p.dbias_part && grp == 0) p.dbias_part[b * p.D + d] = dBiasAcc;
   }
 }
 
 template <typename IO>
 static int launch_fwd_serial(const Params& p, cudaStream_t stream) {
   dim3 grid((unsigned)((p.D + kSerialSpan - 1) / kSerialSpan), (unsigned)p.B);
-  sscan_forward_serial_kernel<IO, 16><<<grid, kSerialLanes, 0, stream>>>(p);
+  if (p.delta_bias || p.delta_softplus) sscan_forward_serial_kernel<IO, 16, true><<<grid, kSerialLanes, 0, stream>>>(p);
+  else sscan_forward_serial_kernel<IO, 16, false><<<grid, kSerialLanes, 0, stream>>>(p);
   return check_cuda(cudaGetLastError(), "sscan_forward_serial_kernel launch");
 }
 
@@ -722,7 +742,8 @@ static int launch_bwd_serial_split(const Params& p, cudaStream_t stream) {
   constexpr int kSpan = kBwdWarps * (32 / kSplit);
   dim3 grid((unsigned)((p.D + kSpan - 1) / kSpan), (unsigned)p.B);
   const size_t smem = sizeof(BwdSmem<IO, 16, kSplit>);
-  auto kernel = sscan_backward_serial_kernel<IO, 16, kSplit>;
+  auto kernel = (p.delta_bias || p.delta_softplus) ? sscan_backward_serial_kernel<IO, 16, kSplit, true>
+                                                   : sscan_backward_serial_kernel<IO, 16, kSplit, false>;
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   kernel<<<grid, kBwdThreads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "sscan_backward_serial_kernel launch");

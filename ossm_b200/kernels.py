@@ -278,10 +278,20 @@ def _check_selective(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor
             raise RuntimeError("ossm_b200: all selective-scan operands must be on one device")
 
 
+def _delta_bias(delta_bias: Optional[Tensor], ch: int, dev) -> Optional[Tensor]:
+    if delta_bias is None:
+        return None
+    if delta_bias.dim() != 1 or delta_bias.size(0) != ch or delta_bias.device != dev:
+        raise RuntimeError("delta_bias must have shape (channels,) on the device of inputs")
+    return delta_bias.float().contiguous()
+
+
 def selective_scan_fwd(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor] = None,
-                       D: Optional[Tensor] = None, save_states: bool = True) -> Tuple[Tensor, Optional[Tensor]]:
+                       D: Optional[Tensor] = None, save_states: bool = True, delta_bias: Optional[Tensor] = None,
+                       delta_softplus: bool = False) -> Tuple[Tensor, Optional[Tensor]]:
     """Fused selective scan; returns ``(out [B,D,L], chunk_states or None)``.
-    ``inputs/gate/B/C`` float32 or bfloat16, ``dt``/``A``/``D`` float32 (cast if not)."""
+    ``inputs/gate/B/C`` float32 or bfloat16, ``dt``/``A``/``D`` float32 (cast if not).  With
+    ``delta_bias [D]`` / ``delta_softplus`` the kernel uses ``softplus(dt + delta_bias[d])`` as the step."""
     _check_selective(inputs, dt, A, B, C, gate)
     bsz, ch, length = inputs.shape
     n = A.size(1)
@@ -302,17 +312,21 @@ def selective_scan_fwd(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tens
     Bt, Ct = _time_major_bc(B), _time_major_bc(C)
     zc = gate.contiguous() if gate is not None else None
     Dc = D.float().contiguous() if D is not None else None
+    bias = _delta_bias(delta_bias, ch, dev)
     with torch.cuda.device(dev):
-        rc = lib.ossm_b200_selective_scan_forward(_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(out),
-                                                  _p(states), bsz, ch, length, n, _IO_DTYPES[inputs.dtype],
-                                                  _stream(dev))
+        rc = lib.ossm_b200_selective_scan_forward(_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias),
+                                                  int(bool(delta_softplus)), _p(out), _p(states), bsz, ch, length, n,
+                                                  _IO_DTYPES[inputs.dtype], _stream(dev))
     _lib.check(rc, "selective_scan_forward")
     return out, states
 
 
 def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor,
-                       gate: Optional[Tensor], chunk_states: Tensor, D: Optional[Tensor] = None):
-    """Gradients ``(du, ddt, dA, dB, dC, dgate, dD)`` (``dgate``/``dD`` ``None`` when absent)."""
+                       gate: Optional[Tensor], chunk_states: Tensor, D: Optional[Tensor] = None,
+                       delta_bias: Optional[Tensor] = None, delta_softplus: bool = False):
+    """Gradients ``(du, ddt, dA, dB, dC, dgate, dD)`` (``dgate``/``dD`` ``None`` when absent).  With
+    ``delta_bias`` / ``delta_softplus`` (as given to the forward) ``ddt`` is the gradient of the raw
+    step and the gradient of ``delta_bias`` (``None`` without a bias) is appended as an eighth entry."""
     _check_selective(inputs, dt, A, B, C, gate)
     if grad_output.shape != inputs.shape:
         raise RuntimeError("grad_output must match the shape of inputs")
@@ -326,8 +340,10 @@ def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tenso
     dCt = torch.empty((bsz, n, length), dtype=torch.float32, device=dev)
     dz = torch.empty_like(du) if gate is not None else None
     dD = torch.empty(ch, dtype=torch.float32, device=dev) if D is not None else None
+    bias = _delta_bias(delta_bias, ch, dev)
+    dbias = torch.empty(ch, dtype=torch.float32, device=dev) if bias is not None else None
     if inputs.numel() == 0 or n == 0:
-        for t in (dA, dBt, dCt, dD):
+        for t in (dA, dBt, dCt, dD, dbias):
             if t is not None:
                 t.zero_()
     else:
@@ -347,13 +363,16 @@ def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tenso
             raise RuntimeError("ossm_b200: chunk_states do not belong to these inputs")
         with torch.cuda.device(dev):
             rc = lib.ossm_b200_selective_scan_backward(
-                _p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(go), _p(chunk_states), _p(du), _p(ddt),
-                _p(dA), _p(dBt), _p(dCt), _p(dz), _p(dD), _p(workspace), ws_bytes, bsz, ch, length, n,
-                _IO_DTYPES[inputs.dtype], _stream(dev))
+                _p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias), int(bool(delta_softplus)), _p(go),
+                _p(chunk_states), _p(du), _p(ddt), _p(dA), _p(dBt), _p(dCt), _p(dz), _p(dD), _p(dbias),
+                _p(workspace), ws_bytes, bsz, ch, length, n, _IO_DTYPES[inputs.dtype], _stream(dev))
         _lib.check(rc, "selective_scan_backward")
     dB = dBt.transpose(1, 2).to(B.dtype)
     dC = dCt.transpose(1, 2).to(C.dtype)
-    return du, ddt.to(dt.dtype), dA.to(A.dtype), dB, dC, dz, (dD.to(D.dtype) if dD is not None else None)
+    res = (du, ddt.to(dt.dtype), dA.to(A.dtype), dB, dC, dz, (dD.to(D.dtype) if dD is not None else None))
+    if delta_bias is not None or delta_softplus:
+        res = res + ((dbias.to(delta_bias.dtype) if dbias is not None else None),)
+    return res
 
 
 # reference-compatible names (bindings.cpp:180-222)

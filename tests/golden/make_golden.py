@@ -14,7 +14,7 @@ Sources of the vectors:
 * ``linoss_im_snapshot.npz``       -- the inline LinOSS-IM snapshot of
   ``tests/test_linoss_parity.py:74-204``.
 * ``dlinoss_generated.npz``, ``linoss_generated.npz``, ``diag_generated.npz``,
-  ``sdlinoss_generated.npz``, ``selective_scan_generated.npz`` -- outputs of the reference itself run here
+  ``sdlinoss_generated.npz``, ``selective_scan_generated.npz``, ``selective_scan_delta.npz`` -- outputs of the reference itself run here
   on seeded inputs: its pure-PyTorch recurrences (float64 and float32, grads by
   autograd) and its compiled CPU kernels (float32).
 """
@@ -220,6 +220,34 @@ def main():
         o3 = kernels.selective_scan(u, dt, A, Bm, Cm, None)
         out[pre + "cpp_out_nogate"] = _np(o3)
     np.savez_compressed(os.path.join(HERE, "selective_scan_generated.npz"), **out)
+    # ---- E2. selective scan with the step transform of the mixer folded in ---------------
+    # dt = softplus(raw + bias[d]) as Mamba4Rec computes it before the scan (mambarec.py:155-157);
+    # float64 run of the reference's Python loop, gradients by autograd
+    out = {}
+    gen = torch.Generator().manual_seed(99)
+    for tag, (Bz, Dn, L, N) in (("s16", (2, 5, 45, 16)), ("s8", (1, 3, 30, 8))):
+        u = torch.randn(Bz, Dn, L, generator=gen)
+        raw = torch.randn(Bz, Dn, L, generator=gen) * 2.0 - 1.0
+        raw[0, 0, :3] = torch.tensor([25.0, 19.5, -30.0])      # both sides of the softplus cut-off and a tiny step
+        bias = torch.randn(Dn, generator=gen) * 0.5
+        A = -torch.exp(torch.randn(Dn, N, generator=gen)) * 0.3
+        Bm = torch.randn(Bz, L, N, generator=gen)
+        Cm = torch.randn(Bz, L, N, generator=gen)
+        gate = torch.randn(Bz, Dn, L, generator=gen)
+        go = torch.randn(Bz, Dn, L, generator=gen)
+        pre = f"{tag}/"
+        for k, v in (("u", u), ("dt_raw", raw), ("delta_bias", bias), ("A", A), ("B", Bm), ("C", Cm), ("gate", gate),
+                     ("grad_out", go)):
+            out[pre + k] = _np(v)
+        leaves = [t.double().clone().requires_grad_(True) for t in (u, raw, A, Bm, Cm, gate, bias)]
+        dt = F.softplus(leaves[1] + leaves[6][None, :, None])
+        y = _selective_scan_mamba(inputs=leaves[0], dt=dt, A=leaves[2], B_t=leaves[3], C_t=leaves[4])
+        o = y * F.silu(leaves[5])
+        (o * go.double()).sum().backward()
+        out[pre + "py64_out"] = _np(o)
+        for name, leaf in zip(("du", "ddt_raw", "dA", "dB", "dC", "dgate", "ddelta_bias"), leaves):
+            out[pre + "py64_" + name] = _np(leaf.grad)
+    np.savez_compressed(os.path.join(HERE, "selective_scan_delta.npz"), **out)
     # ---- F. complex diagonal scan (LRU / S5) ------------------------------
     from ossm.models.lru import _LRUScanFn
     from ossm.models.s5 import _S5ScanFn

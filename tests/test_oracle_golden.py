@@ -210,3 +210,24 @@ def test_sdlinoss_generated(variant, kind):
         want = G[p + "cpp_" + name]
         assert got.shape == want.shape, name
         assert so.max_rel_err(got, want) < 5e-5, name
+
+
+@pytest.mark.parametrize("tag", ["s16", "s8"])
+def test_selective_scan_step_transform(tag):
+    """Selective scan with ``dt = softplus(raw + bias[d])`` folded in, against the reference's Python
+    loop behind ``F.softplus`` (float64 leaves; the loop itself accumulates in float32, hence the
+    tolerances; values on both sides of the softplus cut-off)."""
+    G = _load("selective_scan_delta.npz")
+    p = f"{tag}/"
+    u, raw, bias, A, Bm, Cm, gate, go = (G[p + k].astype(np.float64) for k in
+                                         ("u", "dt_raw", "delta_bias", "A", "B", "C", "gate", "grad_out"))
+    out = so.selective_scan(u, raw, A, Bm, Cm, gate=gate, delta_bias=bias, delta_softplus=True)
+    assert so.max_rel_err(out, G[p + "py64_out"]) < 5e-6
+    grads = so.selective_scan_backward(go, u, raw, A, Bm, Cm, gate=gate, delta_bias=bias, delta_softplus=True)
+    assert len(grads) == 8 and grads[6] is None
+    for name, got in zip(("du", "ddt_raw", "dA", "dB", "dC", "dgate"), grads[:6]):
+        assert so.max_rel_err(got, G[p + "py64_" + name]) < 5e-5, name
+    assert so.max_rel_err(grads[7], G[p + "py64_ddelta_bias"]) < 5e-5
+    # bias without softplus, and softplus without bias, are the same composition
+    plain = so.selective_scan(u, so.delta_transform(raw, bias, False), A, Bm, Cm, gate=gate)
+    assert np.array_equal(plain, so.selective_scan(u, raw, A, Bm, Cm, gate=gate, delta_bias=bias))

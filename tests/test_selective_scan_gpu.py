@@ -224,3 +224,61 @@ def test_serial_and_time_parallel_kernels_agree(shape):
     for a, b in zip(g1, g2):
         if a is not None:
             assert so.max_rel_err(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
+
+
+DELTA = np.load(os.path.join(GOLD, "selective_scan_delta.npz"))
+
+
+@pytest.mark.parametrize("tag", ["s16", "s8"])
+def test_step_transform_fixture(tag):
+    """``dt = softplus(raw + delta_bias[d])`` folded into the scan (serial kernels at d_state 16,
+    time-parallel at 8) against the reference's Python loop behind ``F.softplus``."""
+    from ossm_b200.selective_scan import selective_scan
+
+    p = f"{tag}/"
+    names = ("u", "dt_raw", "A", "B", "C", "gate", "delta_bias")
+    leaves = [dev(DELTA[p + k]).requires_grad_(True) for k in names]
+    u, raw, A, Bm, Cm, gate, bias = leaves
+    out = selective_scan(u, raw, A, Bm, Cm, gate, None, delta_bias=bias, delta_softplus=True)
+    out.backward(dev(DELTA[p + "grad_out"]))
+    np.testing.assert_allclose(out.detach().cpu().numpy(), DELTA[p + "py64_out"], rtol=1e-4, atol=5e-5)
+    for leaf, name in zip(leaves, ("du", "ddt_raw", "dA", "dB", "dC", "dgate", "ddelta_bias")):
+        assert so.max_rel_err(leaf.grad.cpu().numpy(), DELTA[p + "py64_" + name]) <= 1e-4, name
+
+
+@pytest.mark.parametrize("shape", [(2, 70, 300, 16), (1, 9, 257, 8)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("softplus,with_bias", [(True, True), (True, False), (False, True)])
+def test_step_transform_matches_oracle(shape, softplus, with_bias):
+    """Bias and softplus separately and together, ragged sizes, against the float64 oracle; the folded
+    form must also equal the scan run on a step transformed beforehand."""
+    from ossm_b200 import kernels
+
+    u, dt, A, Bm, Cm, gate, go, Dv = make_case(*shape, seed=31)
+    gen = torch.Generator().manual_seed(7)
+    if softplus:
+        raw = torch.randn(shape[0], shape[1], shape[2], generator=gen) * 1.5 - 2.0
+        raw[0, 0, :2] = torch.tensor([24.0, -40.0])
+        bias = torch.randn(shape[1], generator=gen) * 0.5 if with_bias else None
+    else:   # the step must stay positive without the softplus
+        raw = torch.rand(shape[0], shape[1], shape[2], generator=gen) * 0.05
+        bias = torch.rand(shape[1], generator=gen) * 0.02
+    args = [dev(u), dev(raw), dev(A), dev(Bm), dev(Cm), dev(gate)]
+    kw = dict(delta_bias=dev(bias) if with_bias else None, delta_softplus=softplus)
+    out, states = kernels.selective_scan_fwd(*args, dev(Dv), **kw)
+    grads = kernels.selective_scan_bwd(dev(go), *args, states, dev(Dv), **kw)
+    d = lambda t: t.double().numpy()
+    okw = dict(gate=d(gate), D=d(Dv), delta_bias=d(bias) if with_bias else None, delta_softplus=softplus)
+    ref_out = so.selective_scan(d(u), d(raw), d(A), d(Bm), d(Cm), **okw)
+    ref_grads = so.selective_scan_backward(d(go), d(u), d(raw), d(A), d(Bm), d(Cm), **okw)
+    assert so.max_rel_err(out.cpu().numpy(), ref_out) <= 1e-4
+    assert len(grads) == 8
+    for got, want in zip(grads, ref_grads):
+        if want is None:
+            assert got is None
+        else:
+            assert so.max_rel_err(got.cpu().numpy(), want) <= 1e-4
+    # same result as transforming the step first (float32 transform by torch)
+    x = dev(raw) + (dev(bias)[None, :, None] if with_bias else 0.0)
+    pre = torch.nn.functional.softplus(x, threshold=20.0) if softplus else x
+    out2, _ = kernels.selective_scan_fwd(dev(u), pre, dev(A), dev(Bm), dev(Cm), dev(gate), dev(Dv), save_states=False)
+    assert so.max_rel_err(out.cpu().numpy(), out2.cpu().numpy()) <= 2e-5
