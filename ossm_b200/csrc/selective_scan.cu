@@ -842,6 +842,10 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(out) && (!z || sscan::aligned16(z)) &&
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
   if (sscan::serial_ok(N)) {
+    if (!sscan::aligned16(chunk_states)) {
+      set_last_error("selective_scan_forward: chunk_states must be 16-byte aligned");
+      return kErrInvalidArgument;
+    }
     // the B/C tiles are also read with 16-byte loads
     p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm);
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_serial<float>(p, stream)
@@ -896,9 +900,12 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
              (L * es) % 16 == 0 && (L * 4) % 16 == 0;
   int rc;
   if (sscan::serial_ok(N)) {
-    // B/C tiles, saved states, dB and dC are also accessed with 16-byte operations
-    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(chunk_states) &&
-               sscan::aligned16(dB) && sscan::aligned16(dC);
+    if (!sscan::aligned16(chunk_states)) {
+      set_last_error("selective_scan_backward: chunk_states must be 16-byte aligned");
+      return kErrInvalidArgument;
+    }
+    // B/C tiles, dB and dC are also accessed with 16-byte operations
+    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(dB) && sscan::aligned16(dC);
     rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_serial<float>(p, stream)
                                          : sscan::launch_bwd_serial<__nv_bfloat16>(p, stream);
   } else {
