@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "mamba", "sdlinoss", "sharded_layer"],
+    ap.add_argument("--workload", default="dlinoss", choices=["dlinoss", "linoss", "lru", "mamba", "sdlinoss", "sharded_layer"],
                     help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
                          "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
                          "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
@@ -433,6 +433,23 @@ def run_secondary(args):
 
         def bwd(saved):
             return kernels.lti_scan_backward("linoss_im", a, None, dt, bu, saved[2], gx)
+    elif args.workload == "lru":
+        # complex diagonal scan of the LRU / S5 layers at the headline shape: x_t = lambda x_{t-1} + b_t
+        L, B, P = args.length, (args.side_batch or 64), args.ssm
+        mag = torch.rand(P, generator=gen, device=dev) * 0.5 + 0.45
+        ph = torch.rand(P, generator=gen, device=dev) * 6.28
+        lam_re, lam_im = (mag * torch.cos(ph)).contiguous(), (mag * torch.sin(ph)).contiguous()
+        bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev) * 0.5)
+        gx = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device=dev))
+        elems, fb, bb = L * B * P, FWD_BYTES, BWD_BYTES
+        name = f"LRU / S5 complex diagonal scan fwd+bwd, B={B} L={L} P={P}, complex64"
+        metric = "diag_scan_fwd_bwd_gelem_per_s"
+
+        def fwd():
+            return kernels.diag_scan_forward(lam_re, lam_im, bu)
+
+        def bwd(saved):
+            return kernels.diag_scan_backward(lam_re, lam_im, bu, saved[1], gx)
     elif args.workload == "sdlinoss":
         # selective D-LinOSS at the headline shape: per-step a, g, dt fields [L,B,M] from a slowly varying pole
         # field (the layer's map, sdlinoss.py:186-204)
