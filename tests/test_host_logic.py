@@ -56,3 +56,54 @@ def test_torch_library_ops_registered():
     bu = torch.empty(5, 2, 4, dtype=torch.complex64, device="meta")
     st = torch.ops.ossm_b200.dlinoss_imex1_forward(a, a, a, bu)
     assert tuple(st.shape) == (5, 2, 4, 2)
+
+
+def test_sdlinoss_parameter_forms_and_errors():
+    """Selective D-LinOSS host logic: axis assignment of (M,), (L,M), (B,M), (L,B,M) parameters as element strides
+    (0 = broadcast), the reference's messages for bad shapes, and no CPU path."""
+    from ossm_b200.sdlinoss import run_sdlinoss
+
+    L, B, M = 6, 3, 5
+    full = torch.rand(L, B, M)
+    assert kernels._sd_field(full, "A", L, B, M)[1] == [B * M, M, 1]
+    assert kernels._sd_field(full[0, 0].contiguous(), "A", L, B, M)[1] == [0, 0, 1]
+    assert kernels._sd_field(full[:, 0].contiguous(), "A", L, B, M)[1] == [M, 0, 1]        # first axis = length
+    assert kernels._sd_field(full[0].contiguous(), "A", L, B, M)[1] == [0, M, 1]           # first axis = batch
+    assert kernels._sd_field(full[:1].contiguous(), "A", L, B, M)[1] == [0, M, 1]
+    with pytest.raises(RuntimeError, match="Expected size"):
+        kernels._sd_field(torch.rand(L, B, M + 1), "A", L, B, M)
+    with pytest.raises(RuntimeError, match="First dimension must match length or batch"):
+        kernels._sd_field(torch.rand(4, M), "A", L, B, M)
+    with pytest.raises(RuntimeError, match="1, 2, or 3 dimensions"):
+        kernels._sd_field(torch.rand(1, L, B, M), "A", L, B, M)
+    bu = torch.zeros(L, B, M, dtype=torch.complex64)
+    a = torch.rand(M)
+    with pytest.raises(ValueError, match="Unsupported variant"):
+        run_sdlinoss("rk4", a, a, a, bu)
+    with pytest.raises(ValueError, match="must be shaped"):
+        run_sdlinoss("imex1", torch.rand(M + 1), a, a, bu)
+    with pytest.raises(TypeError, match="complex"):
+        run_sdlinoss("imex1", a, a, a, bu.real)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        run_sdlinoss("imex1", a, a, a, bu)                                               # valid shapes, CPU tensors
+    assert run_sdlinoss("ex", a, a, a, torch.zeros(0, B, M, dtype=torch.complex64)).shape == (0, B, M)
+
+
+def test_selective_scan_host_checks():
+    """Selective-scan wrappers: shape checks before any device work, tuning keys, state interval by state size."""
+    u = torch.zeros(2, 3, 8)
+    A = torch.zeros(3, 16)
+    Bm = torch.zeros(2, 8, 16)
+    with pytest.raises(RuntimeError, match="dt must match"):
+        kernels.selective_scan_fwd(u, torch.zeros(2, 3, 7), A, Bm, Bm)
+    with pytest.raises(RuntimeError, match="A must have shape"):
+        kernels.selective_scan_fwd(u, u, torch.zeros(4, 16), Bm, Bm)
+    assert kernels.selective_scan_chunk(16) == 8          # serial kernels: a saved state every 8 steps
+    assert kernels.selective_scan_chunk(32) == 64         # time-parallel kernels
+    kernels.set_selective_scan_tuning("serial", 0)
+    try:
+        assert kernels.selective_scan_chunk(16) == 128
+    finally:
+        kernels.set_selective_scan_tuning("serial", 1)
+    with pytest.raises(RuntimeError, match="unknown key"):
+        kernels.set_selective_scan_tuning("no_such_key", 1)
