@@ -48,6 +48,11 @@ const char* ossm_b200_last_error(void);
 /* Reads (and optionally clears) the device status word that a kernel sets when
  * one of its bounded waits gives up (0 = fine).  Synchronises the device. */
 int ossm_b200_device_status(int* status, int clear);
+/* Self-test of the bounded waits (no counterpart in the reference, whose kernels never wait):
+ * launches one thread that waits on a barrier nothing ever completes, for at most `limit_ns`
+ * (1 ns .. 100 ms) of GPU time.  The wait gives up, the kernel returns normally, *gave_up_dev
+ * (a device int) becomes 1 and the device status word becomes 1 until it is read with clear. */
+int ossm_b200_selftest_wait_timeout(uint64_t limit_ns, int* gave_up_dev, ossm_b200_stream_t stream);
 
 /* ---- D-LinOSS / LinOSS oscillator scan ------------------------------------
  * Replaces ossm::dlinoss_{imex1,imex2,im,ex}_forward / _backward
@@ -112,8 +117,11 @@ int ossm_b200_lti_scan_backward_states(int variant, const float* a, const float*
 
 /* Backward for callers that cannot provide scratch memory (no counterpart in the
  * reference).  Same arguments and results as ossm_b200_lti_scan_backward minus the
- * workspace: the per-series partial sums go to a fixed 1.5 MiB array that is part of
- * the library image on every GPU that loads it.  Meant for hosts that may not
+ * workspace: the per-series partial sums -- and, when a long sequence of few series is
+ * split into time segments, the segment summaries (at most 1.1 MB for any shape the
+ * split applies to, so the split is the one ossm_b200_lti_scan_backward makes with the
+ * workspace it asks for) -- go to a fixed 1.5 MiB array that is part of the library image
+ * on every GPU that loads it.  Meant for hosts that may not
  * allocate device memory when the call is made -- a serving or control process that
  * freezes its allocations after start-up, or a foreign-language stub (cgo, JNI) that
  * owns no CUDA allocator.  Limits and rules:

@@ -20,6 +20,7 @@ SIGNATURES = {
     "ossm_b200_version": (c_int, []),
     "ossm_b200_last_error": (c_char_p, []),
     "ossm_b200_device_status": (c_int, [POINTER(c_int), c_int]),
+    "ossm_b200_selftest_wait_timeout": (c_int, [ctypes.c_uint64, c_void_p, c_void_p]),
     "ossm_b200_lti_chunk": (c_int, []),
     "ossm_b200_lti_carry_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "ossm_b200_lti_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

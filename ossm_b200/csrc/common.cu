@@ -108,9 +108,33 @@ int ensure_dynamic_smem(const void* kernel, size_t bytes) {
 
 }  // namespace ossm_b200
 
+namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_common)
+
+// A CTA of one thread waits on an mbarrier that nothing ever completes, with a short limit: the
+// wait must give up, record kStatusTmaTimeout and let the kernel return.
+__global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, int* gave_up) {
+  __shared__ uint64_t bar;
+  mbar_init(&bar, 1);
+  fence_barrier_init();
+  const bool ok = mbar_wait(&bar, 0, limit_ns);
+  *gave_up = ok ? 0 : 1;
+}
+}  // namespace ossm_b200
+
 extern "C" {
 
 const char* ossm_b200_last_error(void) { return ossm_b200::tls_error; }
+
+int ossm_b200_selftest_wait_timeout(uint64_t limit_ns, int* gave_up_dev, cudaStream_t stream) {
+  using namespace ossm_b200;
+  if (gave_up_dev == nullptr || limit_ns == 0 || limit_ns > 100000000ull) {
+    set_last_error("selftest_wait_timeout: need a device int and a limit of 1 ns .. 100 ms");
+    return kErrInvalidArgument;
+  }
+  wait_timeout_selftest_kernel<<<1, 1, 0, stream>>>(limit_ns, gave_up_dev);
+  return check_cuda(cudaGetLastError(), "wait_timeout_selftest_kernel launch");
+}
 
 int ossm_b200_version(void) { return 1; }
 
@@ -120,13 +144,16 @@ int ossm_b200_device_status(int* status, int clear) {
     set_last_error("device_status: null output pointer");
     return kErrInvalidArgument;
   }
-  int v = 0;
-  if (int rc = check_cuda(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)), "device_status read")) return rc;
-  *status = v;
-  if (clear && v != 0) {
-    int z = 0;
-    if (int rc = check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)), "device_status clear")) return rc;
+  // first non-zero word wins; every word is cleared when asked
+  int (*const words[])(int*, int) = {status_common, status_lti, status_linoss_generic, status_sdlinoss,
+                                     status_selective_scan};
+  int first = 0;
+  for (auto fn : words) {
+    int v = 0;
+    if (int rc = fn(&v, clear)) return rc;
+    if (first == 0) first = v;
   }
+  *status = first;
   return kOk;
 }
 

@@ -1,9 +1,9 @@
 // Shared device/host helpers for the ossm_b200 scan kernels (sm_100a only).
 //
 //  * mbarrier + TMA (cp.async.bulk.tensor) wrappers in inline PTX.  Every wait
-//    is bounded: after kSpinLimit failed polls the waiter records an error in a
-//    device status word and the kernel returns, so a lost copy can never hang
-//    the GPU.
+//    is bounded in time (%globaltimer, kWaitLimitNs): a waiter that runs out
+//    records an error in a device status word and the kernel returns, so a lost
+//    copy can never hang the GPU.
 //  * host-side tensor-map construction through the driver entry point (the
 //    library does not link libcuda).
 #pragma once
@@ -11,6 +11,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <cstring>
 
 namespace ossm_b200 {
 
@@ -28,9 +30,30 @@ int check_cuda(cudaError_t err, const char* what);
 
 // Device status word: 0 = fine, otherwise the code of the first bounded wait
 // that gave up (kStatus*).  Read with ossm_b200_device_status().
-enum : int { kStatusTmaTimeout = 1 };
-// (defined here: the library is built as a single translation unit)
-__device__ int g_device_status = 0;
+enum : int { kStatusTmaTimeout = 1, kStatusMmaTimeout = 2 };
+// Every translation unit has its own word (no relocatable device code); each one
+// exposes it through an accessor made by OSSM_B200_STATUS_ACCESSOR, and
+// ossm_b200_device_status() combines them.
+#ifdef __CUDACC__
+static __device__ int g_device_status = 0;
+#define OSSM_B200_STATUS_ACCESSOR(fn)                                                                   \
+  int fn(int* status, int clear) {                                                                      \
+    int v = 0;                                                                                          \
+    if (int rc = check_cuda(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)), "device_status read")) \
+      return rc;                                                                                        \
+    *status = v;                                                                                        \
+    if (clear && v != 0) {                                                                              \
+      int z = 0;                                                                                        \
+      return check_cuda(cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)), "device_status clear");  \
+    }                                                                                                   \
+    return kOk;                                                                                         \
+  }
+#endif
+int status_common(int* status, int clear);
+int status_lti(int* status, int clear);
+int status_linoss_generic(int* status, int clear);
+int status_sdlinoss(int* status, int clear);
+int status_selective_scan(int* status, int clear);
 
 // ---- tensor maps (host) ----------------------------------------------------
 // 2-D fp32 view [rows, cols] with row pitch `pitch_bytes`; box = box_cols x box_rows.
@@ -51,7 +74,13 @@ int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 // ---- device helpers --------------------------------------------------------
 #ifdef __CUDACC__
-constexpr uint32_t kSpinLimit = 1u << 24;  // polls of mbarrier.try_wait (each blocks up to a HW time slice)
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // longest time any wait may take (wall clock of the GPU)
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -86,12 +115,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false after kSpinLimit polls (the caller must bail out).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait.  Returns false once `limit_ns` of GPU wall-clock time have passed without the
+// phase completing (the caller must bail out); the clock is read every 32 failed polls, each of
+// which may itself block for a hardware-defined slice.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs,
+                                          int code = kStatusTmaTimeout) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t polls = 1;; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((polls & 31u) == 0 && globaltimer_ns() - t0 > limit_ns) break;
   }
-  atomicCAS(&g_device_status, 0, kStatusTmaTimeout);
+  atomicCAS(&g_device_status, 0, code);
   return false;
 }
 

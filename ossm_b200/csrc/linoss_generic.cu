@@ -18,6 +18,7 @@
 #include "../../include/ossm_b200.h"
 
 namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_linoss_generic)
 namespace lgen {
 
 constexpr int kBatch = 8;

@@ -35,6 +35,7 @@
 #include "../../include/ossm_b200.h"
 
 namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_lti)
 namespace lti {
 
 constexpr int kChunk = 32;          // rows per stage == carry interval

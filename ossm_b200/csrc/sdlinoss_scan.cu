@@ -39,6 +39,7 @@
 #include "../../include/ossm_b200.h"
 
 namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_sdlinoss)
 namespace sdl {
 
 constexpr int kSelChunk = 32;   // rows per shared-memory stage

@@ -35,6 +35,7 @@
 #include "../../include/ossm_b200.h"
 
 namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_selective_scan)
 namespace sscan {
 
 constexpr int kWarps = 8;

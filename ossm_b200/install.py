@@ -7,11 +7,108 @@ Seeding ``sys.modules["ossm._kernels"]`` with :mod:`ossm_b200.kernels` *before*
 registers) call into ``libossm_b200.so``.  ``patch_ops=True`` additionally swaps
 ossm's op functions for the leaner ones of this package (no full-state
 materialisation, CUDA backward for LinOSS, bf16 selective scan, selective D-LinOSS from chunk carries).
+
+Scope rule of the swapped functions: inputs this library covers -- CUDA tensors in
+float32 / complex64 (plus bfloat16 and ``d_state <= 256`` for the selective scan)
+-- always run its kernels, and a failure there raises; nothing on a GPU falls back
+silently.  Everything else (CPU tensors of a model moved to the host for export or
+evaluation, float64 / complex128 gradcheck inputs, float16, larger state sizes)
+is handed to ossm's own function, which takes its PyTorch path exactly as it does
+without this package (``_dlinoss_scan.py:648-680``, ``_selective_scan.py:141-145``,
+``mambarec.py:172-180``).
 """
 from __future__ import annotations
 
 import importlib
 import sys
+
+import torch
+
+MAX_D_STATE = 256   # largest Mamba state size of the CUDA kernels (the reference's MAX_DSTATE, selective_scan_common.h:41)
+
+
+def _covered_complex(bu, *coeffs) -> bool:
+    """CUDA, complex64 forcing and float32 coefficients: what the oscillator kernels take."""
+    return bool(bu.is_cuda and bu.dtype == torch.complex64
+                and all(c is None or (c.is_cuda and c.dtype == torch.float32) for c in coeffs))
+
+
+def _wrap_dlinoss(ours, original):
+    def run_dlinoss(variant, a_diag, g_diag, step, bu):
+        if _covered_complex(bu, a_diag, g_diag, step):
+            return ours(variant, a_diag, g_diag, step, bu)
+        return original(variant, a_diag, g_diag, step, bu)
+
+    run_dlinoss.__doc__ = ours.__doc__
+    run_dlinoss.__wrapped__ = original
+    return run_dlinoss
+
+
+def _wrap_sdlinoss(ours, module):
+    original = module.run_sdlinoss
+    normalize = getattr(module, "_normalize_param", None)
+    from_views = getattr(module, "_reference_sdlinoss_states_from_views", None)
+
+    def run_sdlinoss(variant, a_diag, g_diag, step, bu):
+        if torch.is_tensor(bu) and bu.dim() == 3 and _covered_complex(bu, a_diag, g_diag, step):
+            return ours(variant, a_diag, g_diag, step, bu)
+        if (normalize is None or from_views is None or not torch.is_tensor(bu) or bu.dim() != 3
+                or not bu.is_complex() or bu.size(0) == 0):
+            return original(variant, a_diag, g_diag, step, bu)
+        # ossm's run_sdlinoss has no fallback once kernels are present (_sdlinoss_scan.py:414-452);
+        # evaluate its own PyTorch recurrence for inputs the kernels do not take
+        length, batch, ssm = bu.shape
+        real = torch.float64 if bu.dtype == torch.complex128 else torch.float32
+        views = [normalize(p, n, length, batch, ssm, device=bu.device, dtype=real)
+                 for p, n in ((a_diag, "A"), (g_diag, "G"), (step, "step"))]
+        return from_views(variant.lower(), views[0], views[1], views[2], bu)[..., 1]
+
+    run_sdlinoss.__wrapped__ = original
+    return run_sdlinoss
+
+
+def _wrap_try_run_scan(ours):
+    def try_run_scan(m11, m12, m21, m22, b_seq):
+        if b_seq.is_cuda and b_seq.dtype == torch.complex64:
+            return ours(m11, m12, m21, m22, b_seq)
+        return None     # ossm's contract for "no kernel": the caller runs its doubling scan (linoss.py:69-76)
+
+    return try_run_scan
+
+
+def _wrap_associative_scan(ours, original):
+    def _run_associative_scan(a_matrix, b_seq):
+        if b_seq.is_cuda and b_seq.dtype == torch.complex64:
+            return ours(a_matrix, b_seq)
+        return original(a_matrix, b_seq)
+
+    return _run_associative_scan
+
+
+def _wrap_diag_fn(ours, original):
+    class _DiagScanDispatch:
+        """Stands where ``_LRUScanFn`` / ``_S5ScanFn`` stood: the layers only call ``.apply``."""
+
+        @staticmethod
+        def apply(lambda_bar, b_seq):
+            if b_seq.is_cuda and b_seq.dtype == torch.complex64:
+                return ours.apply(lambda_bar, b_seq)
+            return original.apply(lambda_bar, b_seq)
+
+    _DiagScanDispatch.__wrapped__ = original
+    return _DiagScanDispatch
+
+
+def _wrap_try_selective_scan(ours):
+    def try_selective_scan(inputs, dt, A, B, C, gate):
+        covered = (inputs.is_cuda and inputs.dtype in (torch.float32, torch.bfloat16) and A.dim() == 2
+                   and 0 < A.size(1) <= MAX_D_STATE and (gate is None or gate.dtype == inputs.dtype)
+                   and B.dtype == inputs.dtype and C.dtype == inputs.dtype)
+        if covered:
+            return ours(inputs, dt, A, B, C, gate)
+        return None     # ossm's contract for "no kernel": the mixer runs _selective_scan_mamba (mambarec.py:172-180)
+
+    return try_selective_scan
 
 
 def install_as_ossm_kernels(patch_ops: bool = True) -> None:
@@ -38,25 +135,39 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
             mods[name] = importlib.import_module(f"ossm.models.{name}")
         except ImportError:
             continue
-    for name in ("_dlinoss_scan", "dlinoss"):
-        if name in mods:
-            mods[name].run_dlinoss = dlinoss.run_dlinoss
+    if "_dlinoss_scan" in mods:
+        original = mods["_dlinoss_scan"].run_dlinoss
+        original = getattr(original, "__wrapped__", original)      # installing twice must not nest wrappers
+        wrapped = _wrap_dlinoss(dlinoss.run_dlinoss, original)
+        for name in ("_dlinoss_scan", "dlinoss"):
+            if name in mods:
+                mods[name].run_dlinoss = wrapped
     # selective D-LinOSS: the layer imports run_sdlinoss by name (sdlinoss.py:13)
-    for name in ("_sdlinoss_scan", "sdlinoss"):
-        if name in mods:
-            mods[name].run_sdlinoss = sdlinoss.run_sdlinoss
+    if "_sdlinoss_scan" in mods:
+        module = mods["_sdlinoss_scan"]
+        if hasattr(module.run_sdlinoss, "__wrapped__"):
+            module.run_sdlinoss = module.run_sdlinoss.__wrapped__
+        wrapped = _wrap_sdlinoss(sdlinoss.run_sdlinoss, module)
+        for name in ("_sdlinoss_scan", "sdlinoss"):
+            if name in mods:
+                mods[name].run_sdlinoss = wrapped
     if "linoss" in mods:
-        mods["linoss"]._run_associative_scan = linoss.run_associative_scan
-        mods["linoss"].try_run_scan = linoss.try_run_scan
+        original = getattr(mods["linoss"]._run_associative_scan, "__wrapped__", mods["linoss"]._run_associative_scan)
+        wrapped = _wrap_associative_scan(linoss.run_associative_scan, original)
+        wrapped.__wrapped__ = original
+        mods["linoss"]._run_associative_scan = wrapped
+        mods["linoss"].try_run_scan = _wrap_try_run_scan(linoss.try_run_scan)
     if "_linoss_scan" in mods:
-        mods["_linoss_scan"].try_run_scan = linoss.try_run_scan
+        mods["_linoss_scan"].try_run_scan = _wrap_try_run_scan(linoss.try_run_scan)
     # LRU / S5: the layers call ``_LRUScanFn.apply`` / ``_S5ScanFn.apply`` (lru.py:176, s5.py:294)
-    if "lru" in mods:
-        mods["lru"]._LRUScanFn = diag.DiagScanFn
-    if "s5" in mods:
-        mods["s5"]._S5ScanFn = diag.DiagScanFn
+    for name, attr in (("lru", "_LRUScanFn"), ("s5", "_S5ScanFn")):
+        if name in mods:
+            original = getattr(mods[name], attr)
+            original = getattr(original, "__wrapped__", original)
+            setattr(mods[name], attr, _wrap_diag_fn(diag.DiagScanFn, original))
+    wrapped = _wrap_try_selective_scan(selective_scan.try_selective_scan)
     if "_selective_scan" in mods:
-        mods["_selective_scan"].try_selective_scan = selective_scan.try_selective_scan
+        mods["_selective_scan"].try_selective_scan = wrapped
     if "mambarec" in mods:
         # the mixer binds the function under a private alias (mambarec.py:13)
-        mods["mambarec"]._try_selective_scan = selective_scan.try_selective_scan
+        mods["mambarec"]._try_selective_scan = wrapped

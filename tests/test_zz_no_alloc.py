@@ -65,6 +65,28 @@ def test_static_scratch_backward_matches_workspace_backward():
     assert _lib.device_status() == 0
 
 
+def test_static_scratch_with_time_segments():
+    """Few series and a long sequence: the backward splits the time axis and keeps the segment
+    summaries in the same built-in array.  Same split, same kernels as the workspace entry, so the
+    results are identical; a second call straight after finds the array used and still agrees."""
+    from ossm_b200 import _lib, kernels
+
+    lib = _lib.load()
+    for (L, B, P, name, vid) in ((2048, 2, 64, "imex1", 0), (4096, 1, 96, "im", 2)):
+        assert lib.ossm_b200_lti_backward_workspace_bytes(L, B, P) > 6 * B * P * 4     # the heuristic splits it
+        a, g, st, bu, gx = _case(L, B, P, seed=L + P)
+        _, _, carries = kernels.lti_scan_forward(name, a, g, st, bu)
+        want = kernels.lti_scan_backward(name, a, g, st, bu, carries, gx)
+        for _ in range(2):
+            got = _run_static(lib, vid, a, g, st, bu, carries, gx)
+            torch.cuda.synchronize()
+            for w, q in zip(want, got):
+                w = torch.view_as_real(w) if w.is_complex() else w
+                q = torch.view_as_real(q) if q.is_complex() else q
+                assert torch.equal(w, q)
+    assert _lib.device_status() == 0
+
+
 def test_static_scratch_rejects_oversized_problems():
     from ossm_b200 import _lib
 
