@@ -12,6 +12,12 @@ becomes ``-march=x86-64-v3`` (the object must also run on a different host CPU
 than the one that compiled it) and ``-fopenmp`` is kept for compilation but
 dropped at link time when the toolchain cannot link libgomp.
 
+``stage_package`` additionally places a copy of the reference's Python package (``src/ossm``,
+Python files only) under the git-ignored ``oracle/_ref/pkg/`` next to the compiled kernels.  It
+is what the drop-in tests import on a machine that has no ossm checkout (the GPU box): they put
+this library behind the unmodified ossm layers and compare results.  It is never committed and
+nothing in the product package reads it.
+
 Usage:  python oracle/build_ref.py [--reference /path/to/ossm/checkout]
 """
 from __future__ import annotations
@@ -20,6 +26,7 @@ import argparse
 import glob
 import os
 import concurrent.futures
+import shutil
 import subprocess
 import sysconfig
 
@@ -78,6 +85,21 @@ def build(reference: str, verbose: bool = False) -> str:
     return dst
 
 
+def stage_package(reference: str) -> str:
+    """Copies ``<reference>/src/ossm`` (``*.py`` only) to ``oracle/_ref/pkg/ossm``."""
+    src = os.path.join(reference, "src", "ossm")
+    if not os.path.isdir(src):
+        raise FileNotFoundError(f"no ossm package under {src}")
+    dst_root = os.path.join(OUT, "pkg")
+    dst = os.path.join(dst_root, "ossm")
+    if os.path.isdir(dst):
+        shutil.rmtree(dst)
+    shutil.copytree(src, dst, ignore=lambda d, names: [n for n in names
+                                                      if not (n.endswith(".py") or os.path.isdir(os.path.join(d, n)))
+                                                      or n in ("csrc", "__pycache__")])
+    return dst_root
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -86,3 +108,4 @@ if __name__ == "__main__":
     ap.add_argument("-v", "--verbose", action="store_true")
     args = ap.parse_args()
     print(build(args.reference, args.verbose))
+    print(stage_package(args.reference))

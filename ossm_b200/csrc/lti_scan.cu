@@ -702,6 +702,8 @@ lti_param_grad_kernel(const float* __restrict__ a, const float* __restrict__ g, 
   if (grad_step) grad_step[pch] = (float)ds;
 }
 
+#include "lti_scan_twolevel.cuh"
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -712,8 +714,20 @@ struct Tuning {
   int bwd_warps = 4;
   int force_plain = 0;
   int segments = 0;   // 0 = automatic
+  int twolevel = 1;   // 1 = two-level kernels for long sequences of few series, 0 = never
+  int tl_fwd_ring = 4;
+  int tl_bwd_ring = 3;
 };
 static Tuning g_tuning;
+
+// Long sequences of few series take the two-level kernels (lti_scan_twolevel.cuh): enough series for
+// 64 CTAs of 16 columns, too few for the wide kernels to fill the GPU, and at least four tiles of time.
+// The upper bound also keeps the backward's partial sums (6 * 8 * N floats) inside the built-in
+// scratch of the allocation-free entry, so that entry and the workspace entry always take the same path.
+static bool use_twolevel(int variant, long long L, long long N) {
+  if (!g_tuning.twolevel || g_tuning.segments > 0 || g_tuning.force_plain || variant == kDiag) return false;
+  return N >= 1024 && N <= 8192 && L >= 4 * kTlRows;
+}
 
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
@@ -747,6 +761,7 @@ static int pick_segments_for(long long L, long long N, int warps) {
   return V == kDiag ? 1 : pick_segments(L, N, warps);
 }
 
+static size_t twolevel_backward_ws_bytes(long long N) { return (size_t)kNumAcc * kTlSub * N * sizeof(float); }
 static size_t forward_ws_bytes(int S, long long N) { return S > 1 ? (size_t)2 * S * N * sizeof(float4) : 0; }
 static size_t backward_ws_bytes(int S, long long N) {
   return (size_t)kNumAcc * S * N * sizeof(float) + (S > 1 ? (size_t)2 * S * N * sizeof(float4) : 0);
@@ -772,6 +787,19 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
   q.seg_chunks = nchunks;
   q.seg_init = nullptr;
   q.seg_end = nullptr;
+  if (tma && use_twolevel(V, p.L, p.N)) {
+    CUtensorMap tm2;
+    memset(&tm2, 0, sizeof(tm2));
+    if (make_tensor_map_2d_f32(&tm2, p.bu, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2,
+                               kTlRows)) {
+      q.ring = g_tuning.tl_fwd_ring;
+      const size_t smem = 4096 + (size_t)q.ring * kTlTileBytes;
+      if (int rc = set_smem(lti_forward_twolevel_kernel<V, kOut>, smem)) return rc;
+      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
+      lti_forward_twolevel_kernel<V, kOut><<<ctas, kTlThreads, smem, stream>>>(tm2, q);
+      return check_cuda(cudaGetLastError(), "lti_forward_twolevel_kernel launch");
+    }
+  }
   if (tma) {
     q.ring = g_tuning.fwd_ring;
     const size_t smem = 1024 + (size_t)warps * q.ring * kStageBytes;
@@ -838,6 +866,26 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   q.seg_chunks = nchunks;
   q.lam_init = nullptr;
   int S = 1;
+  if (tma && use_twolevel(V, p.L, p.N) && ws_bytes >= twolevel_backward_ws_bytes(p.N)) {
+    CUtensorMap tb, tg;
+    memset(&tb, 0, sizeof(tb));
+    memset(&tg, 0, sizeof(tg));
+    if (make_tensor_map_2d_f32(&tb, p.bu, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2, kTlRows) &&
+        make_tensor_map_2d_f32(&tg, p.grad_x, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2,
+                               kTlRows)) {
+      q.ring = g_tuning.tl_bwd_ring;
+      const size_t smem = 4096 + (size_t)q.ring * 2 * kTlTileBytes;
+      if (int rc = set_smem(lti_backward_twolevel_kernel<V>, smem)) return rc;
+      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
+      lti_backward_twolevel_kernel<V><<<ctas, kTlThreads, smem, stream>>>(tb, tg, q);
+      if (int rc = check_cuda(cudaGetLastError(), "lti_backward_twolevel_kernel launch")) return rc;
+      const unsigned blocks = (unsigned)((p.P + kPgCh - 1) / kPgCh);
+      // the sub-chunk positions of a series are summed like extra batch entries
+      lti_param_grad_kernel<V><<<blocks, kPgCh * kPgGroups, 0, stream>>>(p.a, p.g, p.step, p.partials, grad_a, grad_g,
+                                                                       grad_step, B * kTlSub, p.P);
+      return check_cuda(cudaGetLastError(), "lti_param_grad_kernel launch");
+    }
+  }
   if (tma) {
     q.ring = g_tuning.bwd_ring;
     S = pick_segments_for<V>(p.L, p.N, warps);
@@ -919,6 +967,9 @@ int ossm_b200_lti_set_tuning(const char* key, int value) {
   if (!strcmp(key, "bwd_warps") && value >= 1 && value <= 4) { g_tuning.bwd_warps = value; return kOk; }
   if (!strcmp(key, "force_plain")) { g_tuning.force_plain = value != 0; return kOk; }
   if (!strcmp(key, "segments") && value >= 0 && value <= 64) { g_tuning.segments = value; return kOk; }
+  if (!strcmp(key, "twolevel")) { g_tuning.twolevel = value != 0; return kOk; }
+  if (!strcmp(key, "tl_fwd_ring") && value >= 1 && value <= 6) { g_tuning.tl_fwd_ring = value; return kOk; }
+  if (!strcmp(key, "tl_bwd_ring") && value >= 1 && value <= 3) { g_tuning.tl_bwd_ring = value; return kOk; }
   set_last_error("lti_set_tuning: unknown key or value out of range: %s=%d", key, value);
   return kErrInvalidArgument;
 }
@@ -932,11 +983,14 @@ size_t ossm_b200_lti_carry_bytes(int64_t L, int64_t B, int64_t P) {
 size_t ossm_b200_lti_backward_workspace_bytes(int64_t L, int64_t B, int64_t P) {
   if (L <= 0 || B <= 0 || P <= 0) return 0;
   const int S = g_tuning.segments > 0 ? 64 : pick_segments(L, B * P, g_tuning.bwd_warps);
-  return backward_ws_bytes(S, B * P);
+  const size_t seg = backward_ws_bytes(S, B * P);
+  const size_t two = use_twolevel(kImex1, L, B * P) ? twolevel_backward_ws_bytes(B * P) : 0;
+  return seg > two ? seg : two;
 }
 
 size_t ossm_b200_lti_forward_workspace_bytes(int64_t L, int64_t B, int64_t P) {
   if (L <= 0 || B <= 0 || P <= 0) return 0;
+  if (use_twolevel(kImex1, L, B * P)) return 0;   // the two-level forward needs no scratch
   const int S = g_tuning.segments > 0 ? 64 : pick_segments(L, B * P, g_tuning.fwd_warps);
   return forward_ws_bytes(S, B * P);
 }

@@ -42,6 +42,8 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kCI = 8;                      // channels per warp
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxState = 256;              // the reference kernels' MAX_DSTATE (csrc/mamba/selective_scan_common.h:41)
+constexpr int kStateTile = 64;              // backward: states per pass over a chunk when d_state is larger
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -220,6 +222,7 @@ __device__ __forceinline__ void sts_pairs(float* tile, int pair, int lane, const
 
 // Stages the chunk tile of a [B, N, L] operand (converted to fp32) for the chunk
 // starting at t_base; global reads are coalesced along time.
+// `src_b` points at the first of the N rows to stage (a tile of the states when they are processed in tiles).
 template <typename IO, int kItems>
 __device__ __forceinline__ void stage_tile(float* dst, const IO* src_b, int N, long long t_base, long long L) {
   constexpr int T = 32 * kItems;
@@ -338,6 +341,7 @@ struct Params {
   long long nstates;   // saved states per lane = ceil(L / state_interval)
   int state_interval;  // steps between saved states (= the backward's chunk)
   int cpw;             // channels per warp (<= kCI); smaller for small problems so the grid fills the GPU
+  int state_tile;      // backward: states processed per pass over a chunk (even; >= N means a single pass)
   bool vec_ok;
 };
 
@@ -448,54 +452,68 @@ __global__ void __launch_bounds__(kThreads) sscan_forward_kernel(Params p) {
   }
 }
 
-// Shared memory (floats), NP = ceil(N/2), tile = NP*T*2:
-//   Bs | Cs (one tile each) | acc[kWarps][2 (dB,dC)][tile] | lam[kWarps*kCI*NP*2] | dAacc[kWarps*kCI*NP*2]
-//   | dDacc[kWarps*kCI] | dBiasacc[kWarps*kCI]
+// Shared memory (floats), NP = ceil(N/2); the states are processed in tiles of NT = p.state_tile states
+// (NPt = NT/2 pairs, tile = NPt*T*2; one tile covers all states when N <= 64):
+//   Bs | Cs (one tile each) | acc[kWarps][2 (dB,dC)][tile] | lam[kWarps*cpw*NP*2] | dAacc[kWarps*cpw*NP*2]
+//   | dDacc[kWarps*cpw] | dBiasacc[kWarps*cpw] | part[kWarps*cpw][3][kItems][32][2] (only with several tiles)
 // Every warp owns a private dB/dC accumulator tile, so the warps of a CTA run
-// independently between the three barriers of a chunk (tile staging, flush).
+// independently between the three barriers of a pass (tile staging, flush).  With several state tiles
+// a chunk is walked once per tile; the per-step sums over the states (y, du, ddt) of every channel wait
+// in `part` between the passes and the per-channel outputs are written by the last one.
 template <typename IO, int kItems>
 __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
   constexpr int T = 32 * kItems;
   extern __shared__ __align__(16) float smem[];
   const int N = (int)p.N;
   const int NP = (N + 1) / 2;
-  const int tile = NP * T * 2;
+  const int NT = p.state_tile < 2 * NP ? p.state_tile : 2 * NP;     // states per tile (even)
+  const int ntiles = (2 * NP + NT - 1) / NT;
+  const int tile = (NT / 2) * T * 2;
+  const int cpw = p.cpw;
   float* Bs = smem;
   float* Cs = Bs + tile;
   float* acc = Cs + tile;
   float2* lam = reinterpret_cast<float2*>(acc + kWarps * 2 * tile);   // adjoint carried from the later chunk
-  float2* dAacc = lam + kWarps * kCI * NP;
-  float* dDacc = reinterpret_cast<float*>(dAacc + kWarps * kCI * NP);
-  float* dBiasacc = dDacc + kWarps * kCI;
+  float2* dAacc = lam + kWarps * cpw * NP;
+  float* dDacc = reinterpret_cast<float*>(dAacc + kWarps * cpw * NP);
+  float* dBiasacc = dDacc + kWarps * cpw;
+  float2* part = reinterpret_cast<float2*>(dBiasacc + kWarps * cpw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long b = blockIdx.y;
-  const long long d0 = (long long)blockIdx.x * (kWarps * p.cpw) + warp * p.cpw;
+  const long long d0 = (long long)blockIdx.x * (kWarps * cpw) + warp * cpw;
   const long long nchunks = (p.L + T - 1) / T;
   const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
   const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
   float* accB = acc + warp * 2 * tile;
   float* accC = accB + tile;
 
-  for (int i = threadIdx.x; i < kWarps * kCI * NP; i += kThreads) {
+  for (int i = threadIdx.x; i < kWarps * cpw * NP; i += kThreads) {
     lam[i] = make_float2(0.f, 0.f);
     dAacc[i] = make_float2(0.f, 0.f);
   }
-  for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) { dDacc[i] = 0.0f; dBiasacc[i] = 0.0f; }
+  for (int i = threadIdx.x; i < kWarps * cpw; i += kThreads) { dDacc[i] = 0.0f; dBiasacc[i] = 0.0f; }
 
   for (long long c = nchunks - 1; c >= 0; --c) {
     const long long t_base = c * T;
+    const long long t0 = t_base + (long long)lane * kItems;
+#pragma unroll 1
+    for (int st = 0; st < ntiles; ++st) {
+    const int n0 = st * NT;                                   // first state of this tile
+    const int ncur = (N - n0) < NT ? (N - n0) : NT;           // states in this tile
+    const int npcur = (ncur + 1) / 2;
+    const int pr0 = n0 / 2;
+    const bool first_tile = st == 0, last_tile = st == ntiles - 1;
     __syncthreads();  // previous flush finished
-    stage_tile<IO, kItems>(Bs, Bm_b, N, t_base, p.L);
-    stage_tile<IO, kItems>(Cs, Cm_b, N, t_base, p.L);
+    stage_tile<IO, kItems>(Bs, Bm_b + (long long)n0 * p.L, ncur, t_base, p.L);
+    stage_tile<IO, kItems>(Cs, Cm_b + (long long)n0 * p.L, ncur, t_base, p.L);
     for (int i = threadIdx.x; i < kWarps * 2 * tile; i += kThreads) acc[i] = 0.0f;
     __syncthreads();
-    const long long t0 = t_base + (long long)lane * kItems;
 
     // operands of the first channel; those of channel ci+1 are fetched while ci is processed
     float u[kItems], dt[kItems], go[kItems], zz[kItems];
     auto fetch = [&](int ci, float (&fu)[kItems], float (&fdt)[kItems], float (&fgo)[kItems], float (&fz)[kItems]) {
       const long long d = d0 + ci;
-      const bool ok = ci < p.cpw && d < p.D;
+      const bool ok = ci < cpw && d < p.D;
       const long long row = ok ? (b * p.D + d) * p.L : 0;
       const long long tl = ok ? p.L : 0;
       load_items<IO, kItems>(static_cast<const IO*>(p.u) + row, t0, tl, p.vec_ok, fu);
@@ -510,7 +528,7 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
     };
     fetch(0, u, dt, go, zz);
 #pragma unroll 1
-    for (int ci = 0; ci < p.cpw; ++ci) {
+    for (int ci = 0; ci < cpw; ++ci) {
       const long long d = d0 + ci;
       if (d >= p.D) break;                                    // warp-uniform; no CTA barrier inside this loop
       const long long row = (b * p.D + d) * p.L;
@@ -518,19 +536,27 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
       fetch(ci + 1, nu, ndt, ngo, nz);
       float gy[kItems];
       float2 dtu2[kItems], dus2[kItems], ddts2[kItems], y2[kItems];
+      float2* mypart = part + (size_t)((warp * cpw + ci) * 3) * kItems * 32 + lane;
 #pragma unroll
       for (int j = 0; j < kItems; ++j) {
         gy[j] = p.z ? go[j] * (zz[j] * sigmoidf(zz[j])) : go[j];
         dtu2[j] = splat(dt[j] * u[j]);
-        dus2[j] = make_float2(0.f, 0.f);
-        ddts2[j] = make_float2(0.f, 0.f);
-        y2[j] = make_float2(0.f, 0.f);
+        if (first_tile) {
+          dus2[j] = make_float2(0.f, 0.f);
+          ddts2[j] = make_float2(0.f, 0.f);
+          y2[j] = make_float2(0.f, 0.f);
+        } else {
+          dus2[j] = mypart[(0 * kItems + j) * 32];
+          ddts2[j] = mypart[(1 * kItems + j) * 32];
+          y2[j] = mypart[(2 * kItems + j) * 32];
+        }
       }
-      const int slot = (warp * kCI + ci) * NP;
+      const int slot = (warp * cpw + ci) * NP;
       const float* cs_in = p.chunk_states + ((b * p.D + d) * p.nstates + c * (T / p.state_interval)) * p.N;
 #pragma unroll 1
-      for (int pr = 0; pr < NP; ++pr) {
-        const float2 Ap = load_A_pair(p.A, d, N, pr, true);
+      for (int pr = 0; pr < npcur; ++pr) {
+        const int gp = pr0 + pr;                              // pair index among all states
+        const float2 Ap = load_A_pair(p.A, d, N, gp, true);
         const float2 A2 = make_float2(Ap.x * kLog2e, Ap.y * kLog2e);
         float2 a[kItems], Bv[kItems], Cv[kItems];
         lds_pairs<kItems>(Bs, pr, lane, Bv);
@@ -552,9 +578,9 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
           Q = p2mul(Q, a[j]);
         }
         float2 h_in;
-        h_in.x = __ldg(cs_in + 2 * pr);
-        h_in.y = (2 * pr + 1 < N) ? __ldg(cs_in + 2 * pr + 1) : 0.0f;
-        const float2 lam_in = lam[slot + pr];              // adjoint entering the chunk from the right
+        h_in.x = __ldg(cs_in + 2 * gp);
+        h_in.y = (2 * gp + 1 < N) ? __ldg(cs_in + 2 * gp + 1) : 0.0f;
+        const float2 lam_in = lam[slot + gp];              // adjoint entering the chunk from the right
         float2 Pex, Hex, Qex, Rex, Qtot, Rtot;
         warp_scan_dual(P, H, Q, R, lane, Pex, Hex, Qex, Rex, Qtot, Rtot);
         float2 h = p2fma(Pex, h_in, Hex);             // state entering this thread's steps
@@ -590,10 +616,19 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
           dA2.y += __shfl_xor_sync(0xffffffffu, dA2.y, off);
         }
         if (lane == 0) {
-          lam[slot + pr] = p2fma(Qtot, lam_in, Rtot);
-          dAacc[slot + pr] = p2add(dAacc[slot + pr], dA2);
+          lam[slot + gp] = p2fma(Qtot, lam_in, Rtot);
+          dAacc[slot + gp] = p2add(dAacc[slot + gp], dA2);
         }
       }
+      if (!last_tile) {
+        // sums over the states seen so far wait for the remaining tiles
+#pragma unroll
+        for (int j = 0; j < kItems; ++j) {
+          mypart[(0 * kItems + j) * 32] = dus2[j];
+          mypart[(1 * kItems + j) * 32] = ddts2[j];
+          mypart[(2 * kItems + j) * 32] = y2[j];
+        }
+      } else {
       // du_t = dt_t * sum_n G*B (+ gy*Dskip) ; ddt_t = sum_n q*A + u_t * sum_n G*B
       float ds = 0.0f, dD_t = 0.0f;
       if (p.Dskip) ds = __ldg(p.Dskip + d);
@@ -628,20 +663,21 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
       if (p.dD_part) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dD_t += __shfl_xor_sync(0xffffffffu, dD_t, off);
-        if (lane == 0) dDacc[warp * kCI + ci] += dD_t;
+        if (lane == 0) dDacc[warp * cpw + ci] += dD_t;
       }
       if (p.dbias_part) {
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dbias_t += __shfl_xor_sync(0xffffffffu, dbias_t, off);
-        if (lane == 0) dBiasacc[warp * kCI + ci] += dbias_t;
+        if (lane == 0) dBiasacc[warp * cpw + ci] += dbias_t;
+      }
       }
 #pragma unroll
       for (int j = 0; j < kItems; ++j) { u[j] = nu[j]; dt[j] = ndt[j]; go[j] = ngo[j]; zz[j] = nz[j]; }
       __syncwarp();
     }
-    // sum the warps' private tiles and flush this chunk's dB/dC to global
+    // sum the warps' private tiles and flush this pass's dB/dC rows to global
     __syncthreads();
-    for (int i = threadIdx.x; i < N * T; i += kThreads) {
+    for (int i = threadIdx.x; i < ncur * T; i += kThreads) {
       const int n = i / T, t = i - n * T;
       const long long tt = t_base + t;
       if (tt < p.L) {
@@ -652,33 +688,34 @@ __global__ void __launch_bounds__(kThreads) sscan_backward_kernel(Params p) {
           sb += acc[w * 2 * tile + ti];
           sc += acc[w * 2 * tile + tile + ti];
         }
-        atomicAdd(p.dB + (b * p.N + n) * p.L + tt, sb);
-        atomicAdd(p.dC + (b * p.N + n) * p.L + tt, sc);
+        atomicAdd(p.dB + (b * p.N + n0 + n) * p.L + tt, sb);
+        atomicAdd(p.dC + (b * p.N + n0 + n) * p.L + tt, sc);
       }
     }
+    }  // state tiles
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < kWarps * kCI * N; i += kThreads) {
+  for (int i = threadIdx.x; i < kWarps * cpw * N; i += kThreads) {
     const int wc = i / N, n = i - wc * N;
-    const int w = wc / kCI, ci = wc - w * kCI;
-    const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
-    if (ci < p.cpw && d < p.D) {
+    const int w = wc / cpw, ci = wc - w * cpw;
+    const long long d = (long long)blockIdx.x * (kWarps * cpw) + w * cpw + ci;
+    if (d < p.D) {
       const float2 v = dAacc[wc * NP + (n >> 1)];
       p.dA_part[(b * p.D + d) * p.N + n] = (n & 1) ? v.y : v.x;
     }
   }
   if (p.dD_part) {
-    for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) {
-      const int w = i / kCI, ci = i - w * kCI;
-      const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
-      if (ci < p.cpw && d < p.D) p.dD_part[b * p.D + d] = dDacc[i];
+    for (int i = threadIdx.x; i < kWarps * cpw; i += kThreads) {
+      const int w = i / cpw, ci = i - w * cpw;
+      const long long d = (long long)blockIdx.x * (kWarps * cpw) + w * cpw + ci;
+      if (d < p.D) p.dD_part[b * p.D + d] = dDacc[i];
     }
   }
   if (p.dbias_part) {
-    for (int i = threadIdx.x; i < kWarps * kCI; i += kThreads) {
-      const int w = i / kCI, ci = i - w * kCI;
-      const long long d = (long long)blockIdx.x * (kWarps * p.cpw) + w * p.cpw + ci;
-      if (ci < p.cpw && d < p.D) p.dbias_part[b * p.D + d] = dBiasacc[i];
+    for (int i = threadIdx.x; i < kWarps * cpw; i += kThreads) {
+      const int w = i / cpw, ci = i - w * cpw;
+      const long long d = (long long)blockIdx.x * (kWarps * cpw) + w * cpw + ci;
+      if (d < p.D) p.dbias_part[b * p.D + d] = dBiasacc[i];
     }
   }
 }
@@ -730,8 +767,11 @@ template <typename IO, int kItems>
 static int launch_bwd(const Params& p, cudaStream_t stream) {
   const int T = 32 * kItems;
   const size_t np2 = 2 * (size_t)((p.N + 1) / 2);
-  const size_t smem = sizeof(float) * ((2 + 2 * (size_t)kWarps) * np2 * T + 2 * (size_t)kWarps * kCI * np2 +
-                                       2 * kWarps * kCI);
+  const size_t nt = (size_t)p.state_tile < np2 ? (size_t)p.state_tile : np2;    // states per tile
+  const size_t ntiles = (np2 + nt - 1) / nt;
+  const size_t smem = sizeof(float) * ((2 + 2 * (size_t)kWarps) * nt * T + 2 * (size_t)kWarps * p.cpw * np2 +
+                                       2 * kWarps * p.cpw +
+                                       (ntiles > 1 ? (size_t)kWarps * p.cpw * 3 * kItems * 32 * 2 : 0));
   if (smem > 220 * 1024) { set_last_error("selective_scan_backward: d_state too large"); return kErrUnsupported; }
   if (int rc = set_smem(sscan_backward_kernel<IO, kItems>, smem)) return rc;
   dim3 grid((unsigned)((p.D + kWarps * p.cpw - 1) / (kWarps * p.cpw)), (unsigned)p.B);
@@ -813,7 +853,10 @@ static int sscan_check(const char* fn, const void* u, const float* dt, const flo
     set_last_error("%s: unknown io dtype %d", fn, io_dtype);
     return kErrInvalidArgument;
   }
-  if (N > 64) { set_last_error("%s: d_state > 64 is not supported", fn); return kErrUnsupported; }
+  if (N > sscan::kMaxState) {
+    set_last_error("%s: d_state > %d is not supported", fn, sscan::kMaxState);
+    return kErrUnsupported;
+  }
   if (B > 65535) { set_last_error("%s: batch > 65535 is not supported", fn); return kErrUnsupported; }
   if (B == 0 || D == 0 || L == 0 || N == 0) return kOk;
   if (!u || !dt || !A || !Bm || !Cm) { set_last_error("%s: null input pointer", fn); return kErrInvalidArgument; }
@@ -895,6 +938,8 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
   p.state_interval = sscan::state_interval_for(N);
   p.nstates = (L + p.state_interval - 1) / p.state_interval;
   p.cpw = sscan::pick_cpw(B, D);
+  p.state_tile = sscan::kStateTile;
+  if (N > sscan::kStateTile && p.cpw > 2) p.cpw = 2;   // bounds the per-channel carries in shared memory
   const int es = io_dtype == OSSM_B200_DTYPE_F32 ? 4 : 2;
   p.vec_ok = sscan::aligned16(u) && sscan::aligned16(dt) && sscan::aligned16(dout) && sscan::aligned16(du) &&
              sscan::aligned16(ddt) && (!z || (sscan::aligned16(z) && sscan::aligned16(dz))) &&

@@ -14,7 +14,8 @@ Sources of the vectors:
 * ``linoss_im_snapshot.npz``       -- the inline LinOSS-IM snapshot of
   ``tests/test_linoss_parity.py:74-204``.
 * ``dlinoss_generated.npz``, ``linoss_generated.npz``, ``diag_generated.npz``,
-  ``sdlinoss_generated.npz``, ``selective_scan_generated.npz``, ``selective_scan_delta.npz`` -- outputs of the reference itself run here
+  ``sdlinoss_generated.npz``, ``selective_scan_generated.npz``, ``selective_scan_large_state.npz``,
+  ``selective_scan_delta.npz`` -- outputs of the reference itself run here
   on seeded inputs: its pure-PyTorch recurrences (float64 and float32, grads by
   autograd) and its compiled CPU kernels (float32).
 """
@@ -58,6 +59,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("OSSM_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"),
                     help="ossm checkout (default: $OSSM_REFERENCE, else a directory 'reference' beside this repository)")
+    ap.add_argument("--only", default=None, choices=["large_state"],
+                    help="regenerate one fixture file only (the others are left as they are)")
     args = ap.parse_args()
     ref = args.reference
 
@@ -77,6 +80,38 @@ def main():
     from ossm.models.mambarec import _selective_scan_mamba
 
     ossm._kernels = kernels
+
+    # ---- E3. selective scan with large state sizes (the shipped Mamba4Rec configuration uses
+    # d_state = ssm_size = 256, configs/model/mambarec.yaml:3, mambarec.py:305) ----------------
+    import torch.nn.functional as F
+    out = {}
+    gen = torch.Generator().manual_seed(256)
+    for tag, (Bz, Dn, L, N) in (("n128", (1, 5, 70, 128)), ("n256", (2, 6, 45, 256))):
+        u = torch.randn(Bz, Dn, L, generator=gen)
+        dt = torch.rand(Bz, Dn, L, generator=gen) * 0.05
+        A = -torch.exp(torch.randn(Dn, N, generator=gen))
+        Bm = torch.randn(Bz, L, N, generator=gen)
+        Cm = torch.randn(Bz, L, N, generator=gen)
+        gate = torch.randn(Bz, Dn, L, generator=gen)
+        go = torch.randn(Bz, Dn, L, generator=gen)
+        pre = f"{tag}/"
+        for k, v in (("u", u), ("dt", dt), ("A", A), ("B", Bm), ("C", Cm), ("gate", gate), ("grad_out", go)):
+            out[pre + k] = _np(v)
+        leaves = [t.double().clone().requires_grad_(True) for t in (u, dt, A, Bm, Cm, gate)]
+        y = _selective_scan_mamba(inputs=leaves[0], dt=leaves[1], A=leaves[2], B_t=leaves[3], C_t=leaves[4])
+        o = y.double() * F.silu(leaves[5])
+        (o * go.double()).sum().backward()
+        out[pre + "py_out"] = _np(o)
+        for name, leaf in zip(("du", "ddt", "dA", "dB", "dC", "dgate"), leaves):
+            out[pre + "py_" + name] = _np(leaf.grad)
+        o2 = kernels.selective_scan(u, dt, A, Bm, Cm, gate)
+        grads = kernels.selective_scan_backward(go, u, dt, A, Bm, Cm, gate)
+        out[pre + "cpp_out"] = _np(o2)
+        for name, gr in zip(("du", "ddt", "dA", "dB", "dC", "dgate"), grads):
+            out[pre + "cpp_" + name] = _np(gr)
+    np.savez_compressed(os.path.join(HERE, "selective_scan_large_state.npz"), **out)
+    if args.only == "large_state":
+        return
 
     # ---- A. the reference's own golden JSON -----------------------------
     payload = json.load(open(os.path.join(ref, "tests", "dlinoss_reference_cases.json")))

@@ -165,6 +165,21 @@ def test_selective_scan_generated(tag):
                                rtol=1e-4, atol=5e-5)
 
 
+@pytest.mark.parametrize("tag", ["n128", "n256"])
+def test_selective_scan_large_state(tag):
+    """State sizes above 64 (the shipped Mamba4Rec configuration uses 256): the oracle against the
+    reference's Python loop (its float32 math under autograd) and compiled CPU kernel."""
+    G = _load("selective_scan_large_state.npz")
+    p = f"{tag}/"
+    u, dt, A, Bm, Cm, gate, go = (G[p + k].astype(np.float64) for k in ("u", "dt", "A", "B", "C", "gate", "grad_out"))
+    out = so.selective_scan(u, dt, A, Bm, Cm, gate)
+    grads = so.selective_scan_backward(go, u, dt, A, Bm, Cm, gate)
+    for src in ("py", "cpp"):
+        np.testing.assert_allclose(G[p + src + "_out"], out, rtol=1e-4, atol=5e-5)
+        for name, got in zip(("du", "ddt", "dA", "dB", "dC", "dgate"), grads):
+            assert so.max_rel_err(G[p + src + "_" + name], got) < 1e-4, (src, name)
+
+
 @pytest.mark.parametrize("tag", ["d1", "d2"])
 def test_diag_scan_generated(tag):
     """Complex diagonal scan of the LRU / S5 layers against the reference's two autograd
