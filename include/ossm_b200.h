@@ -144,6 +144,40 @@ int ossm_b200_lti_scan_backward_static(int variant, const float* a, const float*
  * benchmarking and tests. */
 int ossm_b200_lti_set_tuning(const char* key, int value);
 
+/* ---- projections of the D-LinOSS layer on the tensor cores ---------------------------
+ * The layer body around the scan (src/ossm/models/dlinoss.py:217-247):
+ *     bu = u B_re^T + i u B_im^T  ->  permute to [L,B,P]  ->  scan  ->  permute back  ->
+ *     y  = x.real C_re^T - x.imag C_im^T + u * D
+ * is two instances of   out[dest(m), n] = sum_k A[m,k] W[n,k]  (+ diag[n] * aux[dest(m), n])
+ * where dest() is the row permutation between batch-major (b*L + l) and time-major (l*B + b)
+ * row order, so the permute copies and the real / imaginary splits disappear:
+ *     prologue  A = u [B*L, H],   W = rows (B_re[p], B_im[p]) interleaved [2P, H],
+ *               out = bu viewed as float [L*B, 2P], row_map 1
+ *     epilogue  A = x viewed as float [L*B, 2P], W = columns (C_re[:,p], -C_im[:,p]) interleaved [H, 2P],
+ *               out = y [B*L, H], aux = u, diag = D, row_map 2
+ * and likewise in the backward pass.  The product is evaluated on the tcgen05 tensor cores as
+ * three TF32 products of hi / lo operand halves (float32-level accuracy, float32 accumulation).
+ *
+ *   A          float32 [M, K] dense row-major, 16-byte aligned, K a multiple of 4
+ *   W_hi, W_lo float32 [N, K]: the two halves of the weight matrix made by ossm_b200_split_tf32
+ *   out, aux   float32, row pitch ldo floats (aux is read at the same position out is written)
+ *   diag       float32 [N]; aux and diag are both NULL or both given
+ *   row_map    0: dest(m) = m;  1: m = b*length + l -> l*batch + b;  2: m = l*batch + b -> b*length + l
+ *   col_block, plane_stride
+ *              the output may be split into planes of col_block columns each, plane_stride floats apart
+ *              (column n -> plane n / col_block, column n % col_block; ldo is then the row pitch inside a
+ *              plane): the layout a reduce-scatter over the output columns consumes.  col_block <= 0 or
+ *              >= N means one plain [M, N] matrix.
+ */
+#define OSSM_B200_ROWS_IDENTITY 0
+#define OSSM_B200_ROWS_BATCH_TO_TIME 1
+#define OSSM_B200_ROWS_TIME_TO_BATCH 2
+int ossm_b200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, ossm_b200_stream_t stream);
+int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, float* out, const float* aux,
+                          const float* diag, int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t col_block,
+                          int64_t plane_stride, int row_map, int64_t batch, int64_t length,
+                          ossm_b200_stream_t stream);
+
 /* ---- generic LinOSS scan (complex 2x2 per channel, forcing per step) --------
  * Replaces ossm::linoss_scan (src/ossm/csrc/linoss_scan.cpp:115-146; bindings.cpp:160)
  * and the Python-loop backward of _LinossScanFn (src/ossm/models/linoss.py:83-151).

@@ -45,6 +45,8 @@ SIGNATURES = {
                                          + [c_int, c_void_p]),
     "ossm_b200_selective_scan_backward": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 11 + [c_size_t]
                                           + [c_int64] * 4 + [c_int, c_void_p]),
+    "ossm_b200_split_tf32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "ossm_b200_gemm_tf32x3": (c_int, [c_void_p] * 6 + [c_int64] * 6 + [c_int, c_int64, c_int64, c_void_p]),
     "ossm_b200_linoss_scan_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_linoss_scan_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

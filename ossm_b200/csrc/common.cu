@@ -73,6 +73,13 @@ bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, u
                    CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                                  uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+  if (box_cols * 4 != 128) return false;
+  return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, pitch_bytes, box_cols, box_rows,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                             uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
   return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, cols, rows, pitch_bytes, box_cols, box_rows,
@@ -146,7 +153,7 @@ int ossm_b200_device_status(int* status, int clear) {
   }
   // first non-zero word wins; every word is cleared when asked
   int (*const words[])(int*, int) = {status_common, status_lti, status_linoss_generic, status_sdlinoss,
-                                     status_selective_scan};
+                                     status_selective_scan, status_layer};
   int first = 0;
   for (auto fn : words) {
     int v = 0;

@@ -54,6 +54,7 @@ int status_lti(int* status, int clear);
 int status_linoss_generic(int* status, int clear);
 int status_sdlinoss(int* status, int clear);
 int status_selective_scan(int* status, int clear);
+int status_layer(int* status, int clear);
 
 // ---- tensor maps (host) ----------------------------------------------------
 // 2-D fp32 view [rows, cols] with row pitch `pitch_bytes`; box = box_cols x box_rows.
@@ -62,6 +63,10 @@ int status_selective_scan(int* status, int clear);
 // plain-load kernel instead.
 bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                             uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+// Same with the 128-byte shared-memory swizzle (box_cols * 4 must be 128): the layout the tensor-core
+// matrix descriptors of the projection kernels expect.
+bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                                  uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
 // Same for 16-bit elements (bf16 payloads are moved as raw 16-bit words).
 bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                             uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,

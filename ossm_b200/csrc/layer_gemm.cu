@@ -1,0 +1,374 @@
+// Projections of the D-LinOSS layer on the 5th-generation tensor cores (tcgen05, sm_100a).
+//
+// The layer body (src/ossm/models/dlinoss.py:217-247) wraps the scan in two pairs of real GEMMs,
+//     bu = u B_re^T + i u B_im^T            (prologue)      y = Re(C x) + D u       (epilogue)
+// plus permutes between the batch-major activations [B, L, H] and the time-major scan operands
+// [L, B, P] complex64.  Both are instances of
+//     out[dest(m), n] = sum_k A[m, k] * W[n, k]  (+ diag[n] * aux[dest(m), n])
+// with A an activation matrix (rows = (b, l) or (l, b) pairs, K contiguous), W a small weight
+// matrix (K contiguous) and dest(m) the row permutation between the two orders, so the permute
+// copies and the real / imaginary split of the reference disappear into the GEMM's addressing:
+//   prologue   A = u [B*L, H],    W = (B_re | B_im) interleaved [2P, H],  out = bu viewed [L*B, 2P]
+//   epilogue   A = x [L*B, 2P],   W = (C_re | -C_im) interleaved [H, 2P], out = y [B*L, H], aux = u, diag = D
+// and their transposes in the backward pass (grad_x from grad_y, grad_u from grad_bu).
+//
+// Accuracy: the parity bound of the layer is 1e-5, which plain TF32 (10-bit mantissa) misses by two
+// orders of magnitude.  Every float32 operand is therefore split into two TF32 numbers,
+//     v = hi + lo,   hi = v with the 13 low mantissa bits cleared,   lo = v - hi  (exact),
+// and the product is accumulated as  hi*hi + hi*lo + lo*hi  in the float32 accumulator (the dropped
+// lo*lo term is below 2^-22 relative).  The weights are split once by split_tf32_kernel; the
+// activations are split inside the GEMM by four "splitter" warps between the TMA load and the MMA.
+//
+// Kernel structure (one CTA = one 128 x BN output tile, K walked in slices of 32 floats = 128 B):
+//   warp 0       producer: one lane issues the TMA loads (SWIZZLE_128B) of A, W_hi, W_lo per slice
+//   warp 1       allocates the accumulator in tensor memory; one lane issues 12 tcgen05.mma per slice
+//                (4 K-steps of 8 x 3 operand combinations) and commits the stage back to the producer
+//   warps 2..5   splitters: rewrite the A slice in place as hi and write lo beside it; afterwards the
+//                epilogue: tcgen05.ld the accumulator (lane = output row), add diag*aux, store
+// Stages are handed over with mbarriers; every wait is bounded in time and a wait that gives up sets
+// the device status word and lets the CTA run to its normal end (tensor memory is always released).
+// No cluster launch and no multicast: the same kernel runs unchanged under several ranks per node.
+#include "common.cuh"
+
+#include "../../include/ossm_b200.h"
+
+namespace ossm_b200 {
+OSSM_B200_STATUS_ACCESSOR(status_layer)
+namespace layer {
+
+constexpr int kBM = 128;            // output rows per CTA = TMEM lanes
+constexpr int kBK = 32;             // floats per K slice = one 128-byte swizzle row
+constexpr int kThreads = 192;       // producer warp, MMA warp, four splitter / epilogue warps
+constexpr int kATile = kBM * kBK * 4;   // 16 KiB
+
+enum RowMap : int { kRowIdentity = 0, kRowBatchToTime = 1, kRowTimeToBatch = 2 };
+
+struct GemmParams {
+  float* out;            // [rows_out, ldo]
+  const float* aux;      // nullable, same indexing as out
+  const float* diag;     // nullable, [N]
+  long long M, N, K;
+  long long ldo;         // floats between output rows
+  long long col_block;   // output columns per plane (N when the output is one matrix)
+  long long plane_stride;  // floats between planes: column n goes to plane n / col_block, column n % col_block
+  long long batch, length;   // for the row maps: M = batch * length
+  int row_map;
+  int stages;
+};
+
+__device__ __forceinline__ long long dest_row(const GemmParams& p, long long m) {
+  if (p.row_map == kRowBatchToTime) {           // m = b * L + l  ->  l * B + b
+    const long long b = m / p.length, l = m - b * p.length;
+    return l * p.batch + b;
+  }
+  if (p.row_map == kRowTimeToBatch) {           // m = l * B + b  ->  b * L + l
+    const long long l = m / p.batch, b = m - l * p.batch;
+    return b * p.length + l;
+  }
+  return m;
+}
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, TF32 inputs, float32 accumulate, issued by one thread.
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 32 consecutive accumulator columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): groups of 8 rows are 1024 B
+// apart (stride byte offset), the leading byte offset is unused for this layout (1), descriptor
+// version 1 (sm_100), layout type 2 = SWIZZLE_128B.  `addr` must lie in a 1024-byte aligned tile;
+// advancing it by 32 B selects the next K step of 8 TF32 values inside the swizzle row.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                           // leading byte offset (16-byte units), bits [16,30)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                           // descriptor version, bits [46,48)
+  d |= (uint64_t)2 << 61;                           // layout type, bits [61,64)
+  return d;
+}
+
+// Instruction descriptor: float32 accumulator (bits [4,6) = 1), TF32 A and B (bits [7,10), [10,13) = 2),
+// both operands K-major (bits 15, 16 = 0), N >> 3 in bits [17,23), M >> 4 in bits [24,29).
+__host__ __device__ constexpr uint32_t instr_desc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// Shared memory: [0,1024) barriers + TMEM address | stages x (A_hi 16K | A_lo 16K | W_hi BN*128 | W_lo BN*128)
+template <int BN>
+struct Smem {
+  static constexpr int kWTile = BN * kBK * 4;
+  static constexpr int kStage = 2 * kATile + 2 * kWTile;
+  static constexpr size_t bytes(int stages) { return 1024 + (size_t)stages * kStage + 1024; }   // + alignment slack
+};
+
+constexpr int kMaxStages = 4;
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_whi,
+                   const __grid_constant__ CUtensorMap tm_wlo, GemmParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  // swizzled tiles need 1024-byte alignment
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);            // [stages] TMA landed
+  uint64_t* split = full + kMaxStages;                           // [stages] A split into hi / lo
+  uint64_t* empty = split + kMaxStages;                          // [stages] MMAs of the stage finished
+  uint64_t* acc_done = empty + kMaxStages;                       // accumulator complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  unsigned char* stage0 = smem + 1024;
+  using S = Smem<BN>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long m0 = (long long)blockIdx.x * kBM;
+  const long long n0 = (long long)blockIdx.y * BN;
+  const int nslices = (int)((p.K + kBK - 1) / kBK);
+  const int stages = p.stages;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_whi);
+    prefetch_tensormap(&tm_wlo);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&split[s], 128);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);       // BN float32 columns x 128 lanes
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int s = 0; s < nslices; ++s) {
+        const int b = s % stages;
+        if (s >= stages && !mbar_wait(&empty[b], ((s / stages) - 1) & 1, kWaitLimitNs, kStatusMmaTimeout)) break;
+        unsigned char* st = stage0 + (size_t)b * S::kStage;
+        mbar_expect_tx(&full[b], kATile + 2 * S::kWTile);
+        tma_load_2d(st, &tm_a, &full[b], s * kBK, (int32_t)m0);
+        tma_load_2d(st + 2 * kATile, &tm_whi, &full[b], s * kBK, (int32_t)n0);
+        tma_load_2d(st + 2 * kATile + S::kWTile, &tm_wlo, &full[b], s * kBK, (int32_t)n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_tf32(kBM, BN);
+      bool ok = true;
+      for (int s = 0; s < nslices && ok; ++s) {
+        const int b = s % stages;
+        const uint32_t ph = (s / stages) & 1;
+        ok = mbar_wait(&full[b], ph) && mbar_wait(&split[b], ph);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(stage0 + (size_t)b * S::kStage);
+        const uint32_t a_hi = st, a_lo = st + kATile, w_hi = st + 2 * kATile, w_lo = w_hi + S::kWTile;
+#pragma unroll
+        for (int k = 0; k < kBK / 8; ++k) {
+          const uint32_t off = k * 32;     // 8 TF32 values = 32 bytes along the swizzle row
+          umma_tf32(tmem_acc, smem_desc_sw128(a_hi + off), smem_desc_sw128(w_hi + off), idesc, (s | k) != 0);
+          umma_tf32(tmem_acc, smem_desc_sw128(a_hi + off), smem_desc_sw128(w_lo + off), idesc, 1);
+          umma_tf32(tmem_acc, smem_desc_sw128(a_lo + off), smem_desc_sw128(w_hi + off), idesc, 1);
+        }
+        umma_commit(&empty[b]);            // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_done);               // everything issued so far: the accumulator is final
+    }
+  } else {
+    // ---- splitters: hi in place, lo beside it (same swizzled positions, so the layout is irrelevant here)
+    const int t = threadIdx.x - 64;        // 0..127
+    bool ok = true;
+    for (int s = 0; s < nslices; ++s) {
+      const int b = s % stages;
+      ok = mbar_wait(&full[b], (s / stages) & 1);
+      if (!ok) break;
+      float4* hi = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage);
+      float4* lo = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage + kATile);
+#pragma unroll
+      for (int i = 0; i < kATile / 16 / 128; ++i) {
+        const float4 v = hi[i * 128 + t];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+        hi[i * 128 + t] = h;
+        lo[i * 128 + t] = l;
+      }
+      fence_proxy_async();                 // generic-proxy writes become visible to the tensor core
+      mbar_arrive(&split[b]);
+    }
+    // ---- epilogue: lane quarter (warp % 4) of the accumulator, 32 columns at a time
+    if (ok) ok = mbar_wait(acc_done, 0, kWaitLimitNs, kStatusMmaTimeout);
+    if (ok) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const long long m = m0 + q * 32 + lane;
+      const bool row_ok = m < p.M;
+      const long long drow = row_ok ? dest_row(p, m) : 0;
+      float* out_row = p.out + drow * p.ldo;
+      const float* aux_row = p.aux ? p.aux + drow * p.ldo : nullptr;
+      const bool vec = ((p.ldo & 3) == 0) && ((p.plane_stride & 3) == 0) && ((p.col_block & 31) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0) &&
+                       (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        __syncwarp();
+        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);   // whole warp takes part
+        const long long n = n0 + c0;
+        if (!row_ok || n >= p.N) continue;
+        if (vec && n + 32 <= p.N) {
+          // 32 columns of one plane (col_block is a multiple of 32 here)
+          const long long off = (n / p.col_block) * p.plane_stride + (n % p.col_block);
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (aux_row) {
+              const float4 a = *reinterpret_cast<const float4*>(aux_row + off + j);
+              const float4 d = *reinterpret_cast<const float4*>(p.diag + n + j);
+              o.x = fmaf(d.x, a.x, o.x); o.y = fmaf(d.y, a.y, o.y); o.z = fmaf(d.z, a.z, o.z); o.w = fmaf(d.w, a.w, o.w);
+            }
+            *reinterpret_cast<float4*>(out_row + off + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32 && n + j < p.N; ++j) {
+            const long long off = ((n + j) / p.col_block) * p.plane_stride + ((n + j) % p.col_block);
+            float o = v[j];
+            if (aux_row) o = fmaf(p.diag[n + j], aux_row[off], o);
+            out_row[off] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, BN);
+  }
+}
+
+// hi / lo TF32 split of a weight matrix (done once per call of the layer, a few hundred KB).
+__global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
+                                  long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = w[i];
+  const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+  hi[i] = h;
+  lo[i] = v - h;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUtensorMap& tl, GemmParams p,
+                       cudaStream_t stream) {
+  using S = Smem<BN>;
+  int stages = kMaxStages;
+  while (stages > 1 && S::bytes(stages) > 220 * 1024) --stages;
+  const int nslices = (int)((p.K + kBK - 1) / kBK);
+  if (stages > nslices) stages = nslices;
+  p.stages = stages;
+  const size_t smem = S::bytes(stages);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN>), smem)) return rc;
+  dim3 grid((unsigned)((p.M + kBM - 1) / kBM), (unsigned)((p.N + BN - 1) / BN));
+  gemm_tf32x3_kernel<BN><<<grid, kThreads, smem, stream>>>(ta, th, tl, p);
+  return check_cuda(cudaGetLastError(), "gemm_tf32x3_kernel launch");
+}
+
+}  // namespace layer
+}  // namespace ossm_b200
+
+extern "C" {
+
+using namespace ossm_b200;
+
+int ossm_b200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, cudaStream_t stream) {
+  if (count < 0) { set_last_error("split_tf32: negative count"); return kErrInvalidArgument; }
+  if (count == 0) return kOk;
+  if (!w || !w_hi || !w_lo) { set_last_error("split_tf32: null pointer"); return kErrInvalidArgument; }
+  layer::split_tf32_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(w, w_hi, w_lo, count);
+  return check_cuda(cudaGetLastError(), "split_tf32_kernel launch");
+}
+
+int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, float* out, const float* aux,
+                          const float* diag, int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t col_block,
+                          int64_t plane_stride, int row_map, int64_t batch, int64_t length, cudaStream_t stream) {
+  if (M < 0 || N < 0 || K < 0) { set_last_error("gemm_tf32x3: negative extent"); return kErrInvalidArgument; }
+  if (M == 0 || N == 0) return kOk;
+  if (!A || !W_hi || !W_lo || !out || (aux != nullptr) != (diag != nullptr)) {
+    set_last_error("gemm_tf32x3: null pointer (aux and diag come together)");
+    return kErrInvalidArgument;
+  }
+  if (K == 0 || (K & 3) != 0) { set_last_error("gemm_tf32x3: K must be a positive multiple of 4"); return kErrUnsupported; }
+  if (row_map < layer::kRowIdentity || row_map > layer::kRowTimeToBatch ||
+      (row_map != layer::kRowIdentity && (batch <= 0 || length <= 0 || batch * length != M))) {
+    set_last_error("gemm_tf32x3: bad row map (batch * length must equal M)");
+    return kErrInvalidArgument;
+  }
+  if (col_block <= 0 || col_block > N) { col_block = N; plane_stride = 0; }
+  if (ldo < col_block) { set_last_error("gemm_tf32x3: output pitch smaller than the column block"); return kErrInvalidArgument; }
+  if (M > 0x7fffffffLL - layer::kBM || N > 0x7fffffffLL - 256) { set_last_error("gemm_tf32x3: extent too large"); return kErrInvalidArgument; }
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap ta, th, tl;
+  if (!make_tensor_map_2d_f32_sw128(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K * 4, layer::kBK, layer::kBM) ||
+      !make_tensor_map_2d_f32_sw128(&th, W_hi, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kBK, BN) ||
+      !make_tensor_map_2d_f32_sw128(&tl, W_lo, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kBK, BN)) {
+    set_last_error("gemm_tf32x3: operands must be 16-byte aligned, dense row-major matrices");
+    return kErrUnsupported;
+  }
+  layer::GemmParams p{};
+  p.out = out; p.aux = aux; p.diag = diag;
+  p.col_block = col_block; p.plane_stride = plane_stride;
+  p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.batch = batch; p.length = length; p.row_map = row_map;
+  if (BN == 256) return layer::launch_gemm<256>(ta, th, tl, p, stream);
+  if (BN == 128) return layer::launch_gemm<128>(ta, th, tl, p, stream);
+  return layer::launch_gemm<64>(ta, th, tl, p, stream);
+}
+
+}  // extern "C"

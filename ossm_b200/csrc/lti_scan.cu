@@ -715,18 +715,18 @@ struct Tuning {
   int force_plain = 0;
   int segments = 0;   // 0 = automatic
   int twolevel = 1;   // 1 = two-level kernels for long sequences of few series, 0 = never
-  int tl_fwd_ring = 4;
-  int tl_bwd_ring = 3;
+  int tl_fwd_ring = 0;   // stages of the two-level kernels, 0 = by CTA count (measured best)
+  int tl_bwd_ring = 0;
 };
 static Tuning g_tuning;
 
 // Long sequences of few series take the two-level kernels (lti_scan_twolevel.cuh): enough series for
-// 64 CTAs of 16 columns, too few for the wide kernels to fill the GPU, and at least four tiles of time.
+// 96 CTAs of 16 columns, too few for the wide kernels to fill the GPU, and at least four tiles of time.
 // The upper bound also keeps the backward's partial sums (6 * 8 * N floats) inside the built-in
 // scratch of the allocation-free entry, so that entry and the workspace entry always take the same path.
 static bool use_twolevel(int variant, long long L, long long N) {
   if (!g_tuning.twolevel || g_tuning.segments > 0 || g_tuning.force_plain || variant == kDiag) return false;
-  return N >= 1024 && N <= 8192 && L >= 4 * kTlRows;
+  return N >= 1536 && N <= 8192 && L >= 4 * kTlRows;
 }
 
 template <typename K>
@@ -792,10 +792,11 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
     memset(&tm2, 0, sizeof(tm2));
     if (make_tensor_map_2d_f32(&tm2, p.bu, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2,
                                kTlRows)) {
-      q.ring = g_tuning.tl_fwd_ring;
+      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
+      // one CTA per SM wants a deep ring of its own; with several waves the co-resident CTAs overlap instead
+      q.ring = g_tuning.tl_fwd_ring > 0 ? g_tuning.tl_fwd_ring : ((int)ctas <= sm_count() ? 3 : 4);
       const size_t smem = 4096 + (size_t)q.ring * kTlTileBytes;
       if (int rc = set_smem(lti_forward_twolevel_kernel<V, kOut>, smem)) return rc;
-      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
       lti_forward_twolevel_kernel<V, kOut><<<ctas, kTlThreads, smem, stream>>>(tm2, q);
       return check_cuda(cudaGetLastError(), "lti_forward_twolevel_kernel launch");
     }
@@ -873,10 +874,11 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
     if (make_tensor_map_2d_f32(&tb, p.bu, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2, kTlRows) &&
         make_tensor_map_2d_f32(&tg, p.grad_x, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2,
                                kTlRows)) {
-      q.ring = g_tuning.tl_bwd_ring;
+      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
+      // a single stage lets two CTAs share an SM (68 KiB each), which wins once there are several waves
+      q.ring = g_tuning.tl_bwd_ring > 0 ? g_tuning.tl_bwd_ring : ((int)ctas <= sm_count() ? 2 : 1);
       const size_t smem = 4096 + (size_t)q.ring * 2 * kTlTileBytes;
       if (int rc = set_smem(lti_backward_twolevel_kernel<V>, smem)) return rc;
-      const unsigned ctas = (unsigned)((p.N + kTlCols - 1) / kTlCols);
       lti_backward_twolevel_kernel<V><<<ctas, kTlThreads, smem, stream>>>(tb, tg, q);
       if (int rc = check_cuda(cudaGetLastError(), "lti_backward_twolevel_kernel launch")) return rc;
       const unsigned blocks = (unsigned)((p.P + kPgCh - 1) / kPgCh);
@@ -968,8 +970,8 @@ int ossm_b200_lti_set_tuning(const char* key, int value) {
   if (!strcmp(key, "force_plain")) { g_tuning.force_plain = value != 0; return kOk; }
   if (!strcmp(key, "segments") && value >= 0 && value <= 64) { g_tuning.segments = value; return kOk; }
   if (!strcmp(key, "twolevel")) { g_tuning.twolevel = value != 0; return kOk; }
-  if (!strcmp(key, "tl_fwd_ring") && value >= 1 && value <= 6) { g_tuning.tl_fwd_ring = value; return kOk; }
-  if (!strcmp(key, "tl_bwd_ring") && value >= 1 && value <= 3) { g_tuning.tl_bwd_ring = value; return kOk; }
+  if (!strcmp(key, "tl_fwd_ring") && value >= 0 && value <= 6) { g_tuning.tl_fwd_ring = value; return kOk; }
+  if (!strcmp(key, "tl_bwd_ring") && value >= 0 && value <= 3) { g_tuning.tl_bwd_ring = value; return kOk; }
   set_last_error("lti_set_tuning: unknown key or value out of range: %s=%d", key, value);
   return kErrInvalidArgument;
 }

@@ -1,0 +1,133 @@
+"""The D-LinOSS layer body as one op: ``y = Re(C x) + D u`` with ``x = scan(u B^T)``.
+
+Counterpart of ``DampedLinOSSLayer.forward`` after the parameter projection
+(``src/ossm/models/dlinoss.py:217-247``, ``_apply_dlinoss`` :269-278).  The reference runs four real
+library GEMMs (``u B_re^T``, ``u B_im^T``, ``x.real C_re^T``, ``x.imag C_im^T``), two permute copies
+between batch-major ``[B,L,*]`` and time-major ``[L,B,*]`` and the scan.  Here the projections run on
+the tcgen05 tensor cores through :func:`ossm_b200.kernels.gemm_tf32x3` (three TF32 products of split
+operands: float32-level accuracy), which read and write the time-major complex scan operands in place:
+
+  forward    bu = gemm(u, [B_re|B_im])  ->  x = scan(bu)  ->  y = gemm(x, [C_re|-C_im]) + D*u   (fused)
+  backward   grad_x = gemm(grad_y, [C_re|-C_im]^T)  ->  scan backward  ->
+             grad_u = gemm(grad_bu, [B_re|B_im]^T) + D*grad_y                                   (fused)
+
+No permute copy, no real / imaginary split and no separate ``D*u`` pass exist.  The two weight
+gradients (``grad_B``, ``grad_C``: reductions over all ``B*L`` rows into ``[2P, H]``) are strided
+batched library GEMMs (cuBLAS through ``torch.bmm``, float32).
+
+Parameters have the reference's shapes: ``B [P, H, 2]``, ``C [H, P, 2]`` (real / imaginary last,
+``dlinoss.py:93-98``), ``D [H]``; ``a_diag, g_diag, step [P]`` are the projected coefficients the
+layer passes to ``run_dlinoss``.  CUDA float32 only; there is no other path.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import kernels
+
+__all__ = ["dlinoss_layer", "DLinossLayerFn", "pack_input_weights", "pack_output_weights"]
+
+
+def pack_input_weights(B: Tensor) -> Tensor:
+    """``[P, H, 2] -> [2P, H]`` with rows ``(B_re[p], B_im[p])`` interleaved: the GEMM then writes ``bu`` as
+    interleaved (re, im) pairs, i.e. complex64."""
+    P, H, _ = B.shape
+    return B.permute(0, 2, 1).reshape(2 * P, H).contiguous()
+
+
+def pack_output_weights(C: Tensor) -> Tensor:
+    """``[H, P, 2] -> [H, 2P]`` with columns ``(C_re[:,p], -C_im[:,p])`` interleaved, so that the product
+    with the interleaved (re, im) pairs of ``x`` is ``Re(C x)``."""
+    H, P, _ = C.shape
+    sign = torch.tensor([1.0, -1.0], dtype=C.dtype, device=C.device)
+    return (C * sign).reshape(H, 2 * P).contiguous()
+
+
+class DLinossLayerFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, variant: str, a_diag: Tensor, g_diag: Tensor, step: Tensor, B: Tensor, C: Tensor, D: Tensor,
+                u: Tensor) -> Tensor:
+        batch, length, hidden = u.shape
+        ssm = a_diag.numel()
+        dev = u.device
+        u2 = u.contiguous().view(batch * length, hidden)
+        w_in = pack_input_weights(B)                         # [2P, H]
+        w_out = pack_output_weights(C)                       # [H, 2P]
+        bu = torch.empty((length, batch, ssm), dtype=torch.complex64, device=dev)
+        kernels.gemm_tf32x3(u2, *kernels.split_tf32(w_in), torch.view_as_real(bu).view(length * batch, 2 * ssm),
+                            row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=length)
+        needs_grad = any(ctx.needs_input_grad)
+        x, _, carries = kernels.lti_scan_forward(variant, a_diag, g_diag, step, bu, want_carries=needs_grad)
+        y = torch.empty((batch, length, hidden), dtype=torch.float32, device=dev)
+        kernels.gemm_tf32x3(torch.view_as_real(x).view(length * batch, 2 * ssm), *kernels.split_tf32(w_out),
+                            y.view(batch * length, hidden), aux=u2, diag=D.contiguous(),
+                            row_map=kernels.ROWS_TIME_TO_BATCH, batch=batch, length=length)
+        ctx.variant = variant
+        if needs_grad:
+            ctx.save_for_backward(a_diag, g_diag, step, w_in, w_out, D, u2, bu, x, carries)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        a_diag, g_diag, step, w_in, w_out, D, u2, bu, x, carries = ctx.saved_tensors
+        length, batch, ssm = bu.shape
+        hidden = u2.size(1)
+        dev = u2.device
+        gy = grad_y.contiguous().view(batch * length, hidden)
+        # grad_x (torch's convention for complex tensors: d/dre + i d/dim) = grad_y C_re - i grad_y C_im
+        grad_x = torch.empty_like(bu)
+        kernels.gemm_tf32x3(gy, *kernels.split_tf32(w_out.t().contiguous()),
+                            torch.view_as_real(grad_x).view(length * batch, 2 * ssm),
+                            row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=length)
+        grad_a, grad_g, grad_step, grad_bu = kernels.lti_scan_backward(ctx.variant, a_diag, g_diag, step, bu, carries,
+                                                                       grad_x)
+        grad_u = torch.empty((batch, length, hidden), dtype=torch.float32, device=dev)
+        gbu2 = torch.view_as_real(grad_bu).view(length, batch, 2 * ssm)
+        kernels.gemm_tf32x3(gbu2.view(length * batch, 2 * ssm), *kernels.split_tf32(w_in.t().contiguous()),
+                            grad_u.view(batch * length, hidden), aux=gy, diag=D.contiguous(),
+                            row_map=kernels.ROWS_TIME_TO_BATCH, batch=batch, length=length)
+        # weight gradients: sums over every (b, l) row; one strided batched library GEMM each
+        u3 = u2.view(batch, length, hidden)
+        gy3 = gy.view(batch, length, hidden)
+        x2 = torch.view_as_real(x).view(length, batch, 2 * ssm)
+        grad_w_in = torch.bmm(gbu2.permute(1, 2, 0), u3).sum(0)                      # [2P, H]
+        grad_w_out = torch.bmm(gy3.transpose(1, 2), x2.permute(1, 0, 2)).sum(0)      # [H, 2P]
+        grad_D = (gy * u2).sum(0)
+        grad_B = grad_w_in.view(ssm, 2, hidden).permute(0, 2, 1).contiguous()
+        sign = torch.tensor([1.0, -1.0], dtype=grad_w_out.dtype, device=dev)
+        grad_C = grad_w_out.view(hidden, ssm, 2) * sign
+        return None, grad_a, grad_g, grad_step, grad_B, grad_C, grad_D, grad_u
+
+
+def dlinoss_layer(variant: str, a_diag: Tensor, g_diag: Tensor, step: Tensor, B: Tensor, C: Tensor, D: Tensor,
+                  u: Tensor) -> Tensor:
+    """``y [B, L, H]`` of the D-LinOSS layer body for ``u [B, L, H]`` (float32, CUDA)."""
+    variant = variant.lower()
+    if variant not in ("imex1", "imex2", "im", "ex"):
+        raise ValueError(f"Unknown D-LinOSS variant '{variant}'.")
+    if u.dim() != 3:
+        raise ValueError("inputs must have shape (batch, length, hidden_dim).")
+    if not u.is_cuda or u.dtype != torch.float32:
+        raise RuntimeError("ossm_b200: dlinoss_layer needs float32 CUDA tensors (there is no CPU path)")
+    batch, length, hidden = u.shape
+    ssm = a_diag.numel()
+    if tuple(B.shape) != (ssm, hidden, 2) or tuple(C.shape) != (hidden, ssm, 2) or tuple(D.shape) != (hidden,):
+        raise ValueError("B must be [P, H, 2], C [H, P, 2] and D [H]")
+    if length == 0 or batch == 0:
+        return u.new_zeros(batch, length, hidden)
+    # TMA wants 16-byte rows: hidden a multiple of 4 floats, 2P a multiple of 4.  Odd sizes are padded with
+    # zero channels / idle oscillators (zero rows of B, zero columns of C), which leave the result unchanged
+    # and whose gradients are dropped by the slicing below.
+    pad_h = (-hidden) % 4
+    pad_p = ssm % 2
+    if pad_h or pad_p:
+        pad = torch.nn.functional.pad
+        u = pad(u, (0, pad_h))
+        B = pad(B, (0, 0, 0, pad_h, 0, pad_p))
+        C = pad(C, (0, 0, 0, pad_p, 0, pad_h))
+        D = pad(D, (0, pad_h))
+        a_diag, g_diag = pad(a_diag, (0, pad_p)), pad(g_diag, (0, pad_p))
+        step = pad(step, (0, pad_p), value=0.5)
+    y = DLinossLayerFn.apply(variant, a_diag.contiguous(), g_diag.contiguous(), step.contiguous(), B, C, D, u)
+    return y[..., :hidden] if pad_h else y

@@ -61,13 +61,15 @@ def _copy2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width: i
 
 def scan_from_host(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu_host: Tensor,
                    grad_x_host: Optional[Tensor], x_host: Tensor, grad_bu_host: Optional[Tensor] = None, *,
-                   slices: int = 8, device: Optional[torch.device] = None
+                   slices: int = 8, device: Optional[torch.device] = None, copies_only: bool = False
                    ) -> Optional[Tuple[Tensor, Optional[Tensor], Tensor]]:
     """Forward (and, when ``grad_x_host`` is given, backward) of the oscillator scan on
     pinned host tensors ``[L, B, P]`` complex64; results are written to ``x_host`` /
     ``grad_bu_host``.  ``a, g, step`` are device tensors ``[P]``.  Returns the coefficient
     gradients ``(grad_a, grad_g, grad_step)`` on the device (``None`` without backward).
-    The call returns when all results are in host memory.
+    The call returns when all results are in host memory.  ``copies_only=True`` moves the same bytes
+    through the same pipeline without launching the kernels (the results are then meaningless): the
+    ceiling the host and PCIe side puts on this call, for measurements.
     """
     dev = device or a.device
     L, B, P = bu_host.shape
@@ -110,19 +112,21 @@ def scan_from_host(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, b
                 arrived_gx = torch.cuda.Event()
                 arrived_gx.record(up)
             main.wait_event(arrived_bu)
-            x, _, carries = kernels.lti_scan_forward(variant, a, g, step, views["bu"], want_carries=backward)
-            views["x"].copy_(x)     # device-to-device into the staging buffer (keeps `x` out of the copy stream)
+            if not copies_only:
+                x, _, carries = kernels.lti_scan_forward(variant, a, g, step, views["bu"], want_carries=backward)
+                views["x"].copy_(x)     # device-to-device into the staging buffer (keeps `x` out of the copy stream)
             done_fwd = torch.cuda.Event()
             done_fwd.record(main)
             down.wait_event(done_fwd)
             _copy2d(x_host.data_ptr() + off, pitch_h, views["x"].data_ptr(), width, width, L, _D2H, down)
             if backward:
                 main.wait_event(arrived_gx)
-                ga, gg, gs, gbu = kernels.lti_scan_backward(variant, a, g, step, views["bu"], carries, views["gx"])
-                views["gbu"].copy_(gbu)
-                part = (ga, gg, gs)
-                grads = part if grads is None else tuple(
-                    (p + q) if p is not None else None for p, q in zip(grads, part))
+                if not copies_only:
+                    ga, gg, gs, gbu = kernels.lti_scan_backward(variant, a, g, step, views["bu"], carries, views["gx"])
+                    views["gbu"].copy_(gbu)
+                    part = (ga, gg, gs)
+                    grads = part if grads is None else tuple(
+                        (p + q) if p is not None else None for p, q in zip(grads, part))
                 done_bwd = torch.cuda.Event()
                 done_bwd.record(main)
                 down.wait_event(done_bwd)

@@ -606,6 +606,63 @@ def set_sdlinoss_tuning(key: str, value: int) -> None:
     _lib.check(_lib.load().ossm_b200_sdlinoss_set_tuning(key.encode(), int(value)), "sdlinoss_set_tuning")
 
 
+# ---- projections of the D-LinOSS layer on the tensor cores ----------------------
+ROWS_IDENTITY, ROWS_BATCH_TO_TIME, ROWS_TIME_TO_BATCH = 0, 1, 2
+
+
+def split_tf32(w: Tensor) -> Tuple[Tensor, Tensor]:
+    """``(hi, lo)`` halves of a float32 matrix: ``hi`` keeps the 10 mantissa bits a TF32 tensor-core operand
+    has, ``lo = w - hi`` the rest; ``hi*hi + hi*lo + lo*hi`` reproduces float32 products."""
+    _require_cuda("w", w)
+    if w.dtype != torch.float32:
+        raise RuntimeError("ossm_b200: split_tf32 needs a float32 tensor")
+    w = w.contiguous()
+    hi, lo = torch.empty_like(w), torch.empty_like(w)
+    if w.numel():
+        with torch.cuda.device(w.device):
+            rc = _lib.load().ossm_b200_split_tf32(_p(w), _p(hi), _p(lo), w.numel(), _stream(w.device))
+        _lib.check(rc, "split_tf32")
+    return hi, lo
+
+
+def gemm_tf32x3(A: Tensor, w_hi: Tensor, w_lo: Tensor, out: Tensor, *, aux: Optional[Tensor] = None,
+                diag: Optional[Tensor] = None, row_map: int = ROWS_IDENTITY, batch: int = 0, length: int = 0,
+                col_block: int = 0) -> Tensor:
+    """``out[dest(m), n] = sum_k A[m,k] W[n,k] (+ diag[n] * aux[dest(m), n])`` on the tcgen05 tensor cores with
+    float32-level accuracy (three TF32 products of split operands).  ``A [M,K]``, ``w_hi / w_lo [N,K]`` (from
+    :func:`split_tf32`) and ``out / aux [M,N]`` are dense float32 CUDA matrices; ``row_map`` permutes the output
+    rows between batch-major (``b*length + l``) and time-major (``l*batch + b``) order.  With ``col_block`` the
+    output is ``[N // col_block, M, col_block]``: one plane per block of output columns (what a reduce-scatter
+    over the columns takes)."""
+    for name, t in (("A", A), ("w_hi", w_hi), ("w_lo", w_lo), ("out", out), ("aux", aux), ("diag", diag)):
+        if t is None:
+            continue
+        _require_cuda(name, t)
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.device != A.device:
+            raise RuntimeError(f"ossm_b200: {name} must be a contiguous float32 tensor on the device of A")
+    if A.dim() != 2 or w_hi.dim() != 2 or w_hi.shape != w_lo.shape or A.size(1) != w_hi.size(1):
+        raise RuntimeError("ossm_b200: gemm_tf32x3 needs A [M,K] and W [N,K]")
+    M, K = A.shape
+    N = w_hi.size(0)
+    if out.numel() != M * N or (aux is not None and aux.numel() != M * N) or (diag is not None and diag.numel() != N):
+        raise RuntimeError("ossm_b200: gemm_tf32x3 output / aux / diag extents do not match")
+    if (aux is None) != (diag is None):
+        raise RuntimeError("ossm_b200: aux and diag come together")
+    if M == 0 or N == 0:
+        return out
+    ldo, plane = N, 0
+    if col_block and col_block < N:
+        if N % col_block:
+            raise RuntimeError("ossm_b200: col_block must divide N")
+        ldo, plane = col_block, M * col_block
+    with torch.cuda.device(A.device):
+        rc = _lib.load().ossm_b200_gemm_tf32x3(_p(A), _p(w_hi), _p(w_lo), _p(out), _p(aux), _p(diag), M, N, K, ldo,
+                                               int(col_block or 0), plane, int(row_map), int(batch), int(length),
+                                               _stream(A.device))
+    _lib.check(rc, "gemm_tf32x3")
+    return out
+
+
 # ---- names ossm calls unconditionally but that are outside this library ------
 def _out_of_scope(name: str):
     def stub(*_args, **_kwargs):

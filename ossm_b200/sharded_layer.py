@@ -1,19 +1,25 @@
-"""D-LinOSS layer with the oscillators sharded over GPUs (BASELINE config 4).
+"""D-LinOSS layer with the oscillators sharded over GPUs (one process per GPU).
 
-Every rank holds a contiguous shard of the ``P`` oscillators -- the matching
-entries of ``(A, G, step)``, rows of ``B`` and columns of ``C`` -- and the whole
-input ``u`` (replicated).  It projects ``bu_r = u B_r^T``, scans its own series
-(no exchange: series never interact), forms the partial output
-``Re(C_r x_r)`` and the partial outputs are summed over ranks (NCCL all-reduce
-over NVLink); ``D*u`` is added after the sum.  In the backward pass the upstream
-gradient is already replicated, so the only exchange is the sum of the
-per-shard input gradients.  The math of one shard is the body of
-``DampedLinOSSLayer.forward`` (``src/ossm/models/dlinoss.py:217-247``); the
-reference has no distributed code, the oracle is the single-device result.
+Every rank holds a contiguous shard of the ``P`` oscillators -- the matching entries of
+``(A, G, step)``, rows of ``B`` and columns of ``C`` -- and the whole input ``u`` (replicated).  It
+projects ``bu_r = u B_r^T`` on the tensor cores, scans its own series (no exchange: series never
+interact) and forms the partial output ``Re(C_r x_r)``.  The only exchange of the forward pass is
+the sum of the partial outputs over the ranks.  With ``scatter_output=True`` (default) that sum is
+a reduce-scatter over the hidden dimension: rank ``r`` ends with ``y[..., H_r]``, half the bytes of
+an all-reduce, and the term ``D*u`` is added on the shard (``D`` is then the rank's ``H_r`` slice).
+The time axis is cut into ``chunks`` pieces for the output projection: the reduce-scatter of piece
+``k`` (NCCL, on its own stream) runs while the tensor-core GEMM of piece ``k+1`` computes, and the
+GEMM writes each piece directly as one plane per destination rank, so nothing is repacked or cloned
+before the collective.
 
-The projections are plain library GEMMs (torch.matmul); the scan is this
-package's CUDA op.  The sum over ranks is issued per batch slice on a side
-stream so that it overlaps the projection of the next slice.
+Backward: the gradient of the shard is all-gathered (the transpose of the reduce-scatter), every rank
+computes ``grad_x_r``, runs its scan backward and the local weight gradients; the gradient of the
+replicated input is the sum over ranks (one all-reduce).
+
+The math of one shard is the body of ``DampedLinOSSLayer.forward``
+(``src/ossm/models/dlinoss.py:217-247``); the reference has no distributed code, the oracle is the
+single-device result.  ``scan`` / ``gemm`` can be replaced by plain PyTorch callables so that the
+sharding logic runs on CPU ranks (gloo) in tests.
 """
 from __future__ import annotations
 
@@ -23,7 +29,24 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-__all__ = ["sharded_dlinoss_layer", "CopyToShards", "SumOverShards"]
+__all__ = ["sharded_dlinoss_layer", "CopyToShards", "hidden_shard"]
+
+
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def _rank(group) -> int:
+    return dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
+
+
+def hidden_shard(hidden: int, group=None) -> slice:
+    """Columns of the output this rank owns after the reduce-scatter (``hidden`` must divide evenly)."""
+    world, rank = _world(group), _rank(group)
+    if hidden % world:
+        raise ValueError(f"hidden_dim {hidden} must be a multiple of the number of ranks {world}")
+    hs = hidden // world
+    return slice(rank * hs, (rank + 1) * hs)
 
 
 class CopyToShards(torch.autograd.Function):
@@ -37,51 +60,158 @@ class CopyToShards(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad: Tensor):
         grad = grad.contiguous()
-        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+        if _world(ctx.group) > 1:
             dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
         return grad, None
 
 
-class SumOverShards(torch.autograd.Function):
-    """Sum of per-rank partial results (replicated afterwards); gradient passes through."""
+# ---- the two projections as autograd functions over a pluggable GEMM ---------------------------------
+def _torch_project(a2d: Tensor, w: Tensor) -> Tensor:
+    return a2d @ w.t()
+
+
+class _ProjectIn(torch.autograd.Function):
+    """``bu [L, B, P_r]`` complex64 (time-major) from ``u [B, L, H]`` and ``W_in [2 P_r, H]``."""
 
     @staticmethod
-    def forward(ctx, partial: Tensor, group, slices: int) -> Tensor:
-        out = partial.contiguous().clone()
-        if not (dist.is_initialized() and dist.get_world_size(group) > 1):
-            return out
-        if slices <= 1 or out.size(0) < slices:
-            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
-            return out
-        works = [dist.all_reduce(piece, op=dist.ReduceOp.SUM, group=group, async_op=True)
-                 for piece in out.tensor_split(slices, dim=0)]
-        for w in works:
-            w.wait()
+    def forward(ctx, u: Tensor, w_in: Tensor, use_kernels: bool) -> Tensor:
+        batch, length, hidden = u.shape
+        p2 = w_in.size(0)
+        u2 = u.contiguous().view(batch * length, hidden)
+        if use_kernels:
+            from . import kernels
+
+            bu = torch.empty((length, batch, p2 // 2), dtype=torch.complex64, device=u.device)
+            kernels.gemm_tf32x3(u2, *kernels.split_tf32(w_in), torch.view_as_real(bu).view(length * batch, p2),
+                                row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=length)
+        else:
+            flat = _torch_project(u2, w_in).view(batch, length, p2 // 2, 2).permute(1, 0, 2, 3).contiguous()
+            bu = torch.view_as_complex(flat)
+        ctx.use_kernels = use_kernels
+        ctx.save_for_backward(u2, w_in)
+        ctx.shape = (batch, length, hidden)
+        return bu
+
+    @staticmethod
+    def backward(ctx, grad_bu: Tensor):
+        u2, w_in = ctx.saved_tensors
+        batch, length, hidden = ctx.shape
+        p2 = w_in.size(0)
+        g = torch.view_as_real(grad_bu.contiguous()).view(length, batch, p2)
+        if ctx.use_kernels:
+            from . import kernels
+
+            grad_u = torch.empty((batch, length, hidden), dtype=torch.float32, device=u2.device)
+            kernels.gemm_tf32x3(g.view(length * batch, p2), *kernels.split_tf32(w_in.t().contiguous()),
+                                grad_u.view(batch * length, hidden), row_map=kernels.ROWS_TIME_TO_BATCH, batch=batch,
+                                length=length)
+        else:
+            grad_u = (g.permute(1, 0, 2).reshape(batch * length, p2) @ w_in).view(batch, length, hidden)
+        grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
+        return grad_u, grad_w, None
+
+
+class _ProjectOutReduce(torch.autograd.Function):
+    """Sum over ranks of ``x_r W_out_r^T``: ``x [L, B, P_r]`` complex64 (time-major), ``W_out [H, 2 P_r]``.
+    Returns ``[B, L, H / world]`` (reduce-scatter) or ``[B, L, H]`` (all-reduce)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, w_out: Tensor, group, chunks: int, scatter: bool, use_kernels: bool) -> Tensor:
+        length, batch, ssm = x.shape
+        hidden = w_out.size(0)
+        world = _world(group)
+        xr = torch.view_as_real(x.contiguous()).view(length, batch, 2 * ssm)
+        planes = world if scatter else 1
+        hs = hidden // planes
+        out = torch.empty((batch, length, hs), dtype=torch.float32, device=x.device)
+        chunks = max(1, min(int(chunks), length))
+        bounds = [(length * i) // chunks for i in range(chunks + 1)]
+        if use_kernels:
+            from . import kernels
+
+            w_hi, w_lo = kernels.split_tf32(w_out)
+        pending = []
+        for l0, l1 in zip(bounds[:-1], bounds[1:]):
+            lc = l1 - l0
+            if lc == 0:
+                continue
+            rows = xr[l0:l1].reshape(lc * batch, 2 * ssm)
+            # one plane [B, lc, hs] per destination rank, written by the GEMM itself
+            part = torch.empty((planes, batch, lc, hs), dtype=torch.float32, device=x.device)
+            if use_kernels:
+                kernels.gemm_tf32x3(rows, w_hi, w_lo, part.view(planes, batch * lc, hs), row_map=kernels.ROWS_TIME_TO_BATCH,
+                                    batch=batch, length=lc, col_block=hs)
+            else:
+                full = _torch_project(rows, w_out).view(lc, batch, planes, hs)
+                part.copy_(full.permute(2, 1, 0, 3))
+            if world == 1:
+                out[:, l0:l1].copy_(part[0])
+                continue
+            if scatter:
+                mine = torch.empty((batch, lc, hs), dtype=torch.float32, device=x.device)
+                work = dist.reduce_scatter_tensor(mine, part.view(planes * batch, lc, hs), op=dist.ReduceOp.SUM, group=group,
+                                                  async_op=True)
+            else:
+                mine = part[0]
+                work = dist.all_reduce(mine, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            pending.append((work, mine, part, l0, l1))      # the collective runs while the next piece is projected
+        for work, mine, _part, l0, l1 in pending:
+            work.wait()
+            out[:, l0:l1].copy_(mine)
+        ctx.group, ctx.scatter, ctx.use_kernels = group, scatter, use_kernels
+        ctx.save_for_backward(xr, w_out)
         return out
 
     @staticmethod
-    def backward(ctx, grad: Tensor):
-        return grad, None, None
+    def backward(ctx, grad_out: Tensor):
+        xr, w_out = ctx.saved_tensors
+        length, batch, p2 = xr.shape
+        hidden = w_out.size(0)
+        group, world = ctx.group, _world(ctx.group)
+        gy = grad_out.contiguous()
+        if ctx.scatter and world > 1:
+            gathered = torch.empty((world,) + tuple(gy.shape), dtype=gy.dtype, device=gy.device)
+            dist.all_gather_into_tensor(gathered.view(world * gy.size(0), *gy.shape[1:]), gy, group=group)
+            gy = gathered.permute(1, 2, 0, 3).reshape(batch, length, hidden)   # [B, L, H] again
+        gy2 = gy.reshape(batch * length, hidden)
+        if ctx.use_kernels:
+            from . import kernels
+
+            grad_x = torch.empty((length, batch, p2 // 2), dtype=torch.complex64, device=xr.device)
+            kernels.gemm_tf32x3(gy2, *kernels.split_tf32(w_out.t().contiguous()),
+                                torch.view_as_real(grad_x).view(length * batch, p2),
+                                row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=length)
+        else:
+            flat = (gy2 @ w_out).view(batch, length, p2 // 2, 2).permute(1, 0, 2, 3).contiguous()
+            grad_x = torch.view_as_complex(flat)
+        grad_w = torch.bmm(gy2.view(batch, length, hidden).transpose(1, 2), xr.permute(1, 0, 2)).sum(0)
+        return grad_x, grad_w, None, None, None, None
 
 
-def sharded_dlinoss_layer(variant: str, a: Tensor, g: Tensor, step: Tensor, B_re: Tensor, B_im: Tensor,
-                          C_re: Tensor, C_im: Tensor, D: Tensor, u: Tensor, *, group=None,
-                          scan: Optional[Callable[[str, Tensor, Tensor, Tensor, Tensor], Tensor]] = None,
-                          slices: int = 1) -> Tensor:
-    """``y = sum_r Re(C_r x_r) + D*u`` with ``x_r = scan(bu_r)``, ``bu_r = u B_r^T``.
+def sharded_dlinoss_layer(variant: str, a: Tensor, g: Tensor, step: Tensor, B: Tensor, C: Tensor, D: Tensor, u: Tensor, *,
+                          group=None, scan: Optional[Callable[[str, Tensor, Tensor, Tensor, Tensor], Tensor]] = None,
+                          chunks: int = 4, scatter_output: bool = True, use_kernels: Optional[bool] = None) -> Tensor:
+    """``y = sum_r Re(C_r x_r) + D*u`` with ``x_r = scan(u B_r^T)``.
 
-    Shapes on each rank: ``a, g, step [P_r]`` (already projected), ``B_re, B_im [P_r, H]``,
-    ``C_re, C_im [H, P_r]``, ``D [H]`` and ``u [B, L, H]`` replicated.  Returns ``y [B, L, H]``
-    replicated.  ``scan(variant, a, g, step, bu_seq)`` defaults to :func:`ossm_b200.dlinoss.run_dlinoss`.
-    """
+    On each rank: ``a, g, step [P_r]`` (already projected), ``B [P_r, H, 2]``, ``C [H, P_r, 2]`` (the layer's
+    parameter layout, ``dlinoss.py:93-98``), ``u [B, L, H]`` replicated.  ``scatter_output=True``: ``D`` is the
+    rank's slice ``[H / world]`` and the result is ``y[..., hidden_shard(H)]``; ``False``: ``D [H]`` replicated
+    and the whole ``y`` on every rank.  ``scan(variant, a, g, step, bu_seq)`` defaults to
+    :func:`ossm_b200.dlinoss.run_dlinoss`; ``use_kernels=False`` runs the projections with ``torch.matmul``
+    (CPU tests of the sharding logic)."""
+    from .dlinoss_layer import pack_input_weights, pack_output_weights
+
+    if use_kernels is None:
+        use_kernels = u.is_cuda
     if scan is None:
         from .dlinoss import run_dlinoss as scan
-    batch, length, hidden = u.shape
+    hidden = u.size(-1)
     u_in = CopyToShards.apply(u, group)
-    flat = u_in.reshape(batch * length, hidden)
-    bu = torch.complex(flat @ B_re.t(), flat @ B_im.t()).reshape(batch, length, -1)
-    x = scan(variant, a, g, step, bu.permute(1, 0, 2).contiguous())           # [L, B, P_r]
-    xf = x.permute(1, 0, 2).reshape(batch * length, -1)
-    partial = (xf.real @ C_re.t() - xf.imag @ C_im.t()).reshape(batch, length, hidden)
-    y = SumOverShards.apply(partial, group, slices)
+    bu = _ProjectIn.apply(u_in, pack_input_weights(B), use_kernels)                   # [L, B, P_r]
+    x = scan(variant, a, g, step, bu)
+    y = _ProjectOutReduce.apply(x, pack_output_weights(C), group, chunks, scatter_output, use_kernels)
+    if scatter_output:
+        # each rank adds D*u on its own columns; their gradients on u are disjoint and meet in the all-reduce
+        return y + u_in[..., hidden_shard(hidden, group)] * D
+    # replicated output and replicated D: every rank adds the whole term, so it stays outside the summed gradient
     return y + u * D

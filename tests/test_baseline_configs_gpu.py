@@ -119,6 +119,41 @@ def test_config4_shard_length_automatic_segments():
                tol_step=5e-4)
 
 
+def test_config4_shard_full_size_properties():
+    """The whole 256-oscillator shard (B = 8, P = 256, L = 131072; 2048 series, two-level kernels) with
+    stable parameters: the backward is the adjoint of the forward (<x(bu), g> = <bu, grad_bu(g)>), and the
+    two-level kernels agree with the time-segmented kernels on x, grad_bu and the coefficient gradients."""
+    from ossm_b200 import kernels as K
+    from test_lti_scan_gpu import stable_params
+
+    L, B, P = 131072, 8, 256
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a, g, st = (dev(t) for t in stable_params(P, torch.Generator().manual_seed(1)))
+    bu = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device="cuda") * 0.5)
+    gx = torch.view_as_complex(torch.randn(L, B, P, 2, generator=gen, device="cuda"))
+    x, _, carries = K.lti_scan_forward("imex1", a, g, st, bu)
+    grads = K.lti_scan_backward("imex1", a, g, st, bu, carries, gx)
+
+    def rdot(u, v):
+        return float((u.real.double() * v.real.double() + u.imag.double() * v.imag.double()).sum())
+
+    scale = float(x.abs().double().pow(2).sum().sqrt() * gx.abs().double().pow(2).sum().sqrt())
+    assert abs(rdot(x, gx) - rdot(bu, grads[3])) <= 1e-6 * scale
+    K.set_tuning("twolevel", 0)
+    try:
+        x0, _, carries0 = K.lti_scan_forward("imex1", a, g, st, bu)
+        grads0 = K.lti_scan_backward("imex1", a, g, st, bu, carries0, gx)
+    finally:
+        K.set_tuning("twolevel", 1)
+    tag = "config4 shard L=131072 B=8 P=256: two-level against time-segmented kernels"
+    assert record(tag, "x", float((x - x0).abs().max() / x0.abs().max()), 1e-5) <= 1e-5
+    assert torch.equal(torch.view_as_real(carries), torch.view_as_real(carries0)) or float(
+        (carries - carries0).abs().max() / carries0.abs().max()) <= 1e-5
+    for name, u, v in zip(("grad_A", "grad_G", "grad_step", "grad_bu"), grads, grads0):
+        tol = 1e-5 if name == "grad_bu" else 5e-5
+        assert record(tag, name, float((u - v).abs().max() / v.abs().max()), tol) <= tol
+
+
 def mamba_case(Bz, Dn, L, N, seed):
     gen = torch.Generator().manual_seed(seed)
     u = torch.randn(Bz, Dn, L, generator=gen)

@@ -1,0 +1,106 @@
+"""The D-LinOSS layer body as one op (tensor-core projections around the scan) against the oracle's
+layer math (``dlinoss.py:217-247`` restated in numpy around ``scan_oracle.lti_forward / lti_backward``):
+the output of the reference's golden vectors at the reference's own tolerance, and output plus the seven
+gradients (u, A, G, step, B, C, D) on seeded shapes, max-norm relative error <= 1e-5 (5e-5 on the three
+coefficient gradients, as in the scan tests)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import scan_oracle as so
+from _parity_report import record
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from ossm_b200 import _lib
+
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def layer_oracle(variant, a, g, step, Bp, Cp, D, u, dy):
+    """float64 layer: returns y and the gradients of <y, dy>."""
+    bsz, L, H = u.shape
+    P = a.shape[0]
+    flat = u.reshape(bsz * L, H)
+    bu = (flat @ Bp[..., 0].T + 1j * (flat @ Bp[..., 1].T)).reshape(bsz, L, P)
+    bu_seq = np.ascontiguousarray(bu.transpose(1, 0, 2))
+    states = so.lti_forward(variant, a, g, step, bu_seq)
+    xf = states[..., 1].transpose(1, 0, 2).reshape(bsz * L, P)
+    y = (xf.real @ Cp[..., 0].T - xf.imag @ Cp[..., 1].T).reshape(bsz, L, H) + u * D
+    dyf = dy.reshape(bsz * L, H)
+    gx = (dyf @ Cp[..., 0] - 1j * (dyf @ Cp[..., 1])).reshape(bsz, L, P)
+    da, dg, ds, dbu = so.lti_backward(variant, a, g, step, bu_seq, np.ascontiguousarray(gx.transpose(1, 0, 2)),
+                                      states=states)
+    dbu_f = dbu.transpose(1, 0, 2).reshape(bsz * L, P)
+    du = (dbu_f.real @ Bp[..., 0] + dbu_f.imag @ Bp[..., 1]).reshape(bsz, L, H) + dy * D
+    dB = np.stack((dbu_f.real.T @ flat, dbu_f.imag.T @ flat), axis=-1)
+    dC = np.stack((dyf.T @ xf.real, -(dyf.T @ xf.imag)), axis=-1)
+    dD = (dy * u).sum(axis=(0, 1))
+    return y, dict(u=du, A=da, G=dg, step=ds, B=dB, C=dC, D=dD)
+
+
+def make_layer_case(bsz, L, H, P, seed, variant):
+    from test_lti_scan_gpu import stable_params
+
+    gen = torch.Generator().manual_seed(seed)
+    a, g, st = stable_params(P, gen)
+    bound_b, bound_c = 1.0 / H ** 0.5, 1.0 / P ** 0.5
+    Bp = torch.empty(P, H, 2).uniform_(-bound_b, bound_b, generator=gen)
+    Cp = torch.empty(H, P, 2).uniform_(-bound_c, bound_c, generator=gen)
+    D = torch.randn(H, generator=gen)
+    u = torch.randn(bsz, L, H, generator=gen)
+    dy = torch.randn(bsz, L, H, generator=gen)
+    return a, g, st, Bp, Cp, D, u, dy
+
+
+SHAPES = [(2, 40, 8, 6), (3, 70, 24, 48), (1, 6, 3, 4), (2, 130, 36, 25), (4, 300, 256, 128), (2, 257, 64, 256)]
+
+
+@pytest.mark.parametrize("variant", ["imex1", "imex2", "im", "ex"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_layer_matches_oracle(variant, shape):
+    from ossm_b200.dlinoss_layer import dlinoss_layer
+
+    case = make_layer_case(*shape, seed=sum(shape), variant=variant)
+    leaves = [t.cuda().requires_grad_(True) for t in case[:7]]
+    y = dlinoss_layer(variant, *leaves)
+    y.backward(case[7].cuda())
+    ref_y, ref = layer_oracle(variant, *[t.double().numpy() for t in case])
+    tag = f"D-LinOSS layer op {variant} " + "x".join(map(str, shape))
+    assert record(tag, "y", so.max_rel_err(y.detach().cpu().numpy(), ref_y), 1e-5) <= 1e-5
+    for leaf, name, tol in zip(leaves, ("A", "G", "step", "B", "C", "D", "u"), (5e-5, 5e-5, 5e-5, 1e-5, 1e-5, 1e-5, 1e-5)):
+        assert record(tag, "grad_" + name, so.max_rel_err(leaf.grad.cpu().numpy(), ref[name]), tol) <= tol, name
+
+
+@pytest.mark.parametrize("variant", ["imex1", "imex2", "im", "ex"])
+def test_reference_golden_outputs(variant):
+    """Layer outputs of the reference's golden file (tests/dlinoss_reference_cases.json) at its tolerance."""
+    from ossm_b200.dlinoss_layer import dlinoss_layer
+
+    G = np.load(os.path.join(GOLD, "dlinoss_reference_cases.npz"))
+    c = {k.split("/", 2)[2]: G[k] for k in G.files if k.startswith(f"{variant}/float32/")}
+    args = [torch.from_numpy(c[k]).float().cuda() for k in ("A_diag", "G_diag", "step", "B", "C", "D", "inputs")]
+    y = dlinoss_layer(variant, *args)
+    np.testing.assert_allclose(y.cpu().numpy(), c["outputs"], rtol=5e-6, atol=5e-6)
+
+
+def test_matches_the_unfused_composition():
+    """Same numbers as library GEMMs + permutes + this package's scan op (what the reference layer does)."""
+    from ossm_b200.dlinoss import run_dlinoss
+    from ossm_b200.dlinoss_layer import dlinoss_layer
+
+    a, g, st, Bp, Cp, D, u, dy = (t.cuda() for t in make_layer_case(4, 512, 64, 64, seed=5, variant="imex1"))
+    y = dlinoss_layer("imex1", a, g, st, Bp, Cp, D, u)
+    flat = u.reshape(-1, 64)
+    bu = torch.complex(flat @ Bp[..., 0].t(), flat @ Bp[..., 1].t()).reshape(4, 512, 64)
+    x = run_dlinoss("imex1", a, g, st, bu.permute(1, 0, 2).contiguous()).permute(1, 0, 2).reshape(-1, 64)
+    want = (x.real @ Cp[..., 0].t() - x.imag @ Cp[..., 1].t()).reshape(4, 512, 64) + u * D
+    assert float((y - want).abs().max() / want.abs().max()) <= 1e-5

@@ -1,5 +1,7 @@
-"""Oscillator-sharded D-LinOSS layer on two GPUs (NCCL) with the CUDA scan,
-against the same layer on one GPU.  Needs two devices; skipped otherwise."""
+"""Oscillator-sharded D-LinOSS layer on two GPUs (NCCL) with the CUDA scan and the tensor-core
+projections, reduce-scatter and all-reduce forms, against the same layer on one GPU.  Needs two
+devices; skipped otherwise (``bench.py --gpus N`` runs the same comparison before its timed region
+and reports it under ``sharded_parity``)."""
 import os
 import socket
 
@@ -10,7 +12,7 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
-SHARD_DIM = dict(a=0, g=0, step=0, B_re=0, B_im=0, C_re=1, C_im=1)
+SHARD_DIM = dict(a=0, g=0, step=0, B=0, C=1)
 
 
 def make_problem():
@@ -18,8 +20,7 @@ def make_problem():
     Bz, L, H, P = 3, 130, 16, 96
     p = dict(a=torch.rand(P, generator=gen) * 0.8, g=torch.rand(P, generator=gen) * 0.4,
              step=torch.sigmoid(torch.randn(P, generator=gen)),
-             B_re=torch.randn(P, H, generator=gen) * 0.2, B_im=torch.randn(P, H, generator=gen) * 0.2,
-             C_re=torch.randn(H, P, generator=gen) * 0.2, C_im=torch.randn(H, P, generator=gen) * 0.2,
+             B=torch.randn(P, H, 2, generator=gen) * 0.2, C=torch.randn(H, P, 2, generator=gen) * 0.2,
              D=torch.randn(H, generator=gen))
     return p, torch.randn(Bz, L, H, generator=gen), torch.randn(Bz, L, H, generator=gen)
 
@@ -45,29 +46,34 @@ def _worker(rank, world, port, out):
         params, u, dy = make_problem()
         full = {k: v.to(dev).requires_grad_(True) for k, v in params.items()}
         u_full = u.to(dev).requires_grad_(True)
-        # single-GPU reference: same function, every oscillator on this rank, no collective
-        from ossm_b200.dlinoss import run_dlinoss
+        # single-GPU reference: the unsharded layer op, every oscillator on this rank, no collective
+        from ossm_b200.dlinoss_layer import dlinoss_layer
+        from ossm_b200.sharded_layer import hidden_shard
 
-        bsz, L, H = u.shape
-        flat = u_full.reshape(bsz * L, H)
-        bu = torch.complex(flat @ full["B_re"].t(), flat @ full["B_im"].t()).reshape(bsz, L, -1)
-        x = run_dlinoss("imex1", full["a"], full["g"], full["step"], bu.permute(1, 0, 2).contiguous())
-        xf = x.permute(1, 0, 2).reshape(bsz * L, -1)
-        y_ref = (xf.real @ full["C_re"].t() - xf.imag @ full["C_im"].t()).reshape(bsz, L, H) + u_full * full["D"]
+        H = u.size(-1)
+        y_ref = dlinoss_layer("imex1", full["a"], full["g"], full["step"], full["B"], full["C"], full["D"], u_full)
         y_ref.backward(dy.to(dev))
-
-        loc = {k: (shard_channels(v.to(dev), world, rank, dim=SHARD_DIM[k]) if k in SHARD_DIM else v.to(dev))
-               .requires_grad_(True) for k, v in params.items()}
-        u_loc = u.to(dev).requires_grad_(True)
-        y = sharded_dlinoss_layer("imex1", loc["a"], loc["g"], loc["step"], loc["B_re"], loc["B_im"], loc["C_re"],
-                                  loc["C_im"], loc["D"], u_loc, slices=2)
-        y.backward(dy.to(dev))
-        torch.testing.assert_close(y, y_ref, rtol=2e-5, atol=2e-5)
-        torch.testing.assert_close(u_loc.grad, u_full.grad, rtol=2e-5, atol=2e-5)
         P = params["a"].numel()
-        for k, dim in SHARD_DIM.items():
-            got = gather_channels(loc[k].grad.movedim(dim, -1).contiguous(), P).movedim(-1, dim)
-            torch.testing.assert_close(got, full[k].grad, rtol=1e-4, atol=1e-4, msg=k)
+        for scatter in (True, False):
+            cols = hidden_shard(H) if scatter else slice(0, H)
+            loc = {k: (shard_channels(v.to(dev), world, rank, dim=SHARD_DIM[k]) if k in SHARD_DIM else v.to(dev))
+                   for k, v in params.items()}
+            loc["D"] = params["D"][cols].to(dev)
+            loc = {k: v.requires_grad_(True) for k, v in loc.items()}
+            u_loc = u.to(dev).requires_grad_(True)
+            y = sharded_dlinoss_layer("imex1", loc["a"], loc["g"], loc["step"], loc["B"], loc["C"], loc["D"], u_loc,
+                                      chunks=3, scatter_output=scatter)
+            y.backward(dy.to(dev)[..., cols])
+            torch.testing.assert_close(y, y_ref[..., cols].detach(), rtol=2e-5, atol=2e-5)
+            torch.testing.assert_close(u_loc.grad, u_full.grad, rtol=2e-5, atol=2e-5)
+            for k, dim in SHARD_DIM.items():
+                grad = loc[k].grad
+                if grad.dim() == 3:
+                    got = torch.stack([gather_channels(grad[..., c].movedim(dim, -1).contiguous(), P).movedim(-1, dim)
+                                       for c in (0, 1)], -1)
+                else:
+                    got = gather_channels(grad.contiguous(), P)
+                torch.testing.assert_close(got, full[k].grad, rtol=1e-4, atol=1e-4, msg=k)
         out.put((rank, "ok"))
     except Exception:                                       # pragma: no cover
         import traceback
