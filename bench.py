@@ -797,10 +797,10 @@ def run_ours(args):
         h_pg = torch.empty((3, P), dtype=torch.float32, pin_memory=True)
         from ossm_b200.host_io import scan_from_host
 
-        # The public call for host-resident data: batch slices are copied up, scanned and
+        # The public call for host-resident data: time slices are copied up, scanned and
         # copied down in a pipeline so that both PCIe directions stay busy.
         def e2e_step(copies_only=False):
-            grads = scan_from_host(variant, a, g, dt, h_bu, h_gx, h_x, h_gbu, slices=8, copies_only=copies_only)
+            grads = scan_from_host(variant, a, g, dt, h_bu, h_gx, h_x, h_gbu, slices=16, copies_only=copies_only)
             if grads is not None:
                 for row, t in zip(h_pg, grads):
                     row.copy_(t, non_blocking=True)
@@ -826,7 +826,7 @@ def run_ours(args):
                "copies_only": {"ms_per_step": copy_ms, "value": total_elems / (copy_ms * 1e-3) / 1e9,
                                "what": "the same pinned buffers through the same copy pipeline with no kernel launched: "
                                        "the ceiling the host and PCIe side puts on this call"},
-               "api": "ossm_b200.host_io.scan_from_host (forward + backward, pinned host buffers, 8 batch slices)"}
+               "api": "ossm_b200.host_io.scan_from_host (forward + backward, pinned host buffers, 16 time slices, state handed over on the device)"}
         del h_bu, h_gx, h_x, h_gbu
     del bu, gx
     torch.cuda.empty_cache()

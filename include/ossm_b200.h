@@ -106,6 +106,29 @@ int ossm_b200_lti_scan_backward(int variant, const float* a, const float* g, con
                                 float* grad_g, float* grad_step, void* workspace, size_t workspace_bytes, int64_t L,
                                 int64_t B, int64_t P, ossm_b200_stream_t stream);
 
+/* The scan over one TIME SLICE of a longer sequence (no counterpart in the reference, which always holds the
+ * whole sequence on the device): a caller that streams a long sequence through the GPU piece by piece hands
+ * the recurrence state from slice to slice.
+ *   state_in  : complex64 [B, P, 2] state (s0, s1) entering the slice, NULL = zero (the first slice)
+ *   state_out : complex64 [B, P, 2] state leaving the slice, NULL = not wanted
+ *   carries   : as in ossm_b200_lti_scan_forward, for this slice alone (ossm_b200_lti_carry_bytes(L, B, P))
+ * Backward slices run in reverse time order:
+ *   adjoint_in  : complex64 [B, P, 2] adjoint entering the slice from the later slice, NULL = zero (the last slice)
+ *   adjoint_out : complex64 [B, P, 2] adjoint leaving towards the earlier slice, NULL = not wanted
+ *   state_in    : the state_in the forward call of the same slice was given
+ * grad_a / grad_g / grad_step receive this slice's share of the coefficient gradients (the caller adds the
+ * slices).  The states and grad_bu of a sliced run are those of the unsliced call bit for bit when the slices
+ * are multiples of ossm_b200_lti_chunk() steps (same arithmetic, step for step); the coefficient gradients
+ * agree up to the rounding of their partial sums. */
+int ossm_b200_lti_scan_forward_slice(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                     void* x, void* carries, const void* state_in, void* state_out, int64_t L,
+                                     int64_t B, int64_t P, ossm_b200_stream_t stream);
+int ossm_b200_lti_scan_backward_slice(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                      const void* carries, const void* state_in, const void* grad_x,
+                                      const void* adjoint_in, void* adjoint_out, void* grad_bu, float* grad_a,
+                                      float* grad_g, float* grad_step, void* workspace, size_t workspace_bytes,
+                                      int64_t L, int64_t B, int64_t P, ossm_b200_stream_t stream);
+
 /* Backward with the reference's argument list: the full trajectory `states`
  * ([L,B,P,2], as returned by forward) stands in for the carries
  * (dlinoss_imex1.cpp:354-390 takes a_diag, g_diag, step, bu, states, grad_output). */
@@ -177,6 +200,18 @@ int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, 
                           const float* diag, int64_t M, int64_t N, int64_t K, int64_t ldo, int64_t col_block,
                           int64_t plane_stride, int row_map, int64_t batch, int64_t length,
                           ossm_b200_stream_t stream);
+
+/* Weight gradients of the two projections: out[m, n] = sum over all (b, l) of X[row(b,l), m] * Y[row(b,l), n]
+ * (grad_B from grad_bu and u, grad_C from grad_y and x), same three-product TF32 scheme.  X [batch*length, M] and
+ * Y [batch*length, N] are dense float32 matrices whose rows are ordered batch-major (b*length + l,
+ * *_time_major = 0) or time-major (l*batch + b, 1), independently of each other; M and N must be multiples of 32.
+ * The contraction is divided over *splits_out CTAs per output tile, each of which writes one partial
+ * [M, N] matrix into `partial` (ossm_b200_wgrad_tf32x3_workspace_bytes() bytes); the caller adds the
+ * partials (fixed order: deterministic). */
+size_t ossm_b200_wgrad_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t batch, int64_t length);
+int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int y_time_major, float* partial,
+                           size_t partial_bytes, int* splits_out, int64_t M, int64_t N, int64_t batch,
+                           int64_t length, ossm_b200_stream_t stream);
 
 /* ---- generic LinOSS scan (complex 2x2 per channel, forcing per step) --------
  * Replaces ossm::linoss_scan (src/ossm/csrc/linoss_scan.cpp:115-146; bindings.cpp:160)
@@ -284,6 +319,25 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
                                       float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
                                       float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
                                       int64_t D, int64_t L, int64_t N, int io_dtype, ossm_b200_stream_t stream);
+
+/* ---- causal depthwise conv1d + bias + SiLU of the Mamba mixer ----------------------------------
+ * Replaces the chain transpose -> F.pad -> nn.Conv1d(groups = D) -> nn.SiLU -> transpose of
+ * _MambaMixer.forward (src/ossm/models/mambarec.py:143-151) by one pass that reads x once and writes
+ * the result in both layouts its consumers need:
+ *   x        float32 [B, L, D] with row pitch ldx floats (the x half of in_proj's output has ldx = 2 D)
+ *   weight   float32 [D, taps] (nn.Conv1d's [D, 1, taps]), taps = 1..4;  bias float32 [D] or NULL
+ *   out_bdl  float32 [B, D, L]  (time contiguous: the selective scan's operand), may be NULL
+ *   out_bld  float32 [B, L, D]  (channel contiguous: the x_proj GEMM's operand), may be NULL
+ * Backward takes the upstream gradient of either or both outputs and writes grad_x [B, L, D],
+ * grad_weight [D, taps] and grad_bias [D] (sums over batch and time, accumulated with float atomics:
+ * not bitwise reproducible from run to run). */
+int ossm_b200_conv1d_silu_forward(const float* x, int64_t ldx, const float* weight, const float* bias, float* out_bdl,
+                                  float* out_bld, int64_t B, int64_t L, int64_t D, int taps,
+                                  ossm_b200_stream_t stream);
+int ossm_b200_conv1d_silu_backward(const float* x, int64_t ldx, const float* weight, const float* bias,
+                                   const float* grad_bdl, const float* grad_bld, float* grad_x, float* grad_weight,
+                                   float* grad_bias, int64_t B, int64_t L, int64_t D, int taps,
+                                   ossm_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,9 @@ SIGNATURES = {
     "ossm_b200_lti_scan_backward": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                             c_int64, c_int64, c_int64, c_void_p]),
+    "ossm_b200_lti_scan_forward_slice": (c_int, [c_int] + [c_void_p] * 8 + [c_int64, c_int64, c_int64, c_void_p]),
+    "ossm_b200_lti_scan_backward_slice": (c_int, [c_int] + [c_void_p] * 14 + [c_size_t, c_int64, c_int64, c_int64,
+                                                                             c_void_p]),
     "ossm_b200_lti_scan_backward_states": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                    c_size_t, c_int64, c_int64, c_int64, c_void_p]),
@@ -47,6 +50,13 @@ SIGNATURES = {
                                           + [c_int64] * 4 + [c_int, c_void_p]),
     "ossm_b200_split_tf32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "ossm_b200_gemm_tf32x3": (c_int, [c_void_p] * 6 + [c_int64] * 6 + [c_int, c_int64, c_int64, c_void_p]),
+    "ossm_b200_wgrad_tf32x3_workspace_bytes": (c_size_t, [c_int64] * 4),
+    "ossm_b200_wgrad_tf32x3": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t, POINTER(c_int)]
+                               + [c_int64] * 4 + [c_void_p]),
+    "ossm_b200_conv1d_silu_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                              c_int64, c_int, c_void_p]),
+    "ossm_b200_conv1d_silu_backward": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 + [c_int64, c_int64, c_int64, c_int,
+                                                                                     c_void_p]),
     "ossm_b200_linoss_scan_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_int64, c_int64, c_int64, c_void_p]),
     "ossm_b200_linoss_scan_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),

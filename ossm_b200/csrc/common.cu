@@ -80,6 +80,31 @@ bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t c
                    CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                                  const uint64_t strides_bytes[3], const uint32_t box[4]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || box[0] * 4 != 128) return false;
+  cuuint64_t d[4], st[3];
+  cuuint32_t bx[4], es[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i) {
+    if (dims[i] == 0 || dims[i] > 0xffffffffull || box[i] == 0 || box[i] > 256) return false;
+    d[i] = dims[i];
+    bx[i] = box[i];
+  }
+  for (int i = 0; i < 3; ++i) {
+    if ((strides_bytes[i] & 15u) != 0 || strides_bytes[i] >= (1ull << 40)) return false;
+    st[i] = strides_bytes[i];
+  }
+  CUtensorMap tmp;
+  CUresult r = fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), d, st, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  memcpy(map, &tmp, sizeof(tmp));
+  return true;
+}
+
 bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                             uint32_t box_cols, uint32_t box_rows, bool swizzle128) {
   return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, cols, rows, pitch_bytes, box_cols, box_rows,
@@ -153,7 +178,7 @@ int ossm_b200_device_status(int* status, int clear) {
   }
   // first non-zero word wins; every word is cleared when asked
   int (*const words[])(int*, int) = {status_common, status_lti, status_linoss_generic, status_sdlinoss,
-                                     status_selective_scan, status_layer};
+                                     status_selective_scan, status_layer, status_mixer};
   int first = 0;
   for (auto fn : words) {
     int v = 0;

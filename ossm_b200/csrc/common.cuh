@@ -55,6 +55,7 @@ int status_linoss_generic(int* status, int clear);
 int status_sdlinoss(int* status, int clear);
 int status_selective_scan(int* status, int clear);
 int status_layer(int* status, int clear);
+int status_mixer(int* status, int clear);
 
 // ---- tensor maps (host) ----------------------------------------------------
 // 2-D fp32 view [rows, cols] with row pitch `pitch_bytes`; box = box_cols x box_rows.
@@ -67,6 +68,10 @@ bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, u
 // matrix descriptors of the projection kernels expect.
 bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                                   uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+// Rank-4 float32 map with the 128-byte swizzle.  dims / box are innermost first; strides_bytes are the byte
+// strides of dimensions 1..3 (dimension 0 is dense).  box[0] * 4 must be 128.
+bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                                  const uint64_t strides_bytes[3], const uint32_t box[4]);
 // Same for 16-bit elements (bf16 payloads are moved as raw 16-bit words).
 bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                             uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,
@@ -141,6 +146,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 4-D tiled TMA load global -> shared, completion on `bar` (non-multicast).
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 

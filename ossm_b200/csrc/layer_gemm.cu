@@ -294,6 +294,182 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Weight gradients:  out[m, n] = sum over all (b, l) rows of  X[row_x(b,l), m] * Y[row_y(b,l), n]
+// (grad_B from grad_bu and u, grad_C from grad_y and x: dlinoss.py:217-247 differentiated).  The
+// contraction runs over the ROWS of both activation matrices, which may be stored in different row
+// orders (batch-major b*L + l or time-major l*B + b): a K slice is 32 consecutive time steps of one
+// batch entry, fetched from either order by a rank-4 tensor map (32 columns, time, column block, batch)
+// whose box {32, 32, tile/32, 1} lands in shared memory as column blocks of [32 rows x 128 B] -- the
+// canonical MN-major operand layout of the tensor core (leading byte offset = 4096 B between column
+// blocks, 8-row groups 1024 B apart).  Both operands are activations, so both are split into hi / lo
+// halves by the splitter warps.  The M x N output is small and K = B*L is huge: the K slices are divided
+// over gridDim.z CTAs per output tile, each writes its partial tile, and the caller sums the partials in a
+// fixed order (deterministic, no atomics).
+constexpr int kWgThreads = 64 + 256;      // producer warp, MMA warp, eight splitter warps (four of them also epilogue)
+
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address
+  d |= (uint64_t)(4096 >> 4) << 16;                 // leading byte offset: next block of 32 M/N elements
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset: next group of 8 K rows
+  d |= (uint64_t)1 << 46;                           // descriptor version
+  d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+  return d;
+}
+// as instr_desc_tf32 with both operands MN-major (bits 15 and 16)
+__host__ __device__ constexpr uint32_t instr_desc_tf32_mn(int m, int n) {
+  return instr_desc_tf32(m, n) | (1u << 15) | (1u << 16);
+}
+
+struct WgradParams {
+  float* partial;          // [splits, M, N]
+  long long M, N;
+  long long batch, length;
+  int slices_per_batch;    // ceil(length / 32)
+  int stages;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kWgThreads, 1)
+wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y, WgradParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* split = full + kMaxStages;
+  uint64_t* empty = split + kMaxStages;
+  uint64_t* acc_done = empty + kMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  unsigned char* stage0 = smem + 1024;
+  constexpr int kXTile = kBM * kBK * 4;        // 16 KiB: 4 column blocks of [32][32]
+  constexpr int kYTile = BN * kBK * 4;
+  constexpr int kStage = 2 * kXTile + 2 * kYTile;   // X_hi | X_lo | Y_hi | Y_lo
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long m0 = (long long)blockIdx.x * kBM;
+  const long long n0 = (long long)blockIdx.y * BN;
+  const long long total = p.batch * p.slices_per_batch;
+  const long long per = (total + gridDim.z - 1) / gridDim.z;
+  const long long s_begin = (long long)blockIdx.z * per;
+  const long long s_end = s_begin + per < total ? s_begin + per : total;
+  const int nslices = s_end > s_begin ? (int)(s_end - s_begin) : 0;
+  const int stages = p.stages;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_y);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&split[s], 256);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_done, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int s = 0; s < nslices; ++s) {
+        const int b = s % stages;
+        if (s >= stages && !mbar_wait(&empty[b], ((s / stages) - 1) & 1, kWaitLimitNs, kStatusMmaTimeout)) break;
+        const long long g = s_begin + s;
+        const int bi = (int)(g / p.slices_per_batch);
+        const int l0 = (int)(g - (long long)bi * p.slices_per_batch) * kBK;
+        unsigned char* st = stage0 + (size_t)b * kStage;
+        mbar_expect_tx(&full[b], kXTile + kYTile);
+        tma_load_4d(st, &tm_x, &full[b], 0, l0, (int32_t)(m0 / 32), bi);
+        tma_load_4d(st + 2 * kXTile, &tm_y, &full[b], 0, l0, (int32_t)(n0 / 32), bi);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_tf32_mn(kBM, BN);
+      for (int s = 0; s < nslices; ++s) {
+        const int b = s % stages;
+        const uint32_t ph = (s / stages) & 1;
+        if (!(mbar_wait(&full[b], ph) && mbar_wait(&split[b], ph))) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(stage0 + (size_t)b * kStage);
+        const uint32_t x_hi = st, x_lo = st + kXTile, y_hi = st + 2 * kXTile, y_lo = y_hi + kYTile;
+#pragma unroll
+        for (int k = 0; k < kBK / 8; ++k) {
+          const uint32_t off = k * 1024;     // 8 K rows = one swizzle group inside every column block
+          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_hi + off), idesc, (s | k) != 0);
+          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_lo + off), idesc, 1);
+          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_lo + off), smem_desc_mn_sw128(y_hi + off), idesc, 1);
+        }
+        umma_commit(&empty[b]);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    const int t = threadIdx.x - 64;        // 0..255
+    bool ok = true;
+    for (int s = 0; s < nslices; ++s) {
+      const int b = s % stages;
+      ok = mbar_wait(&full[b], (s / stages) & 1);
+      if (!ok) break;
+      unsigned char* st = stage0 + (size_t)b * kStage;
+      auto split_tile = [&](float4* hi, float4* lo, int vecs) {
+        for (int i = t; i < vecs; i += 256) {
+          const float4 v = hi[i];
+          float4 h, l;
+          h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
+          h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
+          h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
+          h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+          hi[i] = h;
+          lo[i] = l;
+        }
+      };
+      split_tile(reinterpret_cast<float4*>(st), reinterpret_cast<float4*>(st + kXTile), kXTile / 16);
+      split_tile(reinterpret_cast<float4*>(st + 2 * kXTile), reinterpret_cast<float4*>(st + 2 * kXTile + kYTile), kYTile / 16);
+      fence_proxy_async();
+      mbar_arrive(&split[b]);
+    }
+    if (warp < 6) {    // warps 2..5: one accumulator lane quarter each
+      if (ok && nslices > 0) ok = mbar_wait(acc_done, 0, kWaitLimitNs, kStatusMmaTimeout);
+      if (ok) {
+        tc_fence_after();
+        const int q = warp & 3;
+        const long long m = m0 + q * 32 + lane;
+        float* row = p.partial + ((long long)blockIdx.z * p.M + (m < p.M ? m : 0)) * p.N;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          __syncwarp();
+          if (nslices > 0) {
+            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.0f;      // a split without slices contributes zeros
+          }
+          const long long n = n0 + c0;
+          if (m >= p.M || n >= p.N) continue;
+          if (n + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(row + n + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && n + j < p.N; ++j) row[n + j] = v[j];
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, BN);
+  }
+}
+
 // hi / lo TF32 split of a weight matrix (done once per call of the layer, a few hundred KB).
 __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
                                   long long n) {
@@ -321,6 +497,30 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUten
   return check_cuda(cudaGetLastError(), "gemm_tf32x3_kernel launch");
 }
 
+// K slices are divided over enough CTAs to fill the GPU once.
+static int wgrad_splits(long long M, long long N, long long batch, long long length) {
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const long long tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const long long total = batch * ((length + kBK - 1) / kBK);
+  long long splits = (sm_count() + tiles - 1) / tiles;
+  if (splits > total) splits = total;
+  if (splits > 512) splits = 512;
+  return splits < 1 ? 1 : (int)splits;
+}
+
+template <int BN>
+static int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& ty, WgradParams p, int splits, cudaStream_t stream) {
+  constexpr size_t stage = 2 * (size_t)kBM * kBK * 4 + 2 * (size_t)BN * kBK * 4;
+  int stages = kMaxStages;
+  while (stages > 1 && 2048 + stages * stage > 220 * 1024) --stages;
+  p.stages = stages;
+  const size_t smem = 2048 + stages * stage;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(wgrad_tf32x3_kernel<BN>), smem)) return rc;
+  dim3 grid((unsigned)((p.M + kBM - 1) / kBM), (unsigned)((p.N + BN - 1) / BN), (unsigned)splits);
+  wgrad_tf32x3_kernel<BN><<<grid, kWgThreads, smem, stream>>>(tx, ty, p);
+  return check_cuda(cudaGetLastError(), "wgrad_tf32x3_kernel launch");
+}
+
 }  // namespace layer
 }  // namespace ossm_b200
 
@@ -334,6 +534,46 @@ int ossm_b200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count
   if (!w || !w_hi || !w_lo) { set_last_error("split_tf32: null pointer"); return kErrInvalidArgument; }
   layer::split_tf32_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(w, w_hi, w_lo, count);
   return check_cuda(cudaGetLastError(), "split_tf32_kernel launch");
+}
+
+size_t ossm_b200_wgrad_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t batch, int64_t length) {
+  if (M <= 0 || N <= 0 || batch <= 0 || length <= 0) return 0;
+  return (size_t)layer::wgrad_splits(M, N, batch, length) * (size_t)M * (size_t)N * sizeof(float);
+}
+
+int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int y_time_major, float* partial,
+                           size_t partial_bytes, int* splits_out, int64_t M, int64_t N, int64_t batch, int64_t length,
+                           cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0 || length <= 0) { set_last_error("wgrad_tf32x3: extents must be positive"); return kErrInvalidArgument; }
+  if (!X || !Y || !partial || !splits_out) { set_last_error("wgrad_tf32x3: null pointer"); return kErrInvalidArgument; }
+  if ((M % 32) != 0 || (N % 32) != 0) {
+    set_last_error("wgrad_tf32x3: M and N must be multiples of 32 (column blocks of the operand tiles)");
+    return kErrUnsupported;
+  }
+  const int splits = layer::wgrad_splits(M, N, batch, length);
+  if (partial_bytes < (size_t)splits * M * N * sizeof(float)) { set_last_error("wgrad_tf32x3: workspace too small"); return kErrWorkspace; }
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  auto make = [&](CUtensorMap* tm, const float* base, long long C, bool time_major, uint32_t tile) {
+    // dims innermost first: 32 columns of a block, time, column block, batch
+    const uint64_t dims[4] = {32, (uint64_t)length, (uint64_t)(C / 32), (uint64_t)batch};
+    const uint64_t row = (uint64_t)C * 4;
+    const uint64_t strides[3] = {time_major ? row * (uint64_t)batch : row, 128,
+                                 time_major ? row : row * (uint64_t)length};
+    const uint32_t box[4] = {32, (uint32_t)layer::kBK, tile / 32, 1};
+    return make_tensor_map_4d_f32_sw128(tm, base, dims, strides, box);
+  };
+  CUtensorMap tx, ty;
+  if (!make(&tx, X, M, x_time_major != 0, layer::kBM) || !make(&ty, Y, N, y_time_major != 0, (uint32_t)BN)) {
+    set_last_error("wgrad_tf32x3: operands must be 16-byte aligned dense matrices");
+    return kErrUnsupported;
+  }
+  layer::WgradParams p{};
+  p.partial = partial; p.M = M; p.N = N; p.batch = batch; p.length = length;
+  p.slices_per_batch = (int)((length + layer::kBK - 1) / layer::kBK);
+  *splits_out = splits;
+  if (BN == 256) return layer::launch_wgrad<256>(tx, ty, p, splits, stream);
+  if (BN == 128) return layer::launch_wgrad<128>(tx, ty, p, splits, stream);
+  return layer::launch_wgrad<64>(tx, ty, p, splits, stream);
 }
 
 int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, float* out, const float* aux,

@@ -256,6 +256,7 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
 #pragma unroll
       for (int r = 0; r < kBatch; ++r) cur[r] = nxt[r];
     }
+    if (p.seg_end && valid) p.seg_end[n] = make_float4(s0.x, s0.y, s1.x, s1.y);
   }
 }
 
@@ -276,6 +277,8 @@ struct BwdParams {
   int ring;
   long long seg_chunks;       // chunks per time segment (grid.y segments)
   const float4* lam_init;     // [S, N] adjoint entering each segment from the right, or null (zero)
+  const float4* state_in;     // [N] state entering the first chunk (a time slice of a longer sequence), or null (zero)
+  float4* lam_end;            // [S, N] adjoint leaving each segment on the left, or null
 };
 
 // Kahan-compensated add of a chunk-local sum into a running total.
@@ -359,7 +362,8 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
   }
 
   auto load_carry = [&](long long chunk) -> float4 {
-    if (chunk <= 0 || !valid) return make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!valid) return make_float4(0.f, 0.f, 0.f, 0.f);
+    if (chunk <= 0) return p.state_in ? ld_nc_f4(p.state_in + n) : make_float4(0.f, 0.f, 0.f, 0.f);
     return ld_nc_f4(p.carry_src + (chunk * p.carry_mul + p.carry_off) * p.N + n);
   };
 
@@ -477,6 +481,7 @@ lti_backward_kernel(const __grid_constant__ CUtensorMap tm_bu, const __grid_cons
     const long long SN = (long long)gridDim.y * p.N;
 #pragma unroll
     for (int i = 0; i < kNumAcc; ++i) p.partials[(long long)i * SN + (long long)blockIdx.y * p.N + n] = acc[i];
+    if (p.lam_end) p.lam_end[(long long)blockIdx.y * p.N + n] = make_float4(l0.x, l0.y, l1.x, l1.y);
   }
 }
 
@@ -785,9 +790,9 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
   FwdParams q = p;
   q.seg_chunks = nchunks;
-  q.seg_init = nullptr;
-  q.seg_end = nullptr;
-  if (tma && use_twolevel(V, p.L, p.N)) {
+  // a time slice of a longer sequence (state handed in / out by the caller) runs as one segment
+  const bool slice = p.seg_init != nullptr || p.seg_end != nullptr;
+  if (tma && !slice && use_twolevel(V, p.L, p.N)) {
     CUtensorMap tm2;
     memset(&tm2, 0, sizeof(tm2));
     if (make_tensor_map_2d_f32(&tm2, p.bu, (uint64_t)p.N * 2, (uint64_t)p.L, (uint64_t)p.N * 8, kTlCols * 2,
@@ -804,7 +809,7 @@ static int launch_forward_out(const FwdParams& p, cudaStream_t stream, void* wor
   if (tma) {
     q.ring = g_tuning.fwd_ring;
     const size_t smem = 1024 + (size_t)warps * q.ring * kStageBytes;
-    int S = pick_segments_for<V>(p.L, p.N, warps);
+    int S = slice ? 1 : pick_segments_for<V>(p.L, p.N, warps);
     if (workspace == nullptr || ws_bytes < forward_ws_bytes(S, p.N)) S = 1;
     if (S > 1) {
       // pass 1: per-segment end states from zero; pass 2: stitch; pass 3: the scan proper
@@ -865,9 +870,9 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   const long long nchunks = (p.L + kChunk - 1) / kChunk;
   BwdParams q = p;
   q.seg_chunks = nchunks;
-  q.lam_init = nullptr;
+  const bool slice = p.lam_init != nullptr || p.lam_end != nullptr || p.state_in != nullptr;
   int S = 1;
-  if (tma && use_twolevel(V, p.L, p.N) && ws_bytes >= twolevel_backward_ws_bytes(p.N)) {
+  if (tma && !slice && use_twolevel(V, p.L, p.N) && ws_bytes >= twolevel_backward_ws_bytes(p.N)) {
     CUtensorMap tb, tg;
     memset(&tb, 0, sizeof(tb));
     memset(&tg, 0, sizeof(tg));
@@ -890,7 +895,7 @@ static int launch_backward(const BwdParams& p, float* grad_a, float* grad_g, flo
   }
   if (tma) {
     q.ring = g_tuning.bwd_ring;
-    S = pick_segments_for<V>(p.L, p.N, warps);
+    S = slice ? 1 : pick_segments_for<V>(p.L, p.N, warps);
     if (ws_bytes < backward_ws_bytes(S, p.N)) S = 1;
     if (S > 1) {
       q.seg_chunks = (nchunks + S - 1) / S;
@@ -1035,6 +1040,36 @@ int ossm_b200_lti_scan_forward_ws(int variant, const float* a, const float* g, c
   return forward_dispatch(variant, p, stream, workspace, workspace_bytes);
 }
 
+int ossm_b200_lti_scan_forward_slice(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                     void* x, void* carries, const void* state_in, void* state_out, int64_t L,
+                                     int64_t B, int64_t P, cudaStream_t stream) {
+  if (int rc = check_common("lti_scan_forward_slice", variant, a, g, step, L, B, P)) return rc;
+  if (variant == kDiag) { set_last_error("lti_scan_forward_slice: not available for the diagonal variant"); return kErrUnsupported; }
+  if (B == 0 || P == 0) return kOk;
+  if (L == 0) {
+    if (state_out == nullptr) return kOk;
+    if (state_in) return check_cuda(cudaMemcpyAsync(state_out, state_in, (size_t)B * P * 16, cudaMemcpyDeviceToDevice, stream), "state copy");
+    return check_cuda(cudaMemsetAsync(state_out, 0, (size_t)B * P * 16, stream), "state clear");
+  }
+  if (bu == nullptr || x == nullptr) { set_last_error("lti_scan_forward_slice: null bu or x"); return kErrInvalidArgument; }
+  if ((reinterpret_cast<uintptr_t>(bu) & 7u) || (reinterpret_cast<uintptr_t>(x) & 7u) ||
+      (reinterpret_cast<uintptr_t>(carries) & 15u) || (reinterpret_cast<uintptr_t>(state_in) & 15u) ||
+      (reinterpret_cast<uintptr_t>(state_out) & 15u)) {
+    set_last_error("lti_scan_forward_slice: misaligned buffer (bu/x need 8 B, carries/states 16 B)");
+    return kErrInvalidArgument;
+  }
+  FwdParams p;
+  p.a = a; p.g = needs_g(variant) ? g : nullptr; p.step = step;
+  p.bu = static_cast<const float2*>(bu);
+  p.x = static_cast<float2*>(x);
+  p.states = nullptr;
+  p.carries = static_cast<float4*>(carries);
+  p.L = L; p.N = B * P; p.P = P; p.ring = 0; p.seg_chunks = 0;
+  p.seg_init = static_cast<const float4*>(state_in);
+  p.seg_end = static_cast<float4*>(state_out);
+  return forward_dispatch(variant, p, stream, nullptr, 0);
+}
+
 int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, const float* step, const void* bu,
                                void* x, void* states, void* carries, int64_t L, int64_t B, int64_t P,
                                cudaStream_t stream) {
@@ -1045,7 +1080,9 @@ int ossm_b200_lti_scan_forward(int variant, const float* a, const float* g, cons
 static int backward_common(const char* fn, int variant, const float* a, const float* g, const float* step,
                            const void* bu, const void* carry_src, long long mul, long long off, const void* grad_x,
                            void* grad_bu, float* grad_a, float* grad_g, float* grad_step, void* workspace,
-                           size_t workspace_bytes, int64_t L, int64_t B, int64_t P, cudaStream_t stream) {
+                           size_t workspace_bytes, int64_t L, int64_t B, int64_t P, cudaStream_t stream,
+                           const void* state_in = nullptr, const void* adjoint_in = nullptr,
+                           void* adjoint_out = nullptr) {
   if (int rc = check_common(fn, variant, a, g, step, L, B, P)) return rc;
   if (grad_a == nullptr || (needs_step(variant) && grad_step == nullptr) || (needs_g(variant) && grad_g == nullptr)) {
     set_last_error("%s: null coefficient-gradient pointer", fn);
@@ -1086,7 +1123,10 @@ static int backward_common(const char* fn, int variant, const float* a, const fl
   p.grad_bu = static_cast<float2*>(grad_bu);
   p.partials = static_cast<float*>(workspace);
   p.L = L; p.N = B * P; p.P = P; p.ring = 0;
-  p.seg_chunks = 0; p.lam_init = nullptr;
+  p.seg_chunks = 0;
+  p.lam_init = static_cast<const float4*>(adjoint_in);
+  p.state_in = static_cast<const float4*>(state_in);
+  p.lam_end = static_cast<float4*>(adjoint_out);
   return backward_dispatch(variant, p, grad_a, needs_g(variant) ? grad_g : nullptr,
                            needs_step(variant) ? grad_step : nullptr, B, stream,
                            workspace_bytes);
@@ -1099,6 +1139,30 @@ int ossm_b200_lti_scan_backward(int variant, const float* a, const float* g, con
   // carries row r = state after step (r+1)*kChunk - 1 = carry-in of chunk r+1
   return backward_common("lti_scan_backward", variant, a, g, step, bu, carries, 1, -1, grad_x, grad_bu, grad_a,
                          grad_g, grad_step, workspace, workspace_bytes, L, B, P, stream);
+}
+
+int ossm_b200_lti_scan_backward_slice(int variant, const float* a, const float* g, const float* step, const void* bu,
+                                      const void* carries, const void* state_in, const void* grad_x,
+                                      const void* adjoint_in, void* adjoint_out, void* grad_bu, float* grad_a,
+                                      float* grad_g, float* grad_step, void* workspace, size_t workspace_bytes,
+                                      int64_t L, int64_t B, int64_t P, cudaStream_t stream) {
+  if (variant == kDiag) { set_last_error("lti_scan_backward_slice: not available for the diagonal variant"); return kErrUnsupported; }
+  if ((reinterpret_cast<uintptr_t>(state_in) & 15u) || (reinterpret_cast<uintptr_t>(adjoint_in) & 15u) ||
+      (reinterpret_cast<uintptr_t>(adjoint_out) & 15u)) {
+    set_last_error("lti_scan_backward_slice: state / adjoint buffers need 16-byte alignment");
+    return kErrInvalidArgument;
+  }
+  if (L == 0 && B > 0 && P > 0 && adjoint_out != nullptr) {
+    // an empty slice passes the adjoint through
+    if (adjoint_in) {
+      if (int rc = check_cuda(cudaMemcpyAsync(adjoint_out, adjoint_in, (size_t)B * P * 16, cudaMemcpyDeviceToDevice, stream), "adjoint copy")) return rc;
+    } else if (int rc = check_cuda(cudaMemsetAsync(adjoint_out, 0, (size_t)B * P * 16, stream), "adjoint clear")) {
+      return rc;
+    }
+  }
+  return backward_common("lti_scan_backward_slice", variant, a, g, step, bu, carries, 1, -1, grad_x, grad_bu, grad_a,
+                         grad_g, grad_step, workspace, workspace_bytes, L, B, P, stream, state_in, adjoint_in,
+                         adjoint_out);
 }
 
 // ---------------------------------------------------------------------------

@@ -12,8 +12,9 @@ operands: float32-level accuracy), which read and write the time-major complex s
              grad_u = gemm(grad_bu, [B_re|B_im]^T) + D*grad_y                                   (fused)
 
 No permute copy, no real / imaginary split and no separate ``D*u`` pass exist.  The two weight
-gradients (``grad_B``, ``grad_C``: reductions over all ``B*L`` rows into ``[2P, H]``) are strided
-batched library GEMMs (cuBLAS through ``torch.bmm``, float32).
+gradients (``grad_B``, ``grad_C``: reductions over all ``B*L`` rows into ``[2P, H]``) run on the tensor
+cores as well (:func:`ossm_b200.kernels.wgrad_tf32x3`, split over the rows, partials summed in a fixed
+order) when ``2P`` and ``H`` are multiples of 32, else as strided batched library GEMMs.
 
 Parameters have the reference's shapes: ``B [P, H, 2]``, ``C [H, P, 2]`` (real / imaginary last,
 ``dlinoss.py:93-98``), ``D [H]``; ``a_diag, g_diag, step [P]`` are the projected coefficients the
@@ -42,6 +43,17 @@ def pack_output_weights(C: Tensor) -> Tensor:
     H, P, _ = C.shape
     sign = torch.tensor([1.0, -1.0], dtype=C.dtype, device=C.device)
     return (C * sign).reshape(H, 2 * P).contiguous()
+
+
+def weight_gradient(X: Tensor, x_time_major: bool, Y: Tensor, y_time_major: bool, batch: int, length: int) -> Tensor:
+    """``sum_(b,l) X[row(b,l)]^T Y[row(b,l)]`` -> ``[M, N]``.  On the tensor cores when both widths are multiples of
+    32 (column blocks of the operand tiles), otherwise one strided batched library GEMM (cuBLAS, float32)."""
+    M, N = X.size(1), Y.size(1)
+    if M % 32 == 0 and N % 32 == 0:
+        return kernels.wgrad_tf32x3(X, x_time_major, Y, y_time_major, batch, length)
+    xb = X.view(length, batch, M).permute(1, 2, 0) if x_time_major else X.view(batch, length, M).transpose(1, 2)
+    yb = Y.view(length, batch, N).permute(1, 0, 2) if y_time_major else Y.view(batch, length, N)
+    return torch.bmm(xb, yb).sum(0)
 
 
 class DLinossLayerFn(torch.autograd.Function):
@@ -87,12 +99,10 @@ class DLinossLayerFn(torch.autograd.Function):
         kernels.gemm_tf32x3(gbu2.view(length * batch, 2 * ssm), *kernels.split_tf32(w_in.t().contiguous()),
                             grad_u.view(batch * length, hidden), aux=gy, diag=D.contiguous(),
                             row_map=kernels.ROWS_TIME_TO_BATCH, batch=batch, length=length)
-        # weight gradients: sums over every (b, l) row; one strided batched library GEMM each
-        u3 = u2.view(batch, length, hidden)
-        gy3 = gy.view(batch, length, hidden)
+        # weight gradients: sums over every (b, l) row of products of a time-major and a batch-major matrix
         x2 = torch.view_as_real(x).view(length, batch, 2 * ssm)
-        grad_w_in = torch.bmm(gbu2.permute(1, 2, 0), u3).sum(0)                      # [2P, H]
-        grad_w_out = torch.bmm(gy3.transpose(1, 2), x2.permute(1, 0, 2)).sum(0)      # [H, 2P]
+        grad_w_in = weight_gradient(gbu2.view(length * batch, 2 * ssm), True, u2, False, batch, length)     # [2P, H]
+        grad_w_out = weight_gradient(gy, False, x2.view(length * batch, 2 * ssm), True, batch, length)      # [H, 2P]
         grad_D = (gy * u2).sum(0)
         grad_B = grad_w_in.view(ssm, 2, hidden).permute(0, 2, 1).contiguous()
         sign = torch.tensor([1.0, -1.0], dtype=grad_w_out.dtype, device=dev)

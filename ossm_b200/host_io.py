@@ -2,16 +2,15 @@
 
 ``scan_from_host`` runs forward + backward of the scan on host buffers and
 returns host buffers.  PCIe is the bottleneck of such a call (the scan itself
-runs at HBM speed), so the work is cut into batch slices -- independent series --
-and pipelined: while slice ``i`` is scanned, slice ``i+1`` is on its way up and
-the results of slice ``i-1`` are on their way down, which keeps both PCIe
-directions busy.  A batch slice of a time-major ``[L, B, P]`` tensor is a pitched
-2-D region; it is moved with ``cudaMemcpy2DAsync`` (one call per slice and
-tensor) into a dense device buffer, which is what the kernels take.
+runs at HBM speed), so the work is cut into slices and pipelined: while slice
+``i`` is scanned, slice ``i+1`` is on its way up and the results of slice ``i-1``
+are on their way down, which keeps both PCIe directions busy.  The slices are
+pieces of the TIME axis: a time slice of a time-major ``[L, B, P]`` tensor is one
+dense block (plain ``cudaMemcpyAsync``), and the kernels hand the recurrence state
+from one slice to the next on the device.
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Optional, Tuple
 
 import torch
@@ -21,47 +20,10 @@ from . import kernels
 
 __all__ = ["scan_from_host"]
 
-_H2D, _D2H = 1, 2
-_cudart = None
-
-
-def _rt():
-    global _cudart
-    if _cudart is None:
-        import glob
-        import os
-
-        cands = []
-        for base in (os.path.join(os.path.dirname(torch.__file__), "lib"), "/usr/local/cuda/lib64"):
-            cands += sorted(glob.glob(os.path.join(base, "libcudart.so*")))
-        for root, _dirs, files in os.walk(os.path.join(os.path.dirname(os.path.dirname(torch.__file__)), "nvidia")):
-            cands += [os.path.join(root, f) for f in files if f.startswith("libcudart.so")]
-        last = None
-        for path in cands + ["libcudart.so.12", "libcudart.so"]:
-            try:
-                _cudart = ctypes.CDLL(path)
-                break
-            except OSError as exc:
-                last = exc
-        if _cudart is None:
-            raise RuntimeError(f"ossm_b200: cannot load the CUDA runtime for pitched copies: {last}")
-        _cudart.cudaMemcpy2DAsync.restype = ctypes.c_int
-        _cudart.cudaMemcpy2DAsync.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t,
-                                              ctypes.c_size_t, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
-    return _cudart
-
-
-def _copy2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width: int, height: int, kind: int,
-            stream: torch.cuda.Stream) -> None:
-    rc = _rt().cudaMemcpy2DAsync(ctypes.c_void_p(dst_ptr), dst_pitch, ctypes.c_void_p(src_ptr), src_pitch, width,
-                                 height, kind, ctypes.c_void_p(stream.cuda_stream))
-    if rc != 0:
-        raise RuntimeError(f"ossm_b200: cudaMemcpy2DAsync failed with error {rc}")
-
 
 def scan_from_host(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu_host: Tensor,
                    grad_x_host: Optional[Tensor], x_host: Tensor, grad_bu_host: Optional[Tensor] = None, *,
-                   slices: int = 8, device: Optional[torch.device] = None, copies_only: bool = False
+                   slices: int = 16, device: Optional[torch.device] = None, copies_only: bool = False
                    ) -> Optional[Tuple[Tensor, Optional[Tensor], Tensor]]:
     """Forward (and, when ``grad_x_host`` is given, backward) of the oscillator scan on
     pinned host tensors ``[L, B, P]`` complex64; results are written to ``x_host`` /
@@ -70,6 +32,13 @@ def scan_from_host(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, b
     The call returns when all results are in host memory.  ``copies_only=True`` moves the same bytes
     through the same pipeline without launching the kernels (the results are then meaningless): the
     ceiling the host and PCIe side puts on this call, for measurements.
+
+    The sequence is cut into ``slices`` pieces along TIME: in the time-major layout a time slice is one
+    contiguous block, so every transfer is a plain ``cudaMemcpyAsync`` of a dense range.  The recurrence
+    state is handed from slice to slice on the device (``lti_scan_forward_slice`` / ``_backward_slice``);
+    ``bu`` stays resident between its forward and backward use.  Upload order: ``bu`` first to last slice,
+    then ``grad_x`` last to first; download order: ``x`` first to last, then ``grad_bu`` last to first -- both
+    PCIe directions are busy from the second slice on.
     """
     dev = device or a.device
     L, B, P = bu_host.shape
@@ -80,59 +49,97 @@ def scan_from_host(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, b
     backward = grad_x_host is not None
     if backward and grad_bu_host is None:
         raise RuntimeError("ossm_b200: grad_bu_host is required for the backward pass")
-    slices = max(1, min(slices, B))
-    bounds = [(B * i) // slices for i in range(slices + 1)]
-    bmax = max(b1 - b0 for b0, b1 in zip(bounds, bounds[1:]))
+    if L == 0 or B == 0 or P == 0:
+        if not backward:
+            return None
+        return tuple(torch.zeros_like(t) if t is not None else None for t in (a, g, step))
+    chunk = kernels.lti_chunk()
+    nchunks = (L + chunk - 1) // chunk
+    slices = max(1, min(slices, nchunks))
+    # slice boundaries on multiples of the carry interval
+    bounds = sorted({min(L, ((nchunks * i) // slices) * chunk) for i in range(slices)} | {L})
+    spans = list(zip(bounds[:-1], bounds[1:]))
+    lmax = max(l1 - l0 for l0, l1 in spans)
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream()
         up, down = torch.cuda.Stream(), torch.cuda.Stream()
-        # two sets of device buffers so that slice i+1 can arrive while slice i is in use
-        bufs = [{k: torch.empty((L, bmax, P), dtype=torch.complex64, device=dev)
-                 for k in (("bu", "gx", "x", "gbu") if backward else ("bu", "x"))} for _ in range(2)]
-        free = [torch.cuda.Event(), torch.cuda.Event()]      # buffer set no longer read or written
-        for e in free:
+        bu_dev = torch.empty((L, B, P), dtype=torch.complex64, device=dev) if backward else None
+        # rotating buffers: slice i+1 arrives / slice i-1 leaves while slice i is scanned
+        def ring(n):
+            return [torch.empty((lmax, B, P), dtype=torch.complex64, device=dev) for _ in range(n)]
+
+        xbuf = ring(2)
+        bubuf = ring(2) if not backward else None
+        gxbuf, gbubuf = (ring(2), ring(2)) if backward else (None, None)
+        free_x = [torch.cuda.Event(), torch.cuda.Event()]       # download of the buffer finished
+        free_in = [torch.cuda.Event(), torch.cuda.Event()]      # kernel reading the upload buffer finished
+        for e in free_x + free_in:
             e.record(main)
-        grads = None
-        elem = 8
-        pitch_h = B * P * elem
-        for i, (b0, b1) in enumerate(zip(bounds, bounds[1:])):
-            nb = b1 - b0
-            if nb == 0:
-                continue
-            set_ = bufs[i % 2]
-            width = nb * P * elem
-            views = {k: v.view(-1)[: L * nb * P].view(L, nb, P) for k, v in set_.items()}
-            up.wait_event(free[i % 2])
-            off = b0 * P * elem
-            _copy2d(views["bu"].data_ptr(), width, bu_host.data_ptr() + off, pitch_h, width, L, _H2D, up)
-            arrived_bu = torch.cuda.Event()
-            arrived_bu.record(up)
-            if backward:
-                _copy2d(views["gx"].data_ptr(), width, grad_x_host.data_ptr() + off, pitch_h, width, L, _H2D, up)
-                arrived_gx = torch.cuda.Event()
-                arrived_gx.record(up)
-            main.wait_event(arrived_bu)
+        states = [None]          # state entering slice i
+        carries = []
+        # ---- forward, first slice to last ------------------------------------------------------------
+        for i, (l0, l1) in enumerate(spans):
+            n = l1 - l0
+            src = bu_dev[l0:l1] if backward else bubuf[i % 2][:n]
+            if not backward:
+                up.wait_event(free_in[i % 2])
+            with torch.cuda.stream(up):
+                src.copy_(bu_host[l0:l1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(up)
+            main.wait_event(arrived)
+            main.wait_event(free_x[i % 2])
+            xv = xbuf[i % 2][:n]
             if not copies_only:
-                x, _, carries = kernels.lti_scan_forward(variant, a, g, step, views["bu"], want_carries=backward)
-                views["x"].copy_(x)     # device-to-device into the staging buffer (keeps `x` out of the copy stream)
-            done_fwd = torch.cuda.Event()
-            done_fwd.record(main)
-            down.wait_event(done_fwd)
-            _copy2d(x_host.data_ptr() + off, pitch_h, views["x"].data_ptr(), width, width, L, _D2H, down)
-            if backward:
-                main.wait_event(arrived_gx)
+                _, car, st_out = kernels.lti_scan_forward_slice(variant, a, g, step, src, state_in=states[-1],
+                                                                want_state_out=backward or i + 1 < len(spans), x_out=xv)
+                carries.append(car if backward else None)
+                states.append(st_out)
+            done = torch.cuda.Event()
+            done.record(main)
+            if not backward:
+                free_in[i % 2] = done
+            with torch.cuda.stream(down):
+                down.wait_event(done)
+                x_host[l0:l1].copy_(xv, non_blocking=True)
+                free_x[i % 2] = torch.cuda.Event()
+                free_x[i % 2].record(down)
+        grads = None
+        if backward:
+            # ---- backward, last slice to first -------------------------------------------------------
+            adjoint = None
+            free_g = [torch.cuda.Event(), torch.cuda.Event()]
+            free_gb = [torch.cuda.Event(), torch.cuda.Event()]
+            for e in free_g + free_gb:
+                e.record(main)
+            for j, i in enumerate(reversed(range(len(spans)))):
+                l0, l1 = spans[i]
+                n = l1 - l0
+                gv = gxbuf[j % 2][:n]
+                with torch.cuda.stream(up):
+                    up.wait_event(free_g[j % 2])
+                    gv.copy_(grad_x_host[l0:l1], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(up)
+                main.wait_event(arrived)
+                main.wait_event(free_gb[j % 2])
+                gb = gbubuf[j % 2][:n]
                 if not copies_only:
-                    ga, gg, gs, gbu = kernels.lti_scan_backward(variant, a, g, step, views["bu"], carries, views["gx"])
-                    views["gbu"].copy_(gbu)
+                    ga, gg, gs, _, adjoint = kernels.lti_scan_backward_slice(
+                        variant, a, g, step, bu_dev[l0:l1], carries[i], gv, state_in=states[i], adjoint_in=adjoint,
+                        want_adjoint_out=i > 0, grad_bu_out=gb)
                     part = (ga, gg, gs)
                     grads = part if grads is None else tuple(
                         (p + q) if p is not None else None for p, q in zip(grads, part))
-                done_bwd = torch.cuda.Event()
-                done_bwd.record(main)
-                down.wait_event(done_bwd)
-                _copy2d(grad_bu_host.data_ptr() + off, pitch_h, views["gbu"].data_ptr(), width, width, L, _D2H, down)
-            free[i % 2] = torch.cuda.Event()
-            free[i % 2].record(down)
+                done = torch.cuda.Event()
+                done.record(main)
+                free_g[j % 2] = done
+                with torch.cuda.stream(down):
+                    down.wait_event(done)
+                    grad_bu_host[l0:l1].copy_(gb, non_blocking=True)
+                    free_gb[j % 2] = torch.cuda.Event()
+                    free_gb[j % 2].record(down)
         main.wait_stream(down)
+        main.wait_stream(up)
         main.synchronize()
     return grads if backward else None

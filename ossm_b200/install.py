@@ -111,7 +111,25 @@ def _wrap_try_selective_scan(ours):
     return try_selective_scan
 
 
-def install_as_ossm_kernels(patch_ops: bool = True) -> None:
+def _wrap_mixer_forward(original):
+    def forward(self, inputs):
+        covered = (inputs.is_cuda and inputs.dtype in (torch.float32, torch.bfloat16) and self.d_conv <= 4
+                   and 0 < self.d_state <= MAX_D_STATE and not torch.is_autocast_enabled())
+        if covered:
+            from .mixer import mamba_mixer_forward
+
+            return mamba_mixer_forward(self, inputs.float()).to(inputs.dtype)
+        return original(self, inputs)
+
+    forward.__wrapped__ = original
+    return forward
+
+
+def install_as_ossm_kernels(patch_ops: bool = True, fuse_mixer: bool = False) -> None:
+    """``fuse_mixer=True`` also replaces ``_MambaMixer.forward`` (the class, its parameters and its state dict
+    stay ossm's) by :func:`ossm_b200.mixer.mamba_mixer_forward`: causal conv1d + SiLU in one kernel and
+    ``softplus(dt_proj(.))`` folded into the scan (``mambarec.py:143-171``); inputs outside the library's scope
+    keep ossm's own forward."""
     from . import kernels
 
     already = "ossm" in sys.modules
@@ -165,6 +183,10 @@ def install_as_ossm_kernels(patch_ops: bool = True) -> None:
             original = getattr(mods[name], attr)
             original = getattr(original, "__wrapped__", original)
             setattr(mods[name], attr, _wrap_diag_fn(diag.DiagScanFn, original))
+    if fuse_mixer and "mambarec" in mods:
+        cls = mods["mambarec"]._MambaMixer
+        original = getattr(cls.forward, "__wrapped__", cls.forward)
+        cls.forward = _wrap_mixer_forward(original)
     wrapped = _wrap_try_selective_scan(selective_scan.try_selective_scan)
     if "_selective_scan" in mods:
         mods["_selective_scan"].try_selective_scan = wrapped

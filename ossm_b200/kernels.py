@@ -141,6 +141,58 @@ def lti_scan_backward(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor
     return _lti_backward("ossm_b200_lti_scan_backward", variant, a, g, step, bu, carries, grad_x)
 
 
+def lti_scan_forward_slice(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor, *,
+                           state_in: Optional[Tensor] = None, want_state_out: bool = True,
+                           x_out: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Optional[Tensor]]:
+    """The scan over one time slice of a longer sequence: ``state_in [B, P, 2]`` complex64 is the state entering
+    the slice (``None`` = zero).  Returns ``(x, carries, state_out)``; ``x_out`` receives ``x`` when given."""
+    vid = VARIANT_IDS[variant]
+    L, B, P = _check_lti_inputs(a, g, step, bu)
+    dev = bu.device
+    x = x_out if x_out is not None else torch.empty((L, B, P), dtype=torch.complex64, device=dev)
+    if tuple(x.shape) != (L, B, P) or x.dtype != torch.complex64 or not x.is_contiguous() or x.device != dev:
+        raise RuntimeError("ossm_b200: x_out must be a contiguous complex64 [L, B, P] tensor on the device of bu")
+    rows = max((L + lti_chunk() - 1) // lti_chunk() - 1, 0)
+    carries = torch.empty((rows, B, P, 2), dtype=torch.complex64, device=dev)
+    state_out = torch.empty((B, P, 2), dtype=torch.complex64, device=dev) if want_state_out else None
+    if state_in is not None and (tuple(state_in.shape) != (B, P, 2) or state_in.dtype != torch.complex64
+                                 or not state_in.is_contiguous()):
+        raise RuntimeError("ossm_b200: state_in must be a contiguous complex64 [B, P, 2] tensor")
+    with torch.cuda.device(dev):
+        rc = _lib.load().ossm_b200_lti_scan_forward_slice(
+            vid, _p(a), _p(g), _p(step), _p(bu), _p(x), _p(carries) if carries.numel() else None, _p(state_in),
+            _p(state_out), L, B, P, _stream(dev))
+    _lib.check(rc, "lti_scan_forward_slice")
+    return x, carries, state_out
+
+
+def lti_scan_backward_slice(variant: str, a: Tensor, g: Optional[Tensor], step: Tensor, bu: Tensor, carries: Tensor,
+                            grad_x: Tensor, *, state_in: Optional[Tensor] = None, adjoint_in: Optional[Tensor] = None,
+                            want_adjoint_out: bool = True, grad_bu_out: Optional[Tensor] = None):
+    """Backward of one time slice (slices run last to first): returns ``(grad_a, grad_g, grad_step, grad_bu,
+    adjoint_out)`` where the coefficient gradients are this slice's share."""
+    vid = VARIANT_IDS[variant]
+    L, B, P = _check_lti_inputs(a, g, step, bu)
+    dev = bu.device
+    if grad_x.shape != bu.shape or grad_x.dtype != torch.complex64 or not grad_x.is_contiguous():
+        raise RuntimeError("grad_output must match bu shape")
+    grad_bu = grad_bu_out if grad_bu_out is not None else torch.empty_like(bu)
+    grad_a = torch.empty_like(a)
+    grad_g = torch.empty_like(g) if g is not None else None
+    grad_step = torch.empty_like(step)
+    adjoint_out = torch.empty((B, P, 2), dtype=torch.complex64, device=dev) if want_adjoint_out else None
+    lib = _lib.load()
+    ws_bytes = int(lib.ossm_b200_lti_backward_workspace_bytes(L, B, P))
+    workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.ossm_b200_lti_scan_backward_slice(
+            vid, _p(a), _p(g), _p(step), _p(bu), _p(carries) if carries is not None and carries.numel() else None,
+            _p(state_in), _p(grad_x), _p(adjoint_in), _p(adjoint_out), _p(grad_bu), _p(grad_a), _p(grad_g),
+            _p(grad_step), _p(workspace), ws_bytes, L, B, P, _stream(dev))
+    _lib.check(rc, "lti_scan_backward_slice")
+    return grad_a, grad_g, grad_step, grad_bu, adjoint_out
+
+
 # ---- reference-compatible D-LinOSS entry points ----------------------------
 def _make_dlinoss(variant: str):
     def forward(a_diag: Tensor, g_diag: Tensor, step: Tensor, bu: Tensor) -> Tensor:
@@ -661,6 +713,27 @@ def gemm_tf32x3(A: Tensor, w_hi: Tensor, w_lo: Tensor, out: Tensor, *, aux: Opti
                                                _stream(A.device))
     _lib.check(rc, "gemm_tf32x3")
     return out
+
+
+def wgrad_tf32x3(X: Tensor, x_time_major: bool, Y: Tensor, y_time_major: bool, batch: int, length: int) -> Tensor:
+    """``out [M, N] = sum_(b,l) X[row(b,l), :]^T Y[row(b,l), :]`` on the tensor cores (three TF32 products of split
+    operands).  ``X [batch*length, M]``, ``Y [batch*length, N]`` dense float32; each has its rows in batch-major
+    (``b*length + l``) or time-major (``l*batch + b``) order.  ``M`` and ``N`` must be multiples of 32."""
+    for name, t in (("X", X), ("Y", Y)):
+        _require_cuda(name, t)
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.dim() != 2 or t.size(0) != batch * length:
+            raise RuntimeError(f"ossm_b200: {name} must be a contiguous float32 [batch*length, C] CUDA matrix")
+    M, N = X.size(1), Y.size(1)
+    lib = _lib.load()
+    ws_bytes = int(lib.ossm_b200_wgrad_tf32x3_workspace_bytes(M, N, batch, length))
+    partial = torch.empty(ws_bytes // 4, dtype=torch.float32, device=X.device)
+    splits = ctypes.c_int(0)
+    with torch.cuda.device(X.device):
+        rc = lib.ossm_b200_wgrad_tf32x3(_p(X), int(bool(x_time_major)), _p(Y), int(bool(y_time_major)), _p(partial),
+                                        ws_bytes, ctypes.byref(splits), M, N, int(batch), int(length),
+                                        _stream(X.device))
+    _lib.check(rc, "wgrad_tf32x3")
+    return partial[: splits.value * M * N].view(splits.value, M, N).sum(0)
 
 
 # ---- names ossm calls unconditionally but that are outside this library ------

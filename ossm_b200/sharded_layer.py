@@ -107,7 +107,12 @@ class _ProjectIn(torch.autograd.Function):
                                 length=length)
         else:
             grad_u = (g.permute(1, 0, 2).reshape(batch * length, p2) @ w_in).view(batch, length, hidden)
-        grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
+        if ctx.use_kernels:
+            from .dlinoss_layer import weight_gradient
+
+            grad_w = weight_gradient(g.view(length * batch, p2), True, u2, False, batch, length)
+        else:
+            grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
         return grad_u, grad_w, None
 
 
@@ -184,7 +189,12 @@ class _ProjectOutReduce(torch.autograd.Function):
         else:
             flat = (gy2 @ w_out).view(batch, length, p2 // 2, 2).permute(1, 0, 2, 3).contiguous()
             grad_x = torch.view_as_complex(flat)
-        grad_w = torch.bmm(gy2.view(batch, length, hidden).transpose(1, 2), xr.permute(1, 0, 2)).sum(0)
+        if ctx.use_kernels:
+            from .dlinoss_layer import weight_gradient
+
+            grad_w = weight_gradient(gy2, False, xr.view(length * batch, p2), True, batch, length)
+        else:
+            grad_w = torch.bmm(gy2.view(batch, length, hidden).transpose(1, 2), xr.permute(1, 0, 2)).sum(0)
         return grad_x, grad_w, None, None, None, None
 
 

@@ -79,6 +79,27 @@ def test_column_planes():
     assert rel(out, want) <= 5e-6
 
 
+@pytest.mark.parametrize("orders", [(True, False), (False, True), (False, False), (True, True)])
+@pytest.mark.parametrize("shape", [(2, 100, 64, 32), (3, 257, 128, 256), (8, 1024, 512, 256), (1, 31, 32, 96)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_weight_gradient_product(shape, orders):
+    """sum over (b, l) of X[row]^T Y[row] with the two row orders mixed; ragged lengths (partial last slice per
+    batch entry) and more splits than slices included."""
+    from ossm_b200 import kernels as K
+
+    Bz, L, M, N = shape
+    xt, yt = orders
+    gen = torch.Generator().manual_seed(sum(shape))
+    X = torch.randn(Bz, L, M, generator=gen)
+    Y = torch.randn(Bz, L, N, generator=gen)
+    want = torch.einsum("blm,bln->mn", X.double(), Y.double())
+    Xd = (X.permute(1, 0, 2) if xt else X).contiguous().view(Bz * L, M).cuda()
+    Yd = (Y.permute(1, 0, 2) if yt else Y).contiguous().view(Bz * L, N).cuda()
+    out = K.wgrad_tf32x3(Xd, xt, Yd, yt, Bz, L)
+    assert out.shape == (M, N)
+    assert record(f"wgrad_tf32x3 {Bz}x{L}x{M}x{N}", "out", rel(out.cpu(), want), 5e-6) <= 5e-6
+
+
 def test_rejects_bad_arguments():
     from ossm_b200 import kernels as K
 

@@ -336,6 +336,46 @@ def test_full_size_adjoint_and_linearity(K):
 
 
 # ---------------------------------------------------------------------------
+# time slices (state handed over by the caller)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("variant", ["imex1", "im", "linoss_imex"])
+@pytest.mark.parametrize("cuts", [(37,), (32, 64), (1, 50, 99)], ids=lambda c: "-".join(map(str, c)))
+def test_time_slices_match_oracle(K, variant, cuts):
+    """A sequence scanned slice by slice (forward first to last, backward last to first, state and adjoint
+    handed over) gives the oracle's answer; cuts inside and on chunk boundaries, odd series count included."""
+    L, B, P = 100, 3, 35
+    a, g, st, bu, gx = make_case(L, B, P, seed=sum(cuts))
+    ref, da, dg, ds, dbu = oracle(variant, a, g, st, bu, gx)
+    gv = None if variant.startswith("linoss") else dev(g)
+    ad, sd, bud, gxd = dev(a), dev(st), dev(bu), dev(gx)
+    bounds = [0, *cuts, L]
+    spans = list(zip(bounds[:-1], bounds[1:]))
+    states, carries, xs = [None], [], []
+    for l0, l1 in spans:
+        x, car, out = K.lti_scan_forward_slice(variant, ad, gv, sd, bud[l0:l1].contiguous(), state_in=states[-1])
+        xs.append(x)
+        carries.append(car)
+        states.append(out)
+    x = torch.cat(xs, 0)
+    assert so.max_rel_err(x.cpu().numpy(), ref[..., 1]) <= TOL_STATE
+    assert so.max_rel_err(states[-1].cpu().numpy(), ref[-1]) <= TOL_STATE
+    adjoint, gbus, acc = None, [None] * len(spans), None
+    for i in reversed(range(len(spans))):
+        l0, l1 = spans[i]
+        ga, gg, gs, gbu, adjoint = K.lti_scan_backward_slice(variant, ad, gv, sd, bud[l0:l1].contiguous(), carries[i],
+                                                             gxd[l0:l1].contiguous(), state_in=states[i],
+                                                             adjoint_in=adjoint)
+        gbus[i] = gbu
+        part = [ga, gg, gs]
+        acc = part if acc is None else [p + q if p is not None else None for p, q in zip(acc, part)]
+    assert so.max_rel_err(torch.cat(gbus, 0).cpu().numpy(), dbu) <= TOL_STATE
+    assert so.max_rel_err(acc[0].cpu().numpy(), da) <= TOL_COEF
+    assert so.max_rel_err(acc[2].cpu().numpy(), ds) <= TOL_COEF
+    if acc[1] is not None:
+        assert so.max_rel_err(acc[1].cpu().numpy(), dg) <= TOL_COEF
+
+
+# ---------------------------------------------------------------------------
 # time segments (long sequences of few series)
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("variant", ["imex1", "im", "linoss_imex"])
