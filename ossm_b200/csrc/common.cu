@@ -81,7 +81,7 @@ bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t c
 }
 
 bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
-                                  const uint64_t strides_bytes[3], const uint32_t box[4]) {
+                                  const uint64_t strides_bytes[3], const uint32_t box[4], bool atom32) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || box[0] * 4 != 128) return false;
@@ -98,8 +98,9 @@ bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint
   }
   CUtensorMap tmp;
   CUresult r = fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), d, st, bx, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   memcpy(map, &tmp, sizeof(tmp));
   return true;

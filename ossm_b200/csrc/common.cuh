@@ -68,10 +68,12 @@ bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, u
 // matrix descriptors of the projection kernels expect.
 bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                                   uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
-// Rank-4 float32 map with the 128-byte swizzle.  dims / box are innermost first; strides_bytes are the byte
-// strides of dimensions 1..3 (dimension 0 is dense).  box[0] * 4 must be 128.
+// Rank-4 float32 map with a 128-byte swizzle span.  dims / box are innermost first; strides_bytes are the byte
+// strides of dimensions 1..3 (dimension 0 is dense).  box[0] * 4 must be 128.  atom32 selects the variant
+// that swizzles 32-byte chunks (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), the only layout the tensor cores
+// accept for 32-bit operands whose M / N index is the contiguous one.
 bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
-                                  const uint64_t strides_bytes[3], const uint32_t box[4]);
+                                  const uint64_t strides_bytes[3], const uint32_t box[4], bool atom32);
 // Same for 16-bit elements (bf16 payloads are moved as raw 16-bit words).
 bool make_tensor_map_2d_b16(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                             uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,

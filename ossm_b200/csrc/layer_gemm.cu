@@ -301,8 +301,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 // orders (batch-major b*L + l or time-major l*B + b): a K slice is 32 consecutive time steps of one
 // batch entry, fetched from either order by a rank-4 tensor map (32 columns, time, column block, batch)
 // whose box {32, 32, tile/32, 1} lands in shared memory as column blocks of [32 rows x 128 B] -- the
-// canonical MN-major operand layout of the tensor core (leading byte offset = 4096 B between column
-// blocks, 8-row groups 1024 B apart).  Both operands are activations, so both are split into hi / lo
+// canonical MN-major operand layout of the tensor core: leading byte offset = 4096 B between column
+// blocks, K rows 128 B apart in groups of 4 (512 B, the stride byte offset).  For 32-bit operands in this
+// orientation the hardware takes one swizzle only, 32-byte chunks within the 128-byte row
+// (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B on the TMA side, layout type 1 in the matrix descriptor).  Both operands are activations, so both are split into hi / lo
 // halves by the splitter warps.  The M x N output is small and K = B*L is huge: the K slices are divided
 // over gridDim.z CTAs per output tile, each writes its partial tile, and the caller sums the partials in a
 // fixed order (deterministic, no atomics).
@@ -312,9 +314,9 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address
   d |= (uint64_t)(4096 >> 4) << 16;                 // leading byte offset: next block of 32 M/N elements
-  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset: next group of 8 K rows
+  d |= (uint64_t)(512 >> 4) << 32;                  // stride byte offset: next group of 4 K rows
   d |= (uint64_t)1 << 46;                           // descriptor version
-  d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+  d |= (uint64_t)1 << 61;                           // 128-byte swizzle span with 32-byte chunks
   return d;
 }
 // as instr_desc_tf32 with both operands MN-major (bits 15 and 16)
@@ -398,7 +400,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const uint32_t x_hi = st, x_lo = st + kXTile, y_hi = st + 2 * kXTile, y_lo = y_hi + kYTile;
 #pragma unroll
         for (int k = 0; k < kBK / 8; ++k) {
-          const uint32_t off = k * 1024;     // 8 K rows = one swizzle group inside every column block
+          const uint32_t off = k * 1024;     // 8 K rows = two swizzle groups inside every column block
           umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_hi + off), idesc, (s | k) != 0);
           umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_lo + off), idesc, 1);
           umma_tf32(tmem_acc, smem_desc_mn_sw128(x_lo + off), smem_desc_mn_sw128(y_hi + off), idesc, 1);
@@ -560,7 +562,7 @@ int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int
     const uint64_t strides[3] = {time_major ? row * (uint64_t)batch : row, 128,
                                  time_major ? row : row * (uint64_t)length};
     const uint32_t box[4] = {32, (uint32_t)layer::kBK, tile / 32, 1};
-    return make_tensor_map_4d_f32_sw128(tm, base, dims, strides, box);
+    return make_tensor_map_4d_f32_sw128(tm, base, dims, strides, box, true);
   };
   CUtensorMap tx, ty;
   if (!make(&tx, X, M, x_time_major != 0, layer::kBM) || !make(&ty, Y, N, y_time_major != 0, (uint32_t)BN)) {

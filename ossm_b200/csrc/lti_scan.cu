@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(128) lti_forward_kernel(const __grid_constant_
 #pragma unroll
       for (int r = 0; r < kBatch; ++r) {
         const long long t = t0 + r;
-        fwd_step<V>(c, s0, s1, cur[r]);
+        if (t < p.L) fwd_step<V>(c, s0, s1, cur[r]);     // the state after the last real step leaves through seg_end
         if (valid && t < p.L) {
           const long long off = t * p.N;
           if constexpr (kOut & 1) xp[off] = s1;

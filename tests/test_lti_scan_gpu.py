@@ -340,10 +340,12 @@ def test_full_size_adjoint_and_linearity(K):
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("variant", ["imex1", "im", "linoss_imex"])
 @pytest.mark.parametrize("cuts", [(37,), (32, 64), (1, 50, 99)], ids=lambda c: "-".join(map(str, c)))
-def test_time_slices_match_oracle(K, variant, cuts):
+@pytest.mark.parametrize("P", [35, 36], ids=["plain_loads", "tma"])
+def test_time_slices_match_oracle(K, variant, cuts, P):
     """A sequence scanned slice by slice (forward first to last, backward last to first, state and adjoint
-    handed over) gives the oracle's answer; cuts inside and on chunk boundaries, odd series count included."""
-    L, B, P = 100, 3, 35
+    handed over) gives the oracle's answer; cuts inside and on chunk boundaries, odd (plain-load kernels) and
+    even (TMA-staged kernels) series counts."""
+    L, B = 100, 3
     a, g, st, bu, gx = make_case(L, B, P, seed=sum(cuts))
     ref, da, dg, ds, dbu = oracle(variant, a, g, st, bu, gx)
     gv = None if variant.startswith("linoss") else dev(g)
