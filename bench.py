@@ -65,7 +65,7 @@ def parse_args():
     ap.add_argument("--no-config4", action="store_true", help="skip the sharded long-sequence configuration")
     ap.add_argument("--config4-length", type=int, default=131072)
     ap.add_argument("--workload", default="dlinoss",
-                    choices=["dlinoss", "linoss", "lru", "mamba", "sdlinoss", "generic", "layer", "shard", "sharded_layer"],
+                    choices=["dlinoss", "linoss", "lru", "mamba", "sdlinoss", "generic", "layer", "shard", "conv", "sharded_layer"],
                     help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
                          "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
                          "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
@@ -267,8 +267,9 @@ def hbm_peak():
 
 
 def time_pair(fwd, bwd, steps, warmup):
-    """Mean device times (ms) of ``saved = fwd()`` and ``bwd(saved)`` and of the whole step, CUDA events on the
-    current stream, after ``warmup`` untimed steps."""
+    """Median device times (ms) over ``steps`` steps of ``saved = fwd()``, of ``bwd(saved)`` and of the whole step,
+    CUDA events on the current stream, after ``warmup`` untimed steps (the median keeps one stalled step -- an
+    allocator refill, another tenant of the host -- out of the figure)."""
     import torch
 
     for _ in range(max(warmup, 3)):
@@ -282,9 +283,9 @@ def time_pair(fwd, bwd, steps, warmup):
         bwd(saved)
         e[2].record()
     torch.cuda.synchronize()
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
-    return fwd_ms, bwd_ms, evs[0][0].elapsed_time(evs[-1][2]) / steps
+    fwd_ms = statistics.median(e[0].elapsed_time(e[1]) for e in evs)
+    bwd_ms = statistics.median(e[1].elapsed_time(e[2]) for e in evs)
+    return fwd_ms, bwd_ms, statistics.median(e[0].elapsed_time(e[2]) for e in evs)
 
 
 def side_workload(name, args, dev):
@@ -358,6 +359,30 @@ def side_workload(name, args, dev):
                 L * B * P, 28, 48,
                 f"selective D-LinOSS imex1 scan fwd+bwd, B={B} L={L} M={P}, dense per-step coefficients, complex64",
                 "sdlinoss_scan_fwd_bwd_gelem_per_s")
+    if name == "conv":
+        # causal conv1d + SiLU of the Mamba mixer at the selective-scan benchmark shape, on the x half of in_proj's output
+        from ossm_b200.mixer import _ConvSiluFn
+
+        Bz, Dn, L = (args.side_batch or 32), 2048, (args.side_length or 8192)
+        xz = torch.randn(Bz, L, 2 * Dn, generator=gen, device=dev)
+        w = torch.randn(Dn, 1, 4, generator=gen, device=dev) * 0.5
+        bias = torch.randn(Dn, generator=gen, device=dev) * 0.3
+        g1 = torch.randn(Bz, Dn, L, generator=gen, device=dev)
+        g2 = torch.randn(Bz, L, Dn, generator=gen, device=dev)
+        x = xz[..., :Dn].requires_grad_(True)
+        wl, bl = w.requires_grad_(True), bias.requires_grad_(True)
+
+        def cfwd():
+            x.grad = wl.grad = bl.grad = None
+            return _ConvSiluFn.apply(x, wl, bl)
+
+        def cbwd(outs):
+            torch.autograd.backward(outs, (g1, g2))
+
+        # forward: read x 4, write both layouts 8; backward: read x 4 + two gradients 8, write grad_x 4
+        return (cfwd, cbwd, Bz * Dn * L, 12, 16,
+                f"causal conv1d(k=4) + bias + SiLU fwd+bwd, B={Bz} D={Dn} L={L}, float32, both output layouts",
+                "conv1d_silu_fwd_bwd_gelem_per_s")
     if name == "mamba":
         Bz, Dn, L, N = (args.side_batch or 32), 2048, (args.side_length or 8192), 16
         io = torch.bfloat16
@@ -876,7 +901,7 @@ def run_ours(args):
     side = None
     if world == 1 and not args.no_side:
         side = {}
-        for name, n_steps in (("linoss", 30), ("mamba", 5), ("sdlinoss", 30), ("lru", 30), ("generic", 20), ("shard", 20)):
+        for name, n_steps in (("linoss", 30), ("mamba", 5), ("sdlinoss", 30), ("lru", 30), ("generic", 20), ("shard", 20), ("conv", 10)):
             try:
                 side[name] = run_side(name, args, dev, n_steps, 3)
             except Exception as exc:       # a side workload must not take the headline down

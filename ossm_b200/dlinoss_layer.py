@@ -41,8 +41,8 @@ def pack_output_weights(C: Tensor) -> Tensor:
     """``[H, P, 2] -> [H, 2P]`` with columns ``(C_re[:,p], -C_im[:,p])`` interleaved, so that the product
     with the interleaved (re, im) pairs of ``x`` is ``Re(C x)``."""
     H, P, _ = C.shape
-    sign = torch.tensor([1.0, -1.0], dtype=C.dtype, device=C.device)
-    return (C * sign).reshape(H, 2 * P).contiguous()
+    # no host constant: a tensor made from a Python list would cost a blocking host-to-device copy per call
+    return torch.stack((C[..., 0], -C[..., 1]), dim=-1).reshape(H, 2 * P)
 
 
 def weight_gradient(X: Tensor, x_time_major: bool, Y: Tensor, y_time_major: bool, batch: int, length: int) -> Tensor:
@@ -105,8 +105,8 @@ class DLinossLayerFn(torch.autograd.Function):
         grad_w_out = weight_gradient(gy, False, x2.view(length * batch, 2 * ssm), True, batch, length)      # [H, 2P]
         grad_D = (gy * u2).sum(0)
         grad_B = grad_w_in.view(ssm, 2, hidden).permute(0, 2, 1).contiguous()
-        sign = torch.tensor([1.0, -1.0], dtype=grad_w_out.dtype, device=dev)
-        grad_C = grad_w_out.view(hidden, ssm, 2) * sign
+        g3 = grad_w_out.view(hidden, ssm, 2)
+        grad_C = torch.stack((g3[..., 0], -g3[..., 1]), dim=-1)
         return None, grad_a, grad_g, grad_step, grad_B, grad_C, grad_D, grad_u
 
 
