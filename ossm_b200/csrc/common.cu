@@ -80,6 +80,13 @@ bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t c
                    CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+bool make_tensor_map_2d_f32_sw64(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+  if (box_cols * 4 != 64) return false;
+  return encode_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, pitch_bytes, box_cols, box_rows,
+                   CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
 bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
                                   const uint64_t strides_bytes[3], const uint32_t box[4], bool atom32) {
   EncodeTiledFn fn = encode_fn();

@@ -68,6 +68,9 @@ bool make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t cols, u
 // matrix descriptors of the projection kernels expect.
 bool make_tensor_map_2d_f32_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                                   uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+// Same with the 64-byte swizzle (box_cols * 4 must be 64).
+bool make_tensor_map_2d_f32_sw64(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
 // Rank-4 float32 map with a 128-byte swizzle span.  dims / box are innermost first; strides_bytes are the byte
 // strides of dimensions 1..3 (dimension 0 is dense).  box[0] * 4 must be 128.  atom32 selects the variant
 // that swizzles 32-byte chunks (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), the only layout the tensor cores

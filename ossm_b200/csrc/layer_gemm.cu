@@ -19,10 +19,10 @@
 // lo*lo term is below 2^-22 relative).  The weights are split once by split_tf32_kernel; the
 // activations are split inside the GEMM by four "splitter" warps between the TMA load and the MMA.
 //
-// Kernel structure (one CTA = one 128 x BN output tile, K walked in slices of 32 floats = 128 B):
-//   warp 0       producer: one lane issues the TMA loads (SWIZZLE_128B) of A, W_hi, W_lo per slice
-//   warp 1       allocates the accumulator in tensor memory; one lane issues 12 tcgen05.mma per slice
-//                (4 K-steps of 8 x 3 operand combinations) and commits the stage back to the producer
+// Kernel structure (one CTA = one 128 x BN output tile, K walked in slices of 16 floats = 64 B, ring of 4 stages):
+//   warp 0       producer: one lane issues the TMA loads (SWIZZLE_64B) of A, W_hi, W_lo per slice
+//   warp 1       allocates the accumulator in tensor memory; one lane issues 6 tcgen05.mma per slice
+//                (2 K-steps of 8 x 3 operand combinations) and commits the stage back to the producer
 //   warps 2..5   splitters: rewrite the A slice in place as hi and write lo beside it; afterwards the
 //                epilogue: tcgen05.ld the accumulator (lane = output row), add diag*aux, store
 // Stages are handed over with mbarriers; every wait is bounded in time and a wait that gives up sets
@@ -37,9 +37,12 @@ OSSM_B200_STATUS_ACCESSOR(status_layer)
 namespace layer {
 
 constexpr int kBM = 128;            // output rows per CTA = TMEM lanes
-constexpr int kBK = 32;             // floats per K slice = one 128-byte swizzle row
+constexpr int kBK = 32;             // weight-gradient kernel: K rows per slice (operand rows are 128-byte swizzle rows)
+constexpr int kPK = 16;             // projection kernel: floats per K slice = one 64-byte swizzle row; the smaller
+                                    // slice buys a four-deep ring (TMA -> split -> MMA needs the depth, the MMAs of
+                                    // one slice take less time than its load and split)
 constexpr int kThreads = 192;       // producer warp, MMA warp, four splitter / epilogue warps
-constexpr int kATile = kBM * kBK * 4;   // 16 KiB
+constexpr int kATile = kBM * kPK * 4;   // 8 KiB
 
 enum RowMap : int { kRowIdentity = 0, kRowBatchToTime = 1, kRowTimeToBatch = 2 };
 
@@ -113,18 +116,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
-// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): groups of 8 rows are 1024 B
-// apart (stride byte offset), the leading byte offset is unused for this layout (1), descriptor
-// version 1 (sm_100), layout type 2 = SWIZZLE_128B.  `addr` must lie in a 1024-byte aligned tile;
-// advancing it by 32 B selects the next K step of 8 TF32 values inside the swizzle row.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+// Shared-memory matrix descriptor of a K-major tile whose rows are 64 bytes (16 floats), stored with the
+// 64-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_64B): groups of 8 rows are 512 B apart
+// (stride byte offset), the leading byte offset is unused for this layout (1), descriptor version 1
+// (sm_100), layout type 4 = SWIZZLE_64B.  `addr` must lie in a 512-byte aligned tile; advancing it by
+// 32 B selects the next K step of 8 TF32 values inside the swizzle row.
+__device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t addr) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address, bits [0,14)
   d |= (uint64_t)1 << 16;                           // leading byte offset (16-byte units), bits [16,30)
-  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits [32,46)
+  d |= (uint64_t)(512 >> 4) << 32;                  // stride byte offset, bits [32,46)
   d |= (uint64_t)1 << 46;                           // descriptor version, bits [46,48)
-  d |= (uint64_t)2 << 61;                           // layout type, bits [61,64)
+  d |= (uint64_t)4 << 61;                           // layout type, bits [61,64)
   return d;
 }
 
@@ -134,15 +137,15 @@ __host__ __device__ constexpr uint32_t instr_desc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// Shared memory: [0,1024) barriers + TMEM address | stages x (A_hi 16K | A_lo 16K | W_hi BN*128 | W_lo BN*128)
+// Shared memory: [0,1024) barriers + TMEM address | stages x (A_hi 8K | A_lo 8K | W_hi BN*64 | W_lo BN*64)
 template <int BN>
 struct Smem {
-  static constexpr int kWTile = BN * kBK * 4;
+  static constexpr int kWTile = BN * kPK * 4;
   static constexpr int kStage = 2 * kATile + 2 * kWTile;
   static constexpr size_t bytes(int stages) { return 1024 + (size_t)stages * kStage + 1024; }   // + alignment slack
 };
 
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 6;
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -161,7 +164,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long m0 = (long long)blockIdx.x * kBM;
   const long long n0 = (long long)blockIdx.y * BN;
-  const int nslices = (int)((p.K + kBK - 1) / kBK);
+  const int nslices = (int)((p.K + kPK - 1) / kPK);
   const int stages = p.stages;
 
   if (threadIdx.x == 0) {
@@ -190,9 +193,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         if (s >= stages && !mbar_wait(&empty[b], ((s / stages) - 1) & 1, kWaitLimitNs, kStatusMmaTimeout)) break;
         unsigned char* st = stage0 + (size_t)b * S::kStage;
         mbar_expect_tx(&full[b], kATile + 2 * S::kWTile);
-        tma_load_2d(st, &tm_a, &full[b], s * kBK, (int32_t)m0);
-        tma_load_2d(st + 2 * kATile, &tm_whi, &full[b], s * kBK, (int32_t)n0);
-        tma_load_2d(st + 2 * kATile + S::kWTile, &tm_wlo, &full[b], s * kBK, (int32_t)n0);
+        tma_load_2d(st, &tm_a, &full[b], s * kPK, (int32_t)m0);
+        tma_load_2d(st + 2 * kATile, &tm_whi, &full[b], s * kPK, (int32_t)n0);
+        tma_load_2d(st + 2 * kATile + S::kWTile, &tm_wlo, &full[b], s * kPK, (int32_t)n0);
       }
     }
   } else if (warp == 1) {
@@ -208,11 +211,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         const uint32_t st = smem_u32(stage0 + (size_t)b * S::kStage);
         const uint32_t a_hi = st, a_lo = st + kATile, w_hi = st + 2 * kATile, w_lo = w_hi + S::kWTile;
 #pragma unroll
-        for (int k = 0; k < kBK / 8; ++k) {
+        for (int k = 0; k < kPK / 8; ++k) {
           const uint32_t off = k * 32;     // 8 TF32 values = 32 bytes along the swizzle row
-          umma_tf32(tmem_acc, smem_desc_sw128(a_hi + off), smem_desc_sw128(w_hi + off), idesc, (s | k) != 0);
-          umma_tf32(tmem_acc, smem_desc_sw128(a_hi + off), smem_desc_sw128(w_lo + off), idesc, 1);
-          umma_tf32(tmem_acc, smem_desc_sw128(a_lo + off), smem_desc_sw128(w_hi + off), idesc, 1);
+          umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_hi + off), idesc, (s | k) != 0);
+          umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_lo + off), idesc, 1);
+          umma_tf32(tmem_acc, smem_desc_k_sw64(a_lo + off), smem_desc_k_sw64(w_hi + off), idesc, 1);
         }
         umma_commit(&empty[b]);            // the stage may be refilled once these MMAs have read it
       }
@@ -229,7 +232,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       float4* hi = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage);
       float4* lo = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage + kATile);
 #pragma unroll
-      for (int i = 0; i < kATile / 16 / 128; ++i) {
+      for (int i = 0; i < kATile / 16 / 128; ++i) {     // 4 vectors of 16 bytes per thread
         const float4 v = hi[i * 128 + t];
         float4 h, l;
         h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
@@ -487,9 +490,11 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUtensorMap& tl, GemmParams p,
                        cudaStream_t stream) {
   using S = Smem<BN>;
+  // two CTAs per SM (each with its own accumulator, 2 x BN <= 512 tensor-memory columns): the epilogue of one
+  // overlaps the K loop of the other, which matters because K is only 256..512 here
   int stages = kMaxStages;
-  while (stages > 1 && S::bytes(stages) > 220 * 1024) --stages;
-  const int nslices = (int)((p.K + kBK - 1) / kBK);
+  while (stages > 1 && S::bytes(stages) > 110 * 1024) --stages;
+  const int nslices = (int)((p.K + kPK - 1) / kPK);
   if (stages > nslices) stages = nslices;
   p.stages = stages;
   const size_t smem = S::bytes(stages);
@@ -598,9 +603,9 @@ int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, 
   if (M > 0x7fffffffLL - layer::kBM || N > 0x7fffffffLL - 256) { set_last_error("gemm_tf32x3: extent too large"); return kErrInvalidArgument; }
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
   CUtensorMap ta, th, tl;
-  if (!make_tensor_map_2d_f32_sw128(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K * 4, layer::kBK, layer::kBM) ||
-      !make_tensor_map_2d_f32_sw128(&th, W_hi, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kBK, BN) ||
-      !make_tensor_map_2d_f32_sw128(&tl, W_lo, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kBK, BN)) {
+  if (!make_tensor_map_2d_f32_sw64(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K * 4, layer::kPK, layer::kBM) ||
+      !make_tensor_map_2d_f32_sw64(&th, W_hi, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kPK, BN) ||
+      !make_tensor_map_2d_f32_sw64(&tl, W_lo, (uint64_t)K, (uint64_t)N, (uint64_t)K * 4, layer::kPK, BN)) {
     set_last_error("gemm_tf32x3: operands must be 16-byte aligned, dense row-major matrices");
     return kErrUnsupported;
   }

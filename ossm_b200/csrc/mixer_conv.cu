@@ -25,8 +25,6 @@ constexpr int kTileD = 32;      // channels per CTA
 constexpr int kMaxTaps = 4;     // kernel sizes 1..4 (Mamba's d_conv default is 4)
 constexpr int kRowsY = 8;       // threadIdx.y extent
 
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
-
 struct ConvParams {
   const float* x;        // [B, L, D] with row pitch ldx floats
   const float* w;        // [D, K]
@@ -43,111 +41,385 @@ struct ConvParams {
   int taps;
 };
 
+// Scalar kernels: any shape and alignment (odd channel counts, sequence lengths that are not multiples of 4).
+// K = number of taps (compile time: the tap loops unroll and the halo is a constant).  Index arithmetic is kept in
+// 32 bits inside a tile and in running pointers across rows; they are bound by instruction issue, not by HBM,
+// which is why aligned shapes take the vector kernels below.
+template <int K>
 __global__ void __launch_bounds__(kTileD * kRowsY) conv_silu_forward_kernel(ConvParams p) {
-  __shared__ float xin[kTileT + kMaxTaps - 1][kTileD + 1];
+  constexpr int halo = K - 1;
+  __shared__ float xin[kTileT + halo][kTileD + 1];
   __shared__ float yout[kTileT][kTileD + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const long long b = blockIdx.z;
-  const long long d0 = (long long)blockIdx.y * kTileD, t0 = (long long)blockIdx.x * kTileT;
-  const int halo = p.taps - 1;
-  const long long d = d0 + tx;
-  const float* xb = p.x + b * p.L * p.ldx;
-  for (int r = ty; r < kTileT + halo; r += kRowsY) {
-    const long long t = t0 - halo + r;
-    xin[r][tx] = (d < p.D && t >= 0 && t < p.L) ? __ldg(xb + t * p.ldx + d) : 0.0f;
+  const int d0 = blockIdx.y * kTileD;
+  const long long t0 = (long long)blockIdx.x * kTileT;
+  const int d = d0 + tx;
+  const bool dok = d < (int)p.D;
+  const int rows_left = (int)((p.L - t0) < (kTileT) ? (p.L - t0) : kTileT);      // real time steps in this tile
+  {
+    const float* src = p.x + (b * p.L + t0 - halo + ty) * p.ldx + d;
+    const long long step = (long long)kRowsY * p.ldx;
+#pragma unroll
+    for (int r = ty; r < kTileT + halo; r += kRowsY, src += step) {
+      const bool ok = dok && (t0 + r >= halo) && (r - halo < rows_left);
+      xin[r][tx] = ok ? __ldg(src) : 0.0f;
+    }
   }
-  float w[kMaxTaps];
+  float w[K];
 #pragma unroll
-  for (int k = 0; k < kMaxTaps; ++k) w[k] = (k < p.taps && d < p.D) ? __ldg(p.w + d * p.taps + k) : 0.0f;
-  const float bias = (p.bias && d < p.D) ? __ldg(p.bias + d) : 0.0f;
+  for (int k = 0; k < K; ++k) w[k] = dok ? __ldg(p.w + d * K + k) : 0.0f;
+  const float bias = (p.bias && dok) ? __ldg(p.bias + d) : 0.0f;
   __syncthreads();
-  for (int r = ty; r < kTileT; r += kRowsY) {
-    float pre = bias;
+  {
+    float* dst = p.out_bld ? p.out_bld + (b * p.L + t0 + ty) * p.D + d : nullptr;
+    const long long step = (long long)kRowsY * p.D;
 #pragma unroll
-    for (int k = 0; k < kMaxTaps; ++k)
-      if (k < p.taps) pre = fmaf(w[k], xin[r + k][tx], pre);
-    const float y = pre * sigmoidf_(pre);
-    yout[r][tx] = y;
-    const long long t = t0 + r;
-    if (p.out_bld && d < p.D && t < p.L) p.out_bld[(b * p.L + t) * p.D + d] = y;
+    for (int r = ty; r < kTileT; r += kRowsY) {
+      float pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) pre = fmaf(w[k], xin[r + k][tx], pre);
+      const float y = __fdividef(pre, 1.0f + __expf(-pre));
+      yout[r][tx] = y;
+      if (dst) {
+        if (dok && r < rows_left) *dst = y;
+        dst += step;
+      }
+    }
   }
   if (p.out_bdl == nullptr) return;
   __syncthreads();
   // transposed store: consecutive threads write consecutive time steps of one channel
-  for (int i = ty * kTileD + tx; i < kTileT * kTileD; i += kTileD * kRowsY) {
+  const int lin = ty * kTileD + tx;
+#pragma unroll
+  for (int i = lin; i < kTileT * kTileD; i += kTileD * kRowsY) {
     const int dd = i / kTileT, tt = i % kTileT;
-    const long long dch = d0 + dd, t = t0 + tt;
-    if (dch < p.D && t < p.L) p.out_bdl[(b * p.D + dch) * p.L + t] = yout[tt][dd];
+    if (d0 + dd < (int)p.D && tt < rows_left) p.out_bdl[(b * p.D + d0 + dd) * p.L + t0 + tt] = yout[tt][dd];
   }
 }
 
+template <int K>
 __global__ void __launch_bounds__(kTileD * kRowsY) conv_silu_backward_kernel(ConvParams p) {
-  __shared__ float xin[kTileT + 2 * (kMaxTaps - 1)][kTileD + 1];    // x for t0-halo .. t0+T+halo
-  __shared__ float dpre[kTileT + kMaxTaps - 1][kTileD + 1];         // d(pre) for t0 .. t0+T+halo
-  __shared__ float red[kRowsY][kMaxTaps + 1][kTileD];
+  constexpr int halo = K - 1;
+  __shared__ float xin[kTileT + 2 * halo][kTileD + 1];     // x for t0-halo .. t0+T+halo
+  __shared__ float dpre[kTileT + halo][kTileD + 1];        // d(pre) for t0 .. t0+T+halo
+  __shared__ float red[kRowsY][K + 1][kTileD];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const long long b = blockIdx.z;
-  const long long d0 = (long long)blockIdx.y * kTileD, t0 = (long long)blockIdx.x * kTileT;
-  const int halo = p.taps - 1;
-  const long long d = d0 + tx;
-  const float* xb = p.x + b * p.L * p.ldx;
-  for (int r = ty; r < kTileT + 2 * halo; r += kRowsY) {
-    const long long t = t0 - halo + r;
-    xin[r][tx] = (d < p.D && t >= 0 && t < p.L) ? __ldg(xb + t * p.ldx + d) : 0.0f;
+  const int d0 = blockIdx.y * kTileD;
+  const long long t0 = (long long)blockIdx.x * kTileT;
+  const int d = d0 + tx;
+  const bool dok = d < (int)p.D;
+  const long long left = p.L - t0;                          // time steps from t0 to the end of the sequence
+  const int rows_ext = (int)(left < kTileT + halo ? left : kTileT + halo);    // real steps among tile + right halo
+  {
+    const float* src = p.x + (b * p.L + t0 - halo + ty) * p.ldx + d;
+    const long long step = (long long)kRowsY * p.ldx;
+#pragma unroll
+    for (int r = ty; r < kTileT + 2 * halo; r += kRowsY, src += step) {
+      const bool ok = dok && (t0 + r >= halo) && (r - halo < left);
+      xin[r][tx] = ok ? __ldg(src) : 0.0f;
+    }
   }
   // upstream gradient of the time-contiguous output, transposed through dpre as staging
   if (p.g_bdl) {
-    for (int i = ty * kTileD + tx; i < (kTileT + halo) * kTileD; i += kTileD * kRowsY) {
+    const int lin = ty * kTileD + tx;
+    for (int i = lin; i < (kTileT + halo) * kTileD; i += kTileD * kRowsY) {
       const int dd = i / (kTileT + halo), tt = i % (kTileT + halo);
-      const long long dch = d0 + dd, t = t0 + tt;
-      dpre[tt][dd] = (dch < p.D && t < p.L) ? __ldg(p.g_bdl + (b * p.D + dch) * p.L + t) : 0.0f;
+      dpre[tt][dd] = (d0 + dd < (int)p.D && tt < rows_ext) ? __ldg(p.g_bdl + (b * p.D + d0 + dd) * p.L + t0 + tt) : 0.0f;
     }
   }
-  float w[kMaxTaps];
+  float w[K];
 #pragma unroll
-  for (int k = 0; k < kMaxTaps; ++k) w[k] = (k < p.taps && d < p.D) ? __ldg(p.w + d * p.taps + k) : 0.0f;
-  const float bias = (p.bias && d < p.D) ? __ldg(p.bias + d) : 0.0f;
+  for (int k = 0; k < K; ++k) w[k] = dok ? __ldg(p.w + d * K + k) : 0.0f;
+  const float bias = (p.bias && dok) ? __ldg(p.bias + d) : 0.0f;
   __syncthreads();
-  float acc_w[kMaxTaps] = {0.f, 0.f, 0.f, 0.f}, acc_b = 0.f;
-  for (int r = ty; r < kTileT + halo; r += kRowsY) {
-    const long long t = t0 + r;
-    float g = p.g_bdl ? dpre[r][tx] : 0.0f;
-    if (p.g_bld && d < p.D && t < p.L) g += __ldg(p.g_bld + (b * p.L + t) * p.D + d);
-    float pre = bias;
+  float acc_w[K], acc_b = 0.f;
 #pragma unroll
-    for (int k = 0; k < kMaxTaps; ++k)
-      if (k < p.taps) pre = fmaf(w[k], xin[r + k][tx], pre);     // x index of output t = t0 + r is r + k (offset halo cancels)
-    const float sg = sigmoidf_(pre);
-    const float dp = (t < p.L) ? g * (sg * (1.0f + pre * (1.0f - sg))) : 0.0f;
-    dpre[r][tx] = dp;
-    if (r < kTileT) {       // the halo rows belong to the next tile's sums
-      acc_b += dp;
+  for (int k = 0; k < K; ++k) acc_w[k] = 0.f;
+  {
+    const float* g2 = p.g_bld ? p.g_bld + (b * p.L + t0 + ty) * p.D + d : nullptr;
+    const long long step = (long long)kRowsY * p.D;
 #pragma unroll
-      for (int k = 0; k < kMaxTaps; ++k)
-        if (k < p.taps) acc_w[k] = fmaf(dp, xin[r + k][tx], acc_w[k]);
+    for (int r = ty; r < kTileT + halo; r += kRowsY) {
+      const bool live = dok && r < rows_ext;
+      float g = p.g_bdl ? dpre[r][tx] : 0.0f;
+      if (g2) {
+        if (live) g += __ldg(g2);
+        g2 += step;
+      }
+      float pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) pre = fmaf(w[k], xin[r + k][tx], pre);   // x index of output t0 + r is r + k
+      const float sg = __fdividef(1.0f, 1.0f + __expf(-pre));
+      const float dp = live ? g * (sg * fmaf(pre, 1.0f - sg, 1.0f)) : 0.0f;
+      dpre[r][tx] = dp;
+      if (r < kTileT) {       // the halo rows belong to the next tile's sums
+        acc_b += dp;
+#pragma unroll
+        for (int k = 0; k < K; ++k) acc_w[k] = fmaf(dp, xin[r + k][tx], acc_w[k]);
+      }
     }
   }
   __syncthreads();
-  // grad_x[t] = sum_k w[k] * dpre[t + halo - k]
-  for (int r = ty; r < kTileT; r += kRowsY) {
-    const long long t = t0 + r;
-    float gx = 0.0f;
+  {
+    // grad_x[t] = sum_k w[k] * dpre[t + halo - k]
+    float* dst = p.grad_x + (b * p.L + t0 + ty) * p.D + d;
+    const long long step = (long long)kRowsY * p.D;
 #pragma unroll
-    for (int k = 0; k < kMaxTaps; ++k)
-      if (k < p.taps) gx = fmaf(w[k], dpre[r + halo - k][tx], gx);
-    if (d < p.D && t < p.L) p.grad_x[(b * p.L + t) * p.D + d] = gx;
+    for (int r = ty; r < kTileT; r += kRowsY, dst += step) {
+      float gx = 0.0f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) gx = fmaf(w[k], dpre[r + halo - k][tx], gx);
+      if (dok && r < left) *dst = gx;
+    }
   }
 #pragma unroll
-  for (int k = 0; k < kMaxTaps; ++k) red[ty][k][tx] = acc_w[k];
-  red[ty][kMaxTaps][tx] = acc_b;
+  for (int k = 0; k < K; ++k) red[ty][k][tx] = acc_w[k];
+  red[ty][K][tx] = acc_b;
   __syncthreads();
-  if (ty == 0 && d < p.D) {
-    for (int k = 0; k <= kMaxTaps; ++k) {
+  if (ty == 0 && dok) {
+#pragma unroll
+    for (int k = 0; k <= K; ++k) {
       float s = 0.0f;
+#pragma unroll
       for (int j = 0; j < kRowsY; ++j) s += red[j][k][tx];
-      if (k < p.taps) atomicAdd(p.grad_w + d * p.taps + k, s);
-      else if (k == kMaxTaps && p.grad_bias) atomicAdd(p.grad_bias + d, s);
+      if (k < K) atomicAdd(p.grad_w + d * K + k, s);
+      else if (p.grad_bias) atomicAdd(p.grad_bias + d, s);
     }
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Vector kernels: the path of every shape the mixer produces (even channel count and pitch, 8-byte aligned
+// rows; sequence length a multiple of 4 where the time-contiguous layout is read or written).  A thread owns
+// two channel pairs (float2 at channels 2*lane and 64 + 2*lane of a 128-channel block) and walks 16 time
+// steps with the taps in registers, so a warp's global accesses are 256 contiguous bytes and the per-element
+// index arithmetic of the scalar kernels is shared by 64 elements.  Shared memory is used for the transpose
+// only: rows of 130 floats make both the float2 row writes and the 4-times-by-8-channels transposed reads
+// conflict-free ((2*(4*tq + i) + c8) mod 32 is a bijection of (tq, c8)), and the time-contiguous layout moves
+// as float4, four lanes per 64-byte run of one channel.
+constexpr int kVT = 64;          // time steps per tile
+constexpr int kVD = 128;         // channels per CTA
+constexpr int kVWarps = 4;
+constexpr int kVSteps = kVT / kVWarps;
+constexpr int kVPitch = 130;
+
+__device__ __forceinline__ float2 ldg2(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+
+template <int K>
+__global__ void __launch_bounds__(32 * kVWarps) conv_silu_forward_vec_kernel(ConvParams p) {
+  constexpr int halo = K - 1;
+  __shared__ __align__(16) float tile[kVT][kVPitch];
+  const int lane = threadIdx.x, w = threadIdx.y;
+  const long long b = blockIdx.z;
+  const int d0 = blockIdx.y * kVD;
+  const long long t0 = (long long)blockIdx.x * kVT;
+  const long long ts = t0 + w * kVSteps;
+  const int D = (int)p.D;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int c = 64 * h + 2 * lane;
+    const bool ok = d0 + c < D;
+    float2 wt[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      wt[k] = ok ? make_float2(__ldg(p.w + (d0 + c) * K + k), __ldg(p.w + (d0 + c + 1) * K + k)) : make_float2(0.f, 0.f);
+    const float2 bias = (ok && p.bias) ? ldg2(p.bias + d0 + c) : make_float2(0.f, 0.f);
+    float2 xv[kVSteps + halo];
+    {
+      const float* src = p.x + (b * p.L + ts - halo) * p.ldx + d0 + c;
+#pragma unroll
+      for (int j = 0; j < kVSteps + halo; ++j, src += p.ldx) {
+        const long long t = ts - halo + j;
+        xv[j] = (ok && t >= 0 && t < p.L) ? ldg2(src) : make_float2(0.f, 0.f);
+      }
+    }
+    float* dst = p.out_bld ? p.out_bld + (b * p.L + ts) * p.D + d0 + c : nullptr;
+#pragma unroll
+    for (int i = 0; i < kVSteps; ++i) {
+      float2 pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        pre.x = fmaf(wt[k].x, xv[i + k].x, pre.x);
+        pre.y = fmaf(wt[k].y, xv[i + k].y, pre.y);
+      }
+      float2 y;
+      y.x = __fdividef(pre.x, 1.0f + __expf(-pre.x));
+      y.y = __fdividef(pre.y, 1.0f + __expf(-pre.y));
+      *reinterpret_cast<float2*>(&tile[w * kVSteps + i][c]) = y;
+      if (dst) {
+        if (ok && ts + i < p.L) *reinterpret_cast<float2*>(dst) = y;
+        dst += p.D;
+      }
+    }
+  }
+  if (p.out_bdl == nullptr) return;
+  __syncthreads();
+  const int tq = lane & 3, c8 = lane >> 2;
+#pragma unroll 4
+  for (int it = w; it < (kVD / 8) * (kVT / 16); it += kVWarps) {
+    const int cc = (it >> 2) * 8 + c8, tt = (it & 3) * 16 + tq * 4;
+    const float4 v = make_float4(tile[tt][cc], tile[tt + 1][cc], tile[tt + 2][cc], tile[tt + 3][cc]);
+    if (d0 + cc < D && t0 + tt < p.L)
+      *reinterpret_cast<float4*>(p.out_bdl + (b * p.D + d0 + cc) * p.L + t0 + tt) = v;
+  }
+}
+
+// One CTA walks `tiles_per_cta` consecutive time tiles of one (batch entry, block of 64 channels: one float2 per
+// thread, which keeps the kernel near 128 registers) and keeps the weight and bias sums in registers across them:
+// one shared-memory reduction and one atomic add per (channel, tap) at the end.
+constexpr int kVDB = 64;
+constexpr int kVPitchB = kVDB + 2;
+template <int K>
+__global__ void __launch_bounds__(32 * kVWarps) conv_silu_backward_vec_kernel(ConvParams p, int tiles_per_cta) {
+  constexpr int halo = K - 1;
+  constexpr int kRows = kVT + halo;
+  static_assert(kRows * kVPitchB >= kVWarps * (K + 1) * kVDB, "reduction reuses the tile");
+  __shared__ __align__(16) float tile[kRows][kVPitchB];     // upstream gradient of the time-contiguous output
+  const int lane = threadIdx.x, w = threadIdx.y;
+  const long long b = blockIdx.z;
+  const int d0 = blockIdx.y * kVDB;
+  const int D = (int)p.D;
+  const int tq = lane & 3, c8 = lane >> 2;
+  const int c = 2 * lane;
+  const bool ok = d0 + c < D;
+  float2 wt[K], accw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    wt[k] = ok ? make_float2(__ldg(p.w + (d0 + c) * K + k), __ldg(p.w + (d0 + c + 1) * K + k)) : make_float2(0.f, 0.f);
+    accw[k] = make_float2(0.f, 0.f);
+  }
+  const float2 bias = (ok && p.bias) ? ldg2(p.bias + d0 + c) : make_float2(0.f, 0.f);
+  float2 accb = make_float2(0.f, 0.f);
+  for (int ti = 0; ti < tiles_per_cta; ++ti) {
+    const long long t0 = ((long long)blockIdx.x * tiles_per_cta + ti) * kVT;
+    if (t0 >= p.L) break;
+    if (p.g_bdl) {
+      if (ti) __syncthreads();        // the previous tile has been consumed
+#pragma unroll 4
+      for (int it = w; it < (kVDB / 8) * (kVT / 16); it += kVWarps) {
+        const int cc = (it >> 2) * 8 + c8, tt = (it & 3) * 16 + tq * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d0 + cc < D && t0 + tt < p.L)
+          v = __ldg(reinterpret_cast<const float4*>(p.g_bdl + (b * p.D + d0 + cc) * p.L + t0 + tt));
+        tile[tt][cc] = v.x; tile[tt + 1][cc] = v.y; tile[tt + 2][cc] = v.z; tile[tt + 3][cc] = v.w;
+      }
+      for (int i = w * 32 + lane; i < halo * kVDB; i += 32 * kVWarps) {     // the K-1 steps after the tile
+        const int r = kVT + i / kVDB, cc = i % kVDB;
+        tile[r][cc] = (d0 + cc < D && t0 + r < p.L) ? __ldg(p.g_bdl + (b * p.D + d0 + cc) * p.L + t0 + r) : 0.0f;
+      }
+      __syncthreads();
+    }
+    const long long ts = t0 + w * kVSteps;
+    float2 xv[kVSteps + 2 * halo];
+    {
+      const float* src = p.x + (b * p.L + ts - halo) * p.ldx + d0 + c;
+#pragma unroll
+      for (int j = 0; j < kVSteps + 2 * halo; ++j, src += p.ldx) {
+        const long long t = ts - halo + j;
+        xv[j] = (ok && t >= 0 && t < p.L) ? ldg2(src) : make_float2(0.f, 0.f);
+      }
+    }
+    float2 gv[kVSteps + halo];
+    {
+      const float* src = p.g_bld ? p.g_bld + (b * p.L + ts) * p.D + d0 + c : nullptr;
+#pragma unroll
+      for (int j = 0; j < kVSteps + halo; ++j)
+        gv[j] = (src && ok && ts + j < p.L) ? ldg2(src + (long long)j * p.D) : make_float2(0.f, 0.f);
+    }
+    float2 dp[kVSteps + halo];
+    float* dst = p.grad_x + (b * p.L + ts) * p.D + d0 + c;
+#pragma unroll
+    for (int j = 0; j < kVSteps + halo; ++j) {
+      float2 g = gv[j];
+      if (p.g_bdl) {
+        const float2 s = *reinterpret_cast<const float2*>(&tile[w * kVSteps + j][c]);
+        g.x += s.x; g.y += s.y;
+      }
+      float2 pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        pre.x = fmaf(wt[k].x, xv[j + k].x, pre.x);
+        pre.y = fmaf(wt[k].y, xv[j + k].y, pre.y);
+      }
+      const float sx = __fdividef(1.0f, 1.0f + __expf(-pre.x)), sy = __fdividef(1.0f, 1.0f + __expf(-pre.y));
+      const bool live = ok && ts + j < p.L;
+      dp[j].x = live ? g.x * (sx * fmaf(pre.x, 1.0f - sx, 1.0f)) : 0.0f;
+      dp[j].y = live ? g.y * (sy * fmaf(pre.y, 1.0f - sy, 1.0f)) : 0.0f;
+      if (j < kVSteps) {          // the steps after the warp's own belong to the next warp's sums
+        accb.x += dp[j].x; accb.y += dp[j].y;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          accw[k].x = fmaf(dp[j].x, xv[j + k].x, accw[k].x);
+          accw[k].y = fmaf(dp[j].y, xv[j + k].y, accw[k].y);
+        }
+      }
+      if (j >= halo) {            // grad_x[ts + j - halo] = sum_k w[k] * dpre[ts + j - k]
+        float2 gx = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          gx.x = fmaf(wt[k].x, dp[j - k].x, gx.x);
+          gx.y = fmaf(wt[k].y, dp[j - k].y, gx.y);
+        }
+        if (ok && ts + j - halo < p.L) *reinterpret_cast<float2*>(dst) = gx;
+        dst += p.D;
+      }
+    }
+  }
+  __syncthreads();
+  float* red = &tile[0][0];            // [warp][K + 1][kVDB]
+#pragma unroll
+  for (int k = 0; k < K; ++k) *reinterpret_cast<float2*>(red + (w * (K + 1) + k) * kVDB + c) = accw[k];
+  *reinterpret_cast<float2*>(red + (w * (K + 1) + K) * kVDB + c) = accb;
+  __syncthreads();
+  const int cr = w * 32 + lane;
+  if (cr < kVDB && d0 + cr < D) {
+#pragma unroll
+    for (int k = 0; k <= K; ++k) {
+      float s = 0.0f;
+#pragma unroll
+      for (int j = 0; j < kVWarps; ++j) s += red[(j * (K + 1) + k) * kVDB + cr];
+      if (k < K) atomicAdd(p.grad_w + (d0 + cr) * K + k, s);
+      else if (p.grad_bias) atomicAdd(p.grad_bias + d0 + cr, s);
+    }
+  }
+}
+
+static inline bool aligned(const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
+
+static bool forward_vec_ok(const ConvParams& p) {
+  return (p.D % 2 == 0) && (p.ldx % 2 == 0) && aligned(p.x, 8) && aligned(p.bias, 8) && aligned(p.out_bld, 8) &&
+         (!p.out_bdl || (p.L % 4 == 0 && aligned(p.out_bdl, 16)));
+}
+static bool backward_vec_ok(const ConvParams& p) {
+  return (p.D % 2 == 0) && (p.ldx % 2 == 0) && aligned(p.x, 8) && aligned(p.bias, 8) && aligned(p.g_bld, 8) &&
+         aligned(p.grad_x, 8) && (!p.g_bdl || (p.L % 4 == 0 && aligned(p.g_bdl, 16)));
+}
+
+template <int K>
+static void launch_forward(const ConvParams& p, cudaStream_t stream) {
+  if (forward_vec_ok(p)) {
+    dim3 grid((unsigned)((p.L + kVT - 1) / kVT), (unsigned)((p.D + kVD - 1) / kVD), (unsigned)p.B);
+    conv_silu_forward_vec_kernel<K><<<grid, dim3(32, kVWarps), 0, stream>>>(p);
+  } else {
+    dim3 grid((unsigned)((p.L + kTileT - 1) / kTileT), (unsigned)((p.D + kTileD - 1) / kTileD), (unsigned)p.B);
+    conv_silu_forward_kernel<K><<<grid, dim3(kTileD, kRowsY), 0, stream>>>(p);
+  }
+}
+template <int K>
+static void launch_backward(const ConvParams& p, cudaStream_t stream) {
+  if (backward_vec_ok(p)) {
+    // enough CTAs for a few waves, as few partial sums (atomics) as that allows
+    const long long tiles_t = (p.L + kVT - 1) / kVT, dblocks = (p.D + kVDB - 1) / kVDB;
+    long long per_cta = tiles_t * dblocks * p.B / 8192;
+    per_cta = per_cta < 1 ? 1 : (per_cta > tiles_t ? tiles_t : per_cta);
+    dim3 grid((unsigned)((tiles_t + per_cta - 1) / per_cta), (unsigned)dblocks, (unsigned)p.B);
+    conv_silu_backward_vec_kernel<K><<<grid, dim3(32, kVWarps), 0, stream>>>(p, (int)per_cta);
+  } else {
+    dim3 grid((unsigned)((p.L + kTileT - 1) / kTileT), (unsigned)((p.D + kTileD - 1) / kTileD), (unsigned)p.B);
+    conv_silu_backward_kernel<K><<<grid, dim3(kTileD, kRowsY), 0, stream>>>(p);
   }
 }
 
@@ -174,8 +446,12 @@ int ossm_b200_conv1d_silu_forward(const float* x, int64_t ldx, const float* weig
   if (int rc = mixer::check("conv1d_silu_forward", p)) return rc;
   if (B == 0 || L == 0 || D == 0) return kOk;
   if (!x || !weight || (!out_bdl && !out_bld)) { set_last_error("conv1d_silu_forward: null pointer"); return kErrInvalidArgument; }
-  dim3 grid((unsigned)((L + mixer::kTileT - 1) / mixer::kTileT), (unsigned)((D + mixer::kTileD - 1) / mixer::kTileD), (unsigned)B);
-  mixer::conv_silu_forward_kernel<<<grid, dim3(mixer::kTileD, mixer::kRowsY), 0, stream>>>(p);
+  switch (taps) {
+    case 1: mixer::launch_forward<1>(p, stream); break;
+    case 2: mixer::launch_forward<2>(p, stream); break;
+    case 3: mixer::launch_forward<3>(p, stream); break;
+    default: mixer::launch_forward<4>(p, stream); break;
+  }
   return check_cuda(cudaGetLastError(), "conv_silu_forward_kernel launch");
 }
 
@@ -194,8 +470,12 @@ int ossm_b200_conv1d_silu_backward(const float* x, int64_t ldx, const float* wei
     if (int rc = check_cuda(cudaMemsetAsync(grad_bias, 0, (size_t)D * sizeof(float), stream), "memset grad_bias")) return rc;
   if (B == 0 || L == 0) return kOk;
   if (!x || !weight || !grad_x || (!grad_bdl && !grad_bld)) { set_last_error("conv1d_silu_backward: null pointer"); return kErrInvalidArgument; }
-  dim3 grid((unsigned)((L + mixer::kTileT - 1) / mixer::kTileT), (unsigned)((D + mixer::kTileD - 1) / mixer::kTileD), (unsigned)B);
-  mixer::conv_silu_backward_kernel<<<grid, dim3(mixer::kTileD, mixer::kRowsY), 0, stream>>>(p);
+  switch (taps) {
+    case 1: mixer::launch_backward<1>(p, stream); break;
+    case 2: mixer::launch_backward<2>(p, stream); break;
+    case 3: mixer::launch_backward<3>(p, stream); break;
+    default: mixer::launch_backward<4>(p, stream); break;
+  }
   return check_cuda(cudaGetLastError(), "conv_silu_backward_kernel launch");
 }
 
