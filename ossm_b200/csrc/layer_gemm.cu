@@ -19,12 +19,14 @@
 // lo*lo term is below 2^-22 relative).  The weights are split once by split_tf32_kernel; the
 // activations are split inside the GEMM by four "splitter" warps between the TMA load and the MMA.
 //
-// Kernel structure (one CTA = one 128 x BN output tile, K walked in slices of 16 floats = 64 B, ring of 4 stages):
+// Kernel structure (persistent CTAs, one per SM, each walking 128 x BN output tiles; K in slices of 16 floats = 64 B
+// through a ring of 4 stages that runs on across tiles; two accumulators alternate in tensor memory):
 //   warp 0       producer: one lane issues the TMA loads (SWIZZLE_64B) of A, W_hi, W_lo per slice
-//   warp 1       allocates the accumulator in tensor memory; one lane issues 6 tcgen05.mma per slice
-//                (2 K-steps of 8 x 3 operand combinations) and commits the stage back to the producer
-//   warps 2..5   splitters: rewrite the A slice in place as hi and write lo beside it; afterwards the
-//                epilogue: tcgen05.ld the accumulator (lane = output row), add diag*aux, store
+//   warp 1       allocates tensor memory; one lane issues 6 tcgen05.mma per slice (2 K-steps of 8 x 3 operand
+//                combinations), commits the stage back to the producer and, per tile, the accumulator to the epilogue
+//   warps 2..5   splitters: rewrite the A slice in place as hi and write lo beside it
+//   warps 6..9   epilogue: tcgen05.ld the finished accumulator (lane = output row), add diag*aux, store, hand the
+//                accumulator back -- while the other warps already work on the next tile
 // Stages are handed over with mbarriers; every wait is bounded in time and a wait that gives up sets
 // the device status word and lets the CTA run to its normal end (tensor memory is always released).
 // No cluster launch and no multicast: the same kernel runs unchanged under several ranks per node.
@@ -37,11 +39,11 @@ OSSM_B200_STATUS_ACCESSOR(status_layer)
 namespace layer {
 
 constexpr int kBM = 128;            // output rows per CTA = TMEM lanes
-constexpr int kBK = 32;             // weight-gradient kernel: K rows per slice (operand rows are 128-byte swizzle rows)
+constexpr int kBK = 16;             // weight-gradient kernel: K rows (time steps) per slice; a four-deep ring fits
 constexpr int kPK = 16;             // projection kernel: floats per K slice = one 64-byte swizzle row; the smaller
                                     // slice buys a four-deep ring (TMA -> split -> MMA needs the depth, the MMAs of
                                     // one slice take less time than its load and split)
-constexpr int kThreads = 192;       // producer warp, MMA warp, four splitter / epilogue warps
+constexpr int kThreads = 320;       // producer warp, MMA warp, four splitter warps, four epilogue warps
 constexpr int kATile = kBM * kPK * 4;   // 8 KiB
 
 enum RowMap : int { kRowIdentity = 0, kRowBatchToTime = 1, kRowTimeToBatch = 2 };
@@ -57,6 +59,7 @@ struct GemmParams {
   long long batch, length;   // for the row maps: M = batch * length
   int row_map;
   int stages;
+  long long tiles_m, tiles_n;   // output tiles of 128 x BN
 };
 
 __device__ __forceinline__ long long dest_row(const GemmParams& p, long long m) {
@@ -147,6 +150,10 @@ struct Smem {
 
 constexpr int kMaxStages = 6;
 
+// Persistent CTA (one per SM): output tiles blockIdx.x, blockIdx.x + gridDim.x, ... in an order that puts the
+// column blocks of one row block on neighbouring SMs at the same time (the second reads its activations from L2).
+// The ring of K slices runs on across tile boundaries, and two accumulators alternate in tensor memory, so the
+// loads and MMAs of tile i+1 overlap the epilogue of tile i.
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_whi,
@@ -157,15 +164,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);            // [stages] TMA landed
   uint64_t* split = full + kMaxStages;                           // [stages] A split into hi / lo
   uint64_t* empty = split + kMaxStages;                          // [stages] MMAs of the stage finished
-  uint64_t* acc_done = empty + kMaxStages;                       // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* acc_full = empty + kMaxStages;                       // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + 2;                            // [2] accumulator read out by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   unsigned char* stage0 = smem + 1024;
   using S = Smem<BN>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long m0 = (long long)blockIdx.x * kBM;
-  const long long n0 = (long long)blockIdx.y * BN;
   const int nslices = (int)((p.K + kPK - 1) / kPK);
   const int stages = p.stages;
+  const long long ntiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tm_a);
@@ -176,88 +183,117 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       mbar_init(&split[s], 128);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);       // BN float32 columns x 128 lanes
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);   // two accumulators of BN float32 columns x 128 lanes
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ---- producer
     if (lane == 0) {
-      for (int s = 0; s < nslices; ++s) {
-        const int b = s % stages;
-        if (s >= stages && !mbar_wait(&empty[b], ((s / stages) - 1) & 1, kWaitLimitNs, kStatusMmaTimeout)) break;
-        unsigned char* st = stage0 + (size_t)b * S::kStage;
-        mbar_expect_tx(&full[b], kATile + 2 * S::kWTile);
-        tma_load_2d(st, &tm_a, &full[b], s * kPK, (int32_t)m0);
-        tma_load_2d(st + 2 * kATile, &tm_whi, &full[b], s * kPK, (int32_t)n0);
-        tma_load_2d(st + 2 * kATile + S::kWTile, &tm_wlo, &full[b], s * kPK, (int32_t)n0);
+      long long g = 0;                              // slices issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int32_t m0 = (int32_t)((tile / p.tiles_n) * kBM), n0 = (int32_t)((tile % p.tiles_n) * BN);
+        for (int s = 0; s < nslices; ++s, ++g) {
+          const int b = (int)(g % stages);
+          if (g >= stages && !mbar_wait(&empty[b], (uint32_t)((g / stages) - 1) & 1u, kWaitLimitNs, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          unsigned char* st = stage0 + (size_t)b * S::kStage;
+          mbar_expect_tx(&full[b], kATile + 2 * S::kWTile);
+          tma_load_2d(st, &tm_a, &full[b], s * kPK, m0);
+          tma_load_2d(st + 2 * kATile, &tm_whi, &full[b], s * kPK, n0);
+          tma_load_2d(st + 2 * kATile + S::kWTile, &tm_wlo, &full[b], s * kPK, n0);
+        }
       }
     }
   } else if (warp == 1) {
+    // ---- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_tf32(kBM, BN);
+      long long g = 0, it = 0;
       bool ok = true;
-      for (int s = 0; s < nslices && ok; ++s) {
-        const int b = s % stages;
-        const uint32_t ph = (s / stages) & 1;
-        ok = mbar_wait(&full[b], ph) && mbar_wait(&split[b], ph);
+      for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+        const int buf = (int)(it & 1);
+        if (it >= 2) ok = mbar_wait(&acc_empty[buf], (uint32_t)((it >> 1) - 1) & 1u);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t st = smem_u32(stage0 + (size_t)b * S::kStage);
-        const uint32_t a_hi = st, a_lo = st + kATile, w_hi = st + 2 * kATile, w_lo = w_hi + S::kWTile;
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+        for (int s = 0; s < nslices; ++s, ++g) {
+          const int b = (int)(g % stages);
+          const uint32_t ph = (uint32_t)(g / stages) & 1u;
+          ok = mbar_wait(&full[b], ph) && mbar_wait(&split[b], ph);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(stage0 + (size_t)b * S::kStage);
+          const uint32_t a_hi = st, a_lo = st + kATile, w_hi = st + 2 * kATile, w_lo = w_hi + S::kWTile;
 #pragma unroll
-        for (int k = 0; k < kPK / 8; ++k) {
-          const uint32_t off = k * 32;     // 8 TF32 values = 32 bytes along the swizzle row
-          umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_hi + off), idesc, (s | k) != 0);
-          umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_lo + off), idesc, 1);
-          umma_tf32(tmem_acc, smem_desc_k_sw64(a_lo + off), smem_desc_k_sw64(w_hi + off), idesc, 1);
+          for (int k = 0; k < kPK / 8; ++k) {
+            const uint32_t off = k * 32;     // 8 TF32 values = 32 bytes along the swizzle row
+            umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_hi + off), idesc, (s | k) != 0);
+            umma_tf32(tmem_acc, smem_desc_k_sw64(a_hi + off), smem_desc_k_sw64(w_lo + off), idesc, 1);
+            umma_tf32(tmem_acc, smem_desc_k_sw64(a_lo + off), smem_desc_k_sw64(w_hi + off), idesc, 1);
+          }
+          umma_commit(&empty[b]);            // the stage may be refilled once these MMAs have read it
         }
-        umma_commit(&empty[b]);            // the stage may be refilled once these MMAs have read it
+        if (ok) umma_commit(&acc_full[buf]);  // everything issued so far: this tile's accumulator is final
       }
-      umma_commit(acc_done);               // everything issued so far: the accumulator is final
     }
-  } else {
+  } else if (warp < 6) {
     // ---- splitters: hi in place, lo beside it (same swizzled positions, so the layout is irrelevant here)
     const int t = threadIdx.x - 64;        // 0..127
+    long long g = 0;
     bool ok = true;
-    for (int s = 0; s < nslices; ++s) {
-      const int b = s % stages;
-      ok = mbar_wait(&full[b], (s / stages) & 1);
-      if (!ok) break;
-      float4* hi = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage);
-      float4* lo = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage + kATile);
+    for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      for (int s = 0; s < nslices; ++s, ++g) {
+        const int b = (int)(g % stages);
+        ok = mbar_wait(&full[b], (uint32_t)(g / stages) & 1u);
+        if (!ok) break;
+        float4* hi = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage);
+        float4* lo = reinterpret_cast<float4*>(stage0 + (size_t)b * S::kStage + kATile);
 #pragma unroll
-      for (int i = 0; i < kATile / 16 / 128; ++i) {     // 4 vectors of 16 bytes per thread
-        const float4 v = hi[i * 128 + t];
-        float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
-        hi[i * 128 + t] = h;
-        lo[i * 128 + t] = l;
+        for (int i = 0; i < kATile / 16 / 128; ++i) {     // 4 vectors of 16 bytes per thread
+          const float4 v = hi[i * 128 + t];
+          float4 h, l;
+          h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
+          h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
+          h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
+          h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+          hi[i * 128 + t] = h;
+          lo[i * 128 + t] = l;
+        }
+        fence_proxy_async();                 // generic-proxy writes become visible to the tensor core
+        mbar_arrive(&split[b]);
       }
-      fence_proxy_async();                 // generic-proxy writes become visible to the tensor core
-      mbar_arrive(&split[b]);
     }
+  } else {
     // ---- epilogue: lane quarter (warp % 4) of the accumulator, 32 columns at a time
-    if (ok) ok = mbar_wait(acc_done, 0, kWaitLimitNs, kStatusMmaTimeout);
-    if (ok) {
+    const int q = warp & 3;
+    const bool vec = ((p.ldo & 3) == 0) && ((p.plane_stride & 3) == 0) && ((p.col_block & 31) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0) &&
+                     (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+    long long it = 0;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+      const int buf = (int)(it & 1);
+      if (!mbar_wait(&acc_full[buf], (uint32_t)(it >> 1) & 1u, kWaitLimitNs, kStatusMmaTimeout)) break;
       tc_fence_after();
-      const int q = warp & 3;
+      const long long m0 = (tile / p.tiles_n) * kBM, n0 = (tile % p.tiles_n) * BN;
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
       const long long m = m0 + q * 32 + lane;
       const bool row_ok = m < p.M;
       const long long drow = row_ok ? dest_row(p, m) : 0;
       float* out_row = p.out + drow * p.ldo;
       const float* aux_row = p.aux ? p.aux + drow * p.ldo : nullptr;
-      const bool vec = ((p.ldo & 3) == 0) && ((p.plane_stride & 3) == 0) && ((p.col_block & 31) == 0) &&
-                       ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0) &&
-                       (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
@@ -287,13 +323,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);          // this thread's reads of the accumulator are complete
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, BN);
+    tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -301,10 +339,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 // Weight gradients:  out[m, n] = sum over all (b, l) rows of  X[row_x(b,l), m] * Y[row_y(b,l), n]
 // (grad_B from grad_bu and u, grad_C from grad_y and x: dlinoss.py:217-247 differentiated).  The
 // contraction runs over the ROWS of both activation matrices, which may be stored in different row
-// orders (batch-major b*L + l or time-major l*B + b): a K slice is 32 consecutive time steps of one
+// orders (batch-major b*L + l or time-major l*B + b): a K slice is 16 consecutive time steps of one
 // batch entry, fetched from either order by a rank-4 tensor map (32 columns, time, column block, batch)
-// whose box {32, 32, tile/32, 1} lands in shared memory as column blocks of [32 rows x 128 B] -- the
-// canonical MN-major operand layout of the tensor core: leading byte offset = 4096 B between column
+// whose box {32, 16, tile/32, 1} lands in shared memory as column blocks of [16 rows x 128 B] -- the
+// canonical MN-major operand layout of the tensor core: leading byte offset = 2048 B between column
 // blocks, K rows 128 B apart in groups of 4 (512 B, the stride byte offset).  For 32-bit operands in this
 // orientation the hardware takes one swizzle only, 32-byte chunks within the 128-byte row
 // (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B on the TMA side, layout type 1 in the matrix descriptor).  Both operands are activations, so both are split into hi / lo
@@ -316,7 +354,7 @@ constexpr int kWgThreads = 64 + 256;      // producer warp, MMA warp, eight spli
 __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3ffffu) >> 4);          // start address
-  d |= (uint64_t)(4096 >> 4) << 16;                 // leading byte offset: next block of 32 M/N elements
+  d |= (uint64_t)((kBK * 128) >> 4) << 16;          // leading byte offset: next block of 32 M/N elements
   d |= (uint64_t)(512 >> 4) << 32;                  // stride byte offset: next group of 4 K rows
   d |= (uint64_t)1 << 46;                           // descriptor version
   d |= (uint64_t)1 << 61;                           // 128-byte swizzle span with 32-byte chunks
@@ -346,7 +384,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   uint64_t* acc_done = empty + kMaxStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   unsigned char* stage0 = smem + 1024;
-  constexpr int kXTile = kBM * kBK * 4;        // 16 KiB: 4 column blocks of [32][32]
+  constexpr int kXTile = kBM * kBK * 4;        // 8 KiB: 4 column blocks of [16 rows][32 floats]
   constexpr int kYTile = BN * kBK * 4;
   constexpr int kStage = 2 * kXTile + 2 * kYTile;   // X_hi | X_lo | Y_hi | Y_lo
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -490,16 +528,15 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUtensorMap& tl, GemmParams p,
                        cudaStream_t stream) {
   using S = Smem<BN>;
-  // two CTAs per SM (each with its own accumulator, 2 x BN <= 512 tensor-memory columns): the epilogue of one
-  // overlaps the K loop of the other, which matters because K is only 256..512 here
   int stages = kMaxStages;
-  while (stages > 1 && S::bytes(stages) > 110 * 1024) --stages;
-  const int nslices = (int)((p.K + kPK - 1) / kPK);
-  if (stages > nslices) stages = nslices;
+  while (stages > 1 && S::bytes(stages) > 200 * 1024) --stages;
   p.stages = stages;
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
   const size_t smem = S::bytes(stages);
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN>), smem)) return rc;
-  dim3 grid((unsigned)((p.M + kBM - 1) / kBM), (unsigned)((p.N + BN - 1) / BN));
+  const long long ntiles = p.tiles_m * p.tiles_n;
+  const unsigned grid = (unsigned)(ntiles < (long long)sm_count() ? ntiles : (long long)sm_count());
   gemm_tf32x3_kernel<BN><<<grid, kThreads, smem, stream>>>(ta, th, tl, p);
   return check_cuda(cudaGetLastError(), "gemm_tf32x3_kernel launch");
 }

@@ -209,7 +209,7 @@ constexpr int kVPitch = 130;
 __device__ __forceinline__ float2 ldg2(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
 
 template <int K>
-__global__ void __launch_bounds__(32 * kVWarps) conv_silu_forward_vec_kernel(ConvParams p) {
+__global__ void __launch_bounds__(32 * kVWarps, 5) conv_silu_forward_vec_kernel(ConvParams p) {
   constexpr int halo = K - 1;
   __shared__ __align__(16) float tile[kVT][kVPitch];
   const int lane = threadIdx.x, w = threadIdx.y;
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(32 * kVWarps) conv_silu_forward_vec_kernel(Con
 constexpr int kVDB = 64;
 constexpr int kVPitchB = kVDB + 2;
 template <int K>
-__global__ void __launch_bounds__(32 * kVWarps) conv_silu_backward_vec_kernel(ConvParams p, int tiles_per_cta) {
+__global__ void __launch_bounds__(32 * kVWarps, 4) conv_silu_backward_vec_kernel(ConvParams p, int tiles_per_cta) {
   constexpr int halo = K - 1;
   constexpr int kRows = kVT + halo;
   static_assert(kRows * kVPitchB >= kVWarps * (K + 1) * kVDB, "reduction reuses the tile");
