@@ -140,12 +140,15 @@ __host__ __device__ constexpr uint32_t instr_desc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+constexpr int kTurnPitch = 36;      // floats per row of an epilogue turn buffer: 16-byte accesses of 8 lanes hit 32 banks
+
 // Shared memory: [0,1024) barriers + TMEM address | stages x (A_hi 8K | A_lo 8K | W_hi BN*64 | W_lo BN*64)
 template <int BN>
 struct Smem {
   static constexpr int kWTile = BN * kPK * 4;
   static constexpr int kStage = 2 * kATile + 2 * kWTile;
-  static constexpr size_t bytes(int stages) { return 1024 + (size_t)stages * kStage + 1024; }   // + alignment slack
+  // barriers | stages | four epilogue turn buffers | alignment slack
+  static constexpr size_t bytes(int stages) { return 1024 + (size_t)stages * kStage + 4 * 32 * kTurnPitch * 4 + 1024; }
 };
 
 constexpr int kMaxStages = 6;
@@ -269,19 +272,23 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
           h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
           h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
-          hi[i * 128 + t] = h;
-          lo[i * 128 + t] = l;
+          lo[i * 128 + t] = l;                 // hi stays as loaded: the tensor core ignores the 13 low bits
         }
         fence_proxy_async();                 // generic-proxy writes become visible to the tensor core
         mbar_arrive(&split[b]);
       }
     }
   } else {
-    // ---- epilogue: lane quarter (warp % 4) of the accumulator, 32 columns at a time
+    // ---- epilogue: lane quarter (warp % 4) of the accumulator, 32 columns at a time.  tcgen05.ld gives every
+    // lane 32 consecutive columns of ITS row; stored like that, one instruction would touch 32 rows with 16 bytes
+    // each.  The chunk is turned through a padded shared-memory buffer instead, so that eight lanes write one
+    // 128-byte line of a row (and read aux the same way): four full lines per store instruction.
     const int q = warp & 3;
     const bool vec = ((p.ldo & 3) == 0) && ((p.plane_stride & 3) == 0) && ((p.col_block & 31) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0) &&
                      (!p.aux || (reinterpret_cast<uintptr_t>(p.aux) & 15u) == 0);
+    float* turn = reinterpret_cast<float*>(stage0 + (size_t)stages * S::kStage) + q * (32 * kTurnPitch);
+    const int sub = lane >> 3, col4 = (lane & 7) * 4;       // read-out: row 4*i + sub, columns col4 .. col4+3
     long long it = 0;
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       const int buf = (int)(it & 1);
@@ -291,30 +298,40 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
       const long long m = m0 + q * 32 + lane;
       const bool row_ok = m < p.M;
-      const long long drow = row_ok ? dest_row(p, m) : 0;
-      float* out_row = p.out + drow * p.ldo;
-      const float* aux_row = p.aux ? p.aux + drow * p.ldo : nullptr;
+      const long long drow = row_ok ? dest_row(p, m) : -1;     // -1: row beyond M
+      // destination rows of the eight rows this lane stores in the turned layout
+      long long drow_t[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) drow_t[i] = __shfl_sync(0xffffffffu, drow, 4 * i + sub);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
         __syncwarp();
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);   // whole warp takes part
         const long long n = n0 + c0;
-        if (!row_ok || n >= p.N) continue;
+        if (n >= p.N) continue;
         if (vec && n + 32 <= p.N) {
           // 32 columns of one plane (col_block is a multiple of 32 here)
-          const long long off = (n / p.col_block) * p.plane_stride + (n % p.col_block);
+          const long long off = (n / p.col_block) * p.plane_stride + (n % p.col_block) + col4;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            if (aux_row) {
-              const float4 a = *reinterpret_cast<const float4*>(aux_row + off + j);
-              const float4 d = *reinterpret_cast<const float4*>(p.diag + n + j);
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(turn + lane * kTurnPitch + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          __syncwarp();
+          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.aux) d = *reinterpret_cast<const float4*>(p.diag + n + col4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 o = *reinterpret_cast<const float4*>(turn + (4 * i + sub) * kTurnPitch + col4);
+            if (drow_t[i] < 0) continue;
+            if (p.aux) {
+              const float4 a = *reinterpret_cast<const float4*>(p.aux + drow_t[i] * p.ldo + off);
               o.x = fmaf(d.x, a.x, o.x); o.y = fmaf(d.y, a.y, o.y); o.z = fmaf(d.z, a.z, o.z); o.w = fmaf(d.w, a.w, o.w);
             }
-            *reinterpret_cast<float4*>(out_row + off + j) = o;
+            *reinterpret_cast<float4*>(p.out + drow_t[i] * p.ldo + off) = o;
           }
-        } else {
+        } else if (row_ok) {
+          float* out_row = p.out + drow * p.ldo;
+          const float* aux_row = p.aux ? p.aux + drow * p.ldo : nullptr;
           for (int j = 0; j < 32 && n + j < p.N; ++j) {
             const long long off = ((n + j) / p.col_block) * p.plane_stride + ((n + j) % p.col_block);
             float o = v[j];
@@ -466,8 +483,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
           h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
           h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
           h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
-          hi[i] = h;
-          lo[i] = l;
+          lo[i] = l;                           // hi stays as loaded: the tensor core ignores the 13 low bits
         }
       };
       split_tile(reinterpret_cast<float4*>(st), reinterpret_cast<float4*>(st + kXTile), kXTile / 16);
@@ -529,7 +545,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUten
                        cudaStream_t stream) {
   using S = Smem<BN>;
   int stages = kMaxStages;
-  while (stages > 1 && S::bytes(stages) > 200 * 1024) --stages;
+  while (stages > 1 && S::bytes(stages) > 220 * 1024) --stages;
   p.stages = stages;
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
