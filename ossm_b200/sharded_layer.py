@@ -14,7 +14,9 @@ before the collective.
 
 Backward: the gradient of the shard is all-gathered (the transpose of the reduce-scatter), every rank
 computes ``grad_x_r``, runs its scan backward and the local weight gradients; the gradient of the
-replicated input is the sum over ranks (one all-reduce).
+replicated input is the sum over ranks of ``grad_bu_r B_r`` (one all-reduce, started before the
+weight gradient of ``B`` so that it runs beside it) plus the ranks' disjoint ``grad_y D`` slices (an
+all-gather).
 
 The math of one shard is the body of ``DampedLinOSSLayer.forward``
 (``src/ossm/models/dlinoss.py:217-247``); the reference has no distributed code, the oracle is the
@@ -29,7 +31,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-__all__ = ["sharded_dlinoss_layer", "CopyToShards", "hidden_shard"]
+__all__ = ["sharded_dlinoss_layer", "CopyToShards", "OwnColumns", "hidden_shard"]
 
 
 def _world(group) -> int:
@@ -70,11 +72,36 @@ def _torch_project(a2d: Tensor, w: Tensor) -> Tensor:
     return a2d @ w.t()
 
 
-class _ProjectIn(torch.autograd.Function):
-    """``bu [L, B, P_r]`` complex64 (time-major) from ``u [B, L, H]`` and ``W_in [2 P_r, H]``."""
+class OwnColumns(torch.autograd.Function):
+    """``u[..., hidden_shard(H)]`` of a replicated ``u [B, L, H]``; the gradient on ``u`` is the ranks' slices
+    gathered (each rank contributes only its own columns, so an all-gather replaces a sum)."""
 
     @staticmethod
-    def forward(ctx, u: Tensor, w_in: Tensor, use_kernels: bool) -> Tensor:
+    def forward(ctx, u: Tensor, group) -> Tensor:
+        ctx.group = group
+        ctx.hidden = u.size(-1)
+        return u[..., hidden_shard(u.size(-1), group)]
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        world = _world(ctx.group)
+        grad = grad.contiguous()
+        if world == 1:
+            return grad, None
+        batch, length, hs = grad.shape
+        gathered = torch.empty((world, batch, length, hs), dtype=grad.dtype, device=grad.device)
+        dist.all_gather_into_tensor(gathered.view(world * batch, length, hs), grad, group=ctx.group)
+        return gathered.permute(1, 2, 0, 3).reshape(batch, length, ctx.hidden), None
+
+
+class _ProjectIn(torch.autograd.Function):
+    """``bu [L, B, P_r]`` complex64 (time-major) from a replicated ``u [B, L, H]`` and ``W_in [2 P_r, H]``.  The
+    gradient on ``u`` is summed over the ranks here, started before the weight gradient so that the all-reduce
+    runs beside it."""
+
+    @staticmethod
+    def forward(ctx, u: Tensor, w_in: Tensor, use_kernels: bool, group) -> Tensor:
+        ctx.group = group
         batch, length, hidden = u.shape
         p2 = w_in.size(0)
         u2 = u.contiguous().view(batch * length, hidden)
@@ -107,13 +134,18 @@ class _ProjectIn(torch.autograd.Function):
                                 length=length)
         else:
             grad_u = (g.permute(1, 0, 2).reshape(batch * length, p2) @ w_in).view(batch, length, hidden)
+        work = None
+        if _world(ctx.group) > 1:
+            work = dist.all_reduce(grad_u, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
         if ctx.use_kernels:
             from .dlinoss_layer import weight_gradient
 
             grad_w = weight_gradient(g.view(length * batch, p2), True, u2, False, batch, length)
         else:
             grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
-        return grad_u, grad_w, None
+        if work is not None:
+            work.wait()
+        return grad_u, grad_w, None, None
 
 
 class _ProjectOutReduce(torch.autograd.Function):
@@ -215,13 +247,11 @@ def sharded_dlinoss_layer(variant: str, a: Tensor, g: Tensor, step: Tensor, B: T
         use_kernels = u.is_cuda
     if scan is None:
         from .dlinoss import run_dlinoss as scan
-    hidden = u.size(-1)
-    u_in = CopyToShards.apply(u, group)
-    bu = _ProjectIn.apply(u_in, pack_input_weights(B), use_kernels)                   # [L, B, P_r]
+    bu = _ProjectIn.apply(u, pack_input_weights(B), use_kernels, group)               # [L, B, P_r]
     x = scan(variant, a, g, step, bu)
     y = _ProjectOutReduce.apply(x, pack_output_weights(C), group, chunks, scatter_output, use_kernels)
     if scatter_output:
-        # each rank adds D*u on its own columns; their gradients on u are disjoint and meet in the all-reduce
-        return y + u_in[..., hidden_shard(hidden, group)] * D
+        # each rank adds D*u on its own columns; the gradients of these terms on u are disjoint slices
+        return y + OwnColumns.apply(u, group) * D
     # replicated output and replicated D: every rank adds the whole term, so it stays outside the summed gradient
     return y + u * D
