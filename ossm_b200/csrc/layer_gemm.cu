@@ -303,9 +303,27 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       long long drow_t[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) drow_t[i] = __shfl_sync(0xffffffffu, drow, 4 * i + sub);
+      // aux (the D*u term of the output projection) is fetched one chunk ahead: its latency would otherwise be paid
+      // eight times per tile and make the epilogue, not the MMAs, the pace of the kernel
+      float4 aux_next[8];
+      auto fetch_aux = [&](long long n, float4 (&dst)[8]) {
+        const bool in = p.aux && vec && n + 32 <= p.N;
+        const long long off = in ? (n / p.col_block) * p.plane_stride + (n % p.col_block) + col4 : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          dst[i] = (in && drow_t[i] >= 0) ? __ldg(reinterpret_cast<const float4*>(p.aux + drow_t[i] * p.ldo + off))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      if (p.aux) fetch_aux(n0, aux_next);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float v[32];
+        float4 aux_cur[8];
+        if (p.aux) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) aux_cur[i] = aux_next[i];
+          if (c0 + 32 < BN) fetch_aux(n0 + c0 + 32, aux_next);
+        }
         __syncwarp();
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);   // whole warp takes part
         const long long n = n0 + c0;
@@ -324,7 +342,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             float4 o = *reinterpret_cast<const float4*>(turn + (4 * i + sub) * kTurnPitch + col4);
             if (drow_t[i] < 0) continue;
             if (p.aux) {
-              const float4 a = *reinterpret_cast<const float4*>(p.aux + drow_t[i] * p.ldo + off);
+              const float4 a = aux_cur[i];
               o.x = fmaf(d.x, a.x, o.x); o.y = fmaf(d.y, a.y, o.y); o.z = fmaf(d.z, a.z, o.z); o.w = fmaf(d.w, a.w, o.w);
             }
             *reinterpret_cast<float4*>(p.out + drow_t[i] * p.ldo + off) = o;
