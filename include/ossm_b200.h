@@ -213,6 +213,13 @@ int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int
                            size_t partial_bytes, int* splits_out, int64_t M, int64_t N, int64_t batch,
                            int64_t length, ossm_b200_stream_t stream);
 
+/* grad_D of the layer (y = ... + D * u, dlinoss.py:247): partial[c, n] = sum over the rows of CTA c of
+ * X[m, n] * Y[m, n] for dense float32 [rows, cols] matrices (cols a multiple of 4, 16-byte aligned).  `partial` has
+ * ossm_b200_colwise_dot_partials(rows) rows of `cols` floats; the caller adds them (fixed order: deterministic). */
+int ossm_b200_colwise_dot_partials(int64_t rows);
+int ossm_b200_colwise_dot(const float* X, const float* Y, float* partial, int64_t rows, int64_t cols,
+                          ossm_b200_stream_t stream);
+
 /* ---- generic LinOSS scan (complex 2x2 per channel, forcing per step) --------
  * Replaces ossm::linoss_scan (src/ossm/csrc/linoss_scan.cpp:115-146; bindings.cpp:160)
  * and the Python-loop backward of _LinossScanFn (src/ossm/models/linoss.py:83-151).

@@ -558,6 +558,53 @@ __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict
   lo[i] = v - h;
 }
 
+
+// grad_D[n] = sum over rows of X[m, n] * Y[m, n] (dlinoss.py:247 differentiated: y = ... + u * D).  Both matrices are
+// read once with 16-byte loads; a CTA covers a row range and writes one partial row, which the caller adds up in a
+// fixed order.  HBM-bound: 8 B per element.
+constexpr int kDotThreads = 256;
+__global__ void __launch_bounds__(kDotThreads)
+colwise_dot_kernel(const float* __restrict__ X, const float* __restrict__ Y, float* __restrict__ partial,
+                   long long rows, long long cols, long long rows_per_cta) {
+  __shared__ float4 red[kDotThreads];
+  const int vec_cols = (int)(cols >> 2);                    // float4 columns (cols is a multiple of 4)
+  const int lanes_c = vec_cols < kDotThreads ? vec_cols : kDotThreads;   // threads along the columns
+  const int lanes_r = kDotThreads / lanes_c;                // rows in flight per pass
+  const int tc = threadIdx.x % lanes_c, tr = threadIdx.x / lanes_c;
+  const long long r0 = (long long)blockIdx.x * rows_per_cta;
+  const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
+  for (int cb = 0; cb < vec_cols; cb += lanes_c) {          // uniform trip count: the loop holds barriers
+    const int c = cb + tc;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (tr < lanes_r && c < vec_cols) {
+      const float4* x = reinterpret_cast<const float4*>(X) + c;
+      const float4* y = reinterpret_cast<const float4*>(Y) + c;
+#pragma unroll 4
+      for (long long r = r0 + tr; r < r1; r += lanes_r) {
+        const float4 a = ld_nc_f4(x + r * vec_cols), b = ld_nc_f4(y + r * vec_cols);
+        acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+        acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+      }
+    }
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    if (tr == 0 && c < vec_cols) {
+      for (int j = 1; j < lanes_r; ++j) {
+        const float4 o = red[j * lanes_c + tc];
+        acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+      }
+      reinterpret_cast<float4*>(partial + (long long)blockIdx.x * cols)[c] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+static int colwise_dot_ctas(long long rows) {
+  long long n = 4LL * sm_count();
+  if (n > rows) n = rows;
+  return n < 1 ? 1 : (int)n;
+}
+
 template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUtensorMap& tl, GemmParams p,
                        cudaStream_t stream) {
@@ -687,6 +734,22 @@ int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, 
   if (BN == 256) return layer::launch_gemm<256>(ta, th, tl, p, stream);
   if (BN == 128) return layer::launch_gemm<128>(ta, th, tl, p, stream);
   return layer::launch_gemm<64>(ta, th, tl, p, stream);
+}
+
+int ossm_b200_colwise_dot_partials(int64_t rows) { return rows > 0 ? layer::colwise_dot_ctas(rows) : 0; }
+
+int ossm_b200_colwise_dot(const float* X, const float* Y, float* partial, int64_t rows, int64_t cols,
+                          cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) { set_last_error("colwise_dot: extents must be positive"); return kErrInvalidArgument; }
+  if (!X || !Y || !partial) { set_last_error("colwise_dot: null pointer"); return kErrInvalidArgument; }
+  if ((cols & 3) != 0 || ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(partial)) & 15u) != 0) {
+    set_last_error("colwise_dot: the column count must be a multiple of 4 and the matrices 16-byte aligned");
+    return kErrUnsupported;
+  }
+  const int ctas = layer::colwise_dot_ctas(rows);
+  const long long per = (rows + ctas - 1) / ctas;
+  layer::colwise_dot_kernel<<<ctas, layer::kDotThreads, 0, stream>>>(X, Y, partial, rows, cols, per);
+  return check_cuda(cudaGetLastError(), "colwise_dot_kernel launch");
 }
 
 }  // extern "C"

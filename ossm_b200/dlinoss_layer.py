@@ -103,7 +103,7 @@ class DLinossLayerFn(torch.autograd.Function):
         x2 = torch.view_as_real(x).view(length, batch, 2 * ssm)
         grad_w_in = weight_gradient(gbu2.view(length * batch, 2 * ssm), True, u2, False, batch, length)     # [2P, H]
         grad_w_out = weight_gradient(gy, False, x2.view(length * batch, 2 * ssm), True, batch, length)      # [H, 2P]
-        grad_D = (gy * u2).sum(0)
+        grad_D = kernels.colwise_dot(gy, u2) if hidden % 4 == 0 else (gy * u2).sum(0)
         grad_B = grad_w_in.view(ssm, 2, hidden).permute(0, 2, 1).contiguous()
         g3 = grad_w_out.view(hidden, ssm, 2)
         grad_C = torch.stack((g3[..., 0], -g3[..., 1]), dim=-1)

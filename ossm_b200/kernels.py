@@ -736,6 +736,22 @@ def wgrad_tf32x3(X: Tensor, x_time_major: bool, Y: Tensor, y_time_major: bool, b
     return partial[: splits.value * M * N].view(splits.value, M, N).sum(0)
 
 
+def colwise_dot(X: Tensor, Y: Tensor) -> Tensor:
+    """``out[n] = sum_m X[m, n] * Y[m, n]`` for dense float32 ``[rows, cols]`` CUDA matrices (``cols`` a multiple of 4):
+    the layer's ``grad_D`` in one pass over both operands."""
+    for name, t in (("X", X), ("Y", Y)):
+        _require_cuda(name, t)
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.dim() != 2 or t.shape != X.shape:
+            raise RuntimeError(f"ossm_b200: {name} must be a contiguous float32 [rows, cols] CUDA matrix")
+    rows, cols = X.shape
+    lib = _lib.load()
+    partial = torch.empty((int(lib.ossm_b200_colwise_dot_partials(rows)), cols), dtype=torch.float32, device=X.device)
+    with torch.cuda.device(X.device):
+        rc = lib.ossm_b200_colwise_dot(_p(X), _p(Y), _p(partial), rows, cols, _stream(X.device))
+    _lib.check(rc, "colwise_dot")
+    return partial.sum(0)
+
+
 # ---- names ossm calls unconditionally but that are outside this library ------
 def _out_of_scope(name: str):
     def stub(*_args, **_kwargs):

@@ -100,6 +100,25 @@ def test_weight_gradient_product(shape, orders):
     assert record(f"wgrad_tf32x3 {Bz}x{L}x{M}x{N}", "out", rel(out.cpu(), want), 5e-6) <= 5e-6
 
 
+@pytest.mark.parametrize("shape", [(1, 4), (37, 8), (1000, 256), (70000, 512), (5000, 1028), (300, 2052)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_colwise_dot(shape):
+    """``grad_D``: column sums of an elementwise product, one pass, partials added in a fixed order."""
+    from ossm_b200 import kernels as K
+
+    rows, cols = shape
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=gen).cuda()
+    y = torch.randn(rows, cols, generator=gen).cuda()
+    got = K.colwise_dot(x, y)
+    want = (x.double() * y.double()).sum(0)
+    assert got.shape == (cols,)
+    assert rel(got, want) <= 2e-6
+    assert torch.equal(got, K.colwise_dot(x, y))        # deterministic
+    with pytest.raises(RuntimeError):
+        K.colwise_dot(x[:, :3].contiguous(), y[:, :3].contiguous())
+
+
 def test_rejects_bad_arguments():
     from ossm_b200 import kernels as K
 
