@@ -408,7 +408,10 @@ struct WgradParams {
   int stages;
 };
 
-template <int BN>
+// MT = output row tiles of 128 per CTA (1 or 2): with two, the Y slice -- the wider operand -- is fetched and split once
+// for twice the MMAs, and the two accumulators fill tensor memory (there is no epilogue to overlap: a CTA reads its
+// accumulators out once, at the end of its K range).
+template <int BN, int MT>
 __global__ void __launch_bounds__(kWgThreads, 1)
 wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y, WgradParams p) {
   extern __shared__ unsigned char smem_dyn[];
@@ -419,11 +422,11 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   uint64_t* acc_done = empty + kMaxStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   unsigned char* stage0 = smem + 1024;
-  constexpr int kXTile = kBM * kBK * 4;        // 8 KiB: 4 column blocks of [16 rows][32 floats]
+  constexpr int kXTile = MT * kBM * kBK * 4;   // 8 KiB per row tile: 4 column blocks of [16 rows][32 floats] each
   constexpr int kYTile = BN * kBK * 4;
   constexpr int kStage = 2 * kXTile + 2 * kYTile;   // X_hi | X_lo | Y_hi | Y_lo
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long m0 = (long long)blockIdx.x * kBM;
+  const long long m0 = (long long)blockIdx.x * (MT * kBM);
   const long long n0 = (long long)blockIdx.y * BN;
   const long long total = p.batch * p.slices_per_batch;
   const long long per = (total + gridDim.z - 1) / gridDim.z;
@@ -444,7 +447,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  if (warp == 1) tmem_alloc(tmem_slot, MT * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -475,11 +478,16 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const uint32_t st = smem_u32(stage0 + (size_t)b * kStage);
         const uint32_t x_hi = st, x_lo = st + kXTile, y_hi = st + 2 * kXTile, y_lo = y_hi + kYTile;
 #pragma unroll
-        for (int k = 0; k < kBK / 8; ++k) {
-          const uint32_t off = k * 1024;     // 8 K rows = two swizzle groups inside every column block
-          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_hi + off), idesc, (s | k) != 0);
-          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_hi + off), smem_desc_mn_sw128(y_lo + off), idesc, 1);
-          umma_tf32(tmem_acc, smem_desc_mn_sw128(x_lo + off), smem_desc_mn_sw128(y_hi + off), idesc, 1);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t xo = mt * (kBM * kBK * 4);     // the row tile's four column blocks
+          const uint32_t acc = tmem_acc + (uint32_t)(mt * BN);
+#pragma unroll
+          for (int k = 0; k < kBK / 8; ++k) {
+            const uint32_t off = k * 1024;     // 8 K rows = two swizzle groups inside every column block
+            umma_tf32(acc, smem_desc_mn_sw128(x_hi + xo + off), smem_desc_mn_sw128(y_hi + off), idesc, (s | k) != 0);
+            umma_tf32(acc, smem_desc_mn_sw128(x_hi + xo + off), smem_desc_mn_sw128(y_lo + off), idesc, 1);
+            umma_tf32(acc, smem_desc_mn_sw128(x_lo + xo + off), smem_desc_mn_sw128(y_hi + off), idesc, 1);
+          }
         }
         umma_commit(&empty[b]);
       }
@@ -514,14 +522,16 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       if (ok) {
         tc_fence_after();
         const int q = warp & 3;
-        const long long m = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+        const long long m = m0 + mt * kBM + q * 32 + lane;
         float* row = p.partial + ((long long)blockIdx.z * p.M + (m < p.M ? m : 0)) * p.N;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
           __syncwarp();
           if (nslices > 0) {
-            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + c0), v);
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;      // a split without slices contributes zeros
@@ -536,6 +546,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             for (int j = 0; j < 32 && n + j < p.N; ++j) row[n + j] = v[j];
           }
         }
+        }
       }
     }
   }
@@ -543,7 +554,7 @@ wgrad_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, BN);
+    tmem_dealloc(tmem_acc, MT * BN);
   }
 }
 
@@ -623,9 +634,12 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUten
 }
 
 // K slices are divided over enough CTAs to fill the GPU once.
+static int wgrad_row_tiles(long long M) { return M > kBM ? 2 : 1; }
+
 static int wgrad_splits(long long M, long long N, long long batch, long long length) {
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  const long long tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const long long bm = (long long)kBM * wgrad_row_tiles(M);
+  const long long tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
   const long long total = batch * ((length + kBK - 1) / kBK);
   long long splits = (sm_count() + tiles - 1) / tiles;
   if (splits > total) splits = total;
@@ -633,16 +647,16 @@ static int wgrad_splits(long long M, long long N, long long batch, long long len
   return splits < 1 ? 1 : (int)splits;
 }
 
-template <int BN>
+template <int BN, int MT>
 static int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& ty, WgradParams p, int splits, cudaStream_t stream) {
-  constexpr size_t stage = 2 * (size_t)kBM * kBK * 4 + 2 * (size_t)BN * kBK * 4;
+  constexpr size_t stage = 2 * (size_t)MT * kBM * kBK * 4 + 2 * (size_t)BN * kBK * 4;
   int stages = kMaxStages;
   while (stages > 1 && 2048 + stages * stage > 220 * 1024) --stages;
   p.stages = stages;
   const size_t smem = 2048 + stages * stage;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(wgrad_tf32x3_kernel<BN>), smem)) return rc;
-  dim3 grid((unsigned)((p.M + kBM - 1) / kBM), (unsigned)((p.N + BN - 1) / BN), (unsigned)splits);
-  wgrad_tf32x3_kernel<BN><<<grid, kWgThreads, smem, stream>>>(tx, ty, p);
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(wgrad_tf32x3_kernel<BN, MT>), smem)) return rc;
+  dim3 grid((unsigned)((p.M + MT * kBM - 1) / (MT * kBM)), (unsigned)((p.N + BN - 1) / BN), (unsigned)splits);
+  wgrad_tf32x3_kernel<BN, MT><<<grid, kWgThreads, smem, stream>>>(tx, ty, p);
   return check_cuda(cudaGetLastError(), "wgrad_tf32x3_kernel launch");
 }
 
@@ -688,7 +702,8 @@ int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int
     return make_tensor_map_4d_f32_sw128(tm, base, dims, strides, box, true);
   };
   CUtensorMap tx, ty;
-  if (!make(&tx, X, M, x_time_major != 0, layer::kBM) || !make(&ty, Y, N, y_time_major != 0, (uint32_t)BN)) {
+  const int MT = layer::wgrad_row_tiles(M);
+  if (!make(&tx, X, M, x_time_major != 0, (uint32_t)(MT * layer::kBM)) || !make(&ty, Y, N, y_time_major != 0, (uint32_t)BN)) {
     set_last_error("wgrad_tf32x3: operands must be 16-byte aligned dense matrices");
     return kErrUnsupported;
   }
@@ -696,9 +711,14 @@ int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int
   p.partial = partial; p.M = M; p.N = N; p.batch = batch; p.length = length;
   p.slices_per_batch = (int)((length + layer::kBK - 1) / layer::kBK);
   *splits_out = splits;
-  if (BN == 256) return layer::launch_wgrad<256>(tx, ty, p, splits, stream);
-  if (BN == 128) return layer::launch_wgrad<128>(tx, ty, p, splits, stream);
-  return layer::launch_wgrad<64>(tx, ty, p, splits, stream);
+  if (MT == 2) {
+    if (BN == 256) return layer::launch_wgrad<256, 2>(tx, ty, p, splits, stream);
+    if (BN == 128) return layer::launch_wgrad<128, 2>(tx, ty, p, splits, stream);
+    return layer::launch_wgrad<64, 2>(tx, ty, p, splits, stream);
+  }
+  if (BN == 256) return layer::launch_wgrad<256, 1>(tx, ty, p, splits, stream);
+  if (BN == 128) return layer::launch_wgrad<128, 1>(tx, ty, p, splits, stream);
+  return layer::launch_wgrad<64, 1>(tx, ty, p, splits, stream);
 }
 
 int ossm_b200_gemm_tf32x3(const float* A, const float* W_hi, const float* W_lo, float* out, const float* aux,
