@@ -51,9 +51,12 @@ def test_generic_scan_fixture_real_matrix(tag):
     assert so.max_rel_err(b.grad.cpu().numpy(), LGEN[p + "real_grad_b"]) <= 5e-5
 
 
-@pytest.mark.parametrize("shape", [(2, 1, 1), (7, 3, 5), (64, 2, 33), (200, 4, 130)],
+@pytest.mark.parametrize("shape", [(2, 1, 1), (7, 3, 5), (64, 2, 33), (200, 4, 130), (33, 1, 64), (129, 2, 64),
+                                   (500, 3, 70), (1000, 8, 256)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_generic_scan_matches_oracle(shape):
+    """Tiles of 32 steps x 64 series through a four-deep ring: lengths around one tile, past the ring depth and
+    with a ragged tail; series counts below, at and across the 64-series box."""
     from ossm_b200 import kernels
 
     L, B, P = shape
