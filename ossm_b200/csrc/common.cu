@@ -87,6 +87,31 @@ bool make_tensor_map_2d_f32_sw64(CUtensorMap* map, const void* base, uint64_t co
                    CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
+bool make_tensor_map_3d_f32(CUtensorMap* map, const void* base, const uint64_t dims[3], const uint64_t strides_bytes[2],
+                            const uint32_t box[3]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (box[0] * 4) % 16 != 0) return false;
+  cuuint64_t d[3], st[2];
+  cuuint32_t bx[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < 3; ++i) {
+    if (dims[i] == 0 || dims[i] > 0xffffffffull || box[i] == 0 || box[i] > 256) return false;
+    d[i] = dims[i];
+    bx[i] = box[i];
+  }
+  for (int i = 0; i < 2; ++i) {
+    if ((strides_bytes[i] & 15u) != 0 || strides_bytes[i] >= (1ull << 40)) return false;
+    st[i] = strides_bytes[i];
+  }
+  CUtensorMap tmp;
+  CUresult r = fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), d, st, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  memcpy(map, &tmp, sizeof(tmp));
+  return true;
+}
+
 bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
                                   const uint64_t strides_bytes[3], const uint32_t box[4], bool atom32) {
   EncodeTiledFn fn = encode_fn();

@@ -75,6 +75,9 @@ bool make_tensor_map_2d_f32_sw64(CUtensorMap* map, const void* base, uint64_t co
 // strides of dimensions 1..3 (dimension 0 is dense).  box[0] * 4 must be 128.  atom32 selects the variant
 // that swizzles 32-byte chunks (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), the only layout the tensor cores
 // accept for 32-bit operands whose M / N index is the contiguous one.
+// Rank-3 tiled map of float32 data without swizzle: dims / box innermost first, strides in bytes of dimensions 1 and 2.
+bool make_tensor_map_3d_f32(CUtensorMap* map, const void* base, const uint64_t dims[3], const uint64_t strides_bytes[2],
+                            const uint32_t box[3]);
 bool make_tensor_map_4d_f32_sw128(CUtensorMap* map, const void* base, const uint64_t dims[4],
                                   const uint64_t strides_bytes[3], const uint32_t box[4], bool atom32);
 // Same for 16-bit elements (bf16 payloads are moved as raw 16-bit words).
@@ -151,6 +154,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 3-D tiled TMA load global -> shared, completion on `bar` (non-multicast).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t c0, int32_t c1,
+                                            int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 

@@ -387,6 +387,113 @@ __global__ void __launch_bounds__(32 * kVWarps, 4) conv_silu_backward_vec_kernel
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Staged forward: the same arithmetic as the vector kernel, but x arrives through TMA.  A CTA owns 64 channels of
+// one batch entry and walks consecutive time tiles; a rank-3 tensor map (channels, time, batch) delivers each tile
+// with its K-1 rows of history -- the rows before the start of the sequence come back as zeros, which is the causal
+// padding -- into a ring of stages, several tiles ahead of the arithmetic, so that the loads in flight do not depend
+// on registers or on how many warps are resident.
+constexpr int kSC = 64;                 // channels per CTA = one 256-byte box row
+constexpr int kSPitch = kSC + 2;        // transpose tile pitch (see the vector kernels)
+constexpr int kSMaxRing = 6;
+
+template <int K>
+__global__ void __launch_bounds__(32 * kVWarps)
+conv_silu_forward_staged_kernel(const __grid_constant__ CUtensorMap tm_x, ConvParams p, int tiles_per_cta, int ring) {
+  constexpr int halo = K - 1;
+  constexpr int kStageBytes = (kVT + halo) * kSC * 4;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  unsigned char* ring_base = smem_raw + 1024;
+  float (*turn)[kSPitch] = reinterpret_cast<float (*)[kSPitch]>(ring_base + (size_t)ring * kStageBytes);
+  const int lane = threadIdx.x, w = threadIdx.y;
+  const bool leader = lane == 0 && w == 0;
+  const int b = blockIdx.z;
+  const int d0 = blockIdx.y * kSC;
+  const int D = (int)p.D;
+  const long long tiles_all = (p.L + kVT - 1) / kVT;
+  const long long tile0 = (long long)blockIdx.x * tiles_per_cta;
+  const int ntiles = (int)(tiles_all - tile0 < tiles_per_cta ? tiles_all - tile0 : tiles_per_cta);
+  if (leader) {
+    prefetch_tensormap(&tm_x);
+    for (int s = 0; s < ring; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    for (int s = 0; s < ring && s < ntiles; ++s) {
+      mbar_expect_tx(&bars[s], kStageBytes);
+      tma_load_3d(ring_base + (size_t)s * kStageBytes, &tm_x, &bars[s], d0, (int32_t)((tile0 + s) * kVT) - halo, b);
+    }
+  }
+  const int c = 2 * lane;
+  const bool ok = d0 + c < D;
+  float2 wt[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k)
+    wt[k] = ok ? make_float2(__ldg(p.w + (d0 + c) * K + k), __ldg(p.w + (d0 + c + 1) * K + k)) : make_float2(0.f, 0.f);
+  const float2 bias = (ok && p.bias) ? ldg2(p.bias + d0 + c) : make_float2(0.f, 0.f);
+  const int tq = lane & 3, c8 = lane >> 2;
+  __syncthreads();
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < ntiles; ++i) {
+    const long long t0 = (tile0 + i) * kVT;
+    const long long ts = t0 + w * kVSteps;
+    if (!mbar_wait(&bars[slot], parity)) return;
+    const float2* rows = reinterpret_cast<const float2*>(ring_base + (size_t)slot * kStageBytes) +
+                         (size_t)(w * kVSteps) * (kSC / 2) + lane;      // row r holds time t0 - halo + r
+    float2 xv[kVSteps + halo];
+#pragma unroll
+    for (int j = 0; j < kVSteps + halo; ++j) xv[j] = rows[j * (kSC / 2)];
+    float* dst = p.out_bld ? p.out_bld + ((long long)b * p.L + ts) * p.D + d0 + c : nullptr;
+#pragma unroll
+    for (int s = 0; s < kVSteps; ++s) {
+      float2 pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        pre.x = fmaf(wt[k].x, xv[s + k].x, pre.x);
+        pre.y = fmaf(wt[k].y, xv[s + k].y, pre.y);
+      }
+      float2 y;
+      y.x = __fdividef(pre.x, 1.0f + __expf(-pre.x));
+      y.y = __fdividef(pre.y, 1.0f + __expf(-pre.y));
+      if (p.out_bdl) *reinterpret_cast<float2*>(&turn[w * kVSteps + s][c]) = y;
+      if (dst) {
+        if (ok && ts + s < p.L) *reinterpret_cast<float2*>(dst) = y;
+        dst += p.D;
+      }
+    }
+    __syncthreads();          // the stage has been read; the turn tile is complete
+    if (leader && i + ring < ntiles) {
+      fence_proxy_async();
+      mbar_expect_tx(&bars[slot], kStageBytes);
+      tma_load_3d(ring_base + (size_t)slot * kStageBytes, &tm_x, &bars[slot], d0,
+                  (int32_t)((tile0 + i + ring) * kVT) - halo, b);
+    }
+    if (p.out_bdl) {
+#pragma unroll 4
+      for (int it = w; it < (kSC / 8) * (kVT / 16); it += kVWarps) {
+        const int cc = (it >> 2) * 8 + c8, tt = (it & 3) * 16 + tq * 4;
+        const float4 v = make_float4(turn[tt][cc], turn[tt + 1][cc], turn[tt + 2][cc], turn[tt + 3][cc]);
+        if (d0 + cc < D && t0 + tt < p.L)
+          *reinterpret_cast<float4*>(p.out_bdl + ((long long)b * p.D + d0 + cc) * p.L + t0 + tt) = v;
+      }
+      __syncthreads();        // the turn tile may be overwritten
+    }
+    if (++slot == ring) { slot = 0; parity ^= 1; }
+  }
+}
+
+// Tensor map (channels, time, batch) over x [B, L, D] with row pitch ldx; boxes of 64 channels x `rows` steps.
+static bool staged_x_map(CUtensorMap* tm, const float* x, long long B, long long L, long long D, long long ldx,
+                         uint32_t rows) {
+  if ((ldx & 3) != 0 || rows > 256) return false;
+  const uint64_t dims[3] = {(uint64_t)D, (uint64_t)L, (uint64_t)B};
+  const uint64_t strides[2] = {(uint64_t)ldx * 4, (uint64_t)L * (uint64_t)ldx * 4};
+  const uint32_t box[3] = {(uint32_t)kSC, rows, 1};
+  return make_tensor_map_3d_f32(tm, x, dims, strides, box);
+}
+
 static inline bool aligned(const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
 
 static bool forward_vec_ok(const ConvParams& p) {
@@ -400,6 +507,21 @@ static bool backward_vec_ok(const ConvParams& p) {
 
 template <int K>
 static void launch_forward(const ConvParams& p, cudaStream_t stream) {
+  CUtensorMap tm;
+  memset(&tm, 0, sizeof(tm));
+  if (forward_vec_ok(p) && p.L >= 4 * kVT && staged_x_map(&tm, p.x, p.B, p.L, p.D, p.ldx, kVT + K - 1)) {
+    const int ring = 3;
+    const size_t smem = 1024 + (size_t)ring * (kVT + K - 1) * kSC * 4 + (size_t)kVT * kSPitch * 4;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(conv_silu_forward_staged_kernel<K>), smem) == kOk) {
+      // a CTA walks up to 16 consecutive time tiles; fewer when that would leave SMs without work
+      const long long tiles_t = (p.L + kVT - 1) / kVT, dblocks = (p.D + kSC - 1) / kSC;
+      long long per_cta = tiles_t * dblocks * p.B / (8LL * sm_count());
+      per_cta = per_cta < 1 ? 1 : (per_cta > 16 ? 16 : per_cta);
+      dim3 grid((unsigned)((tiles_t + per_cta - 1) / per_cta), (unsigned)dblocks, (unsigned)p.B);
+      conv_silu_forward_staged_kernel<K><<<grid, dim3(32, kVWarps), smem, stream>>>(tm, p, (int)per_cta, ring);
+      return;
+    }
+  }
   if (forward_vec_ok(p)) {
     dim3 grid((unsigned)((p.L + kVT - 1) / kVT), (unsigned)((p.D + kVD - 1) / kVD), (unsigned)p.B);
     conv_silu_forward_vec_kernel<K><<<grid, dim3(32, kVWarps), 0, stream>>>(p);

@@ -30,7 +30,8 @@ def rel(got, want):
     return float((got.double().cpu() - want).abs().max() / want.abs().max().clamp_min(1e-30))
 
 
-@pytest.mark.parametrize("shape", [(2, 70, 40, 4), (1, 1, 3, 4), (3, 130, 96, 3), (2, 64, 32, 2), (1, 200, 33, 1)],
+@pytest.mark.parametrize("shape", [(2, 70, 40, 4), (1, 1, 3, 4), (3, 130, 96, 3), (2, 64, 32, 2), (1, 200, 33, 1),
+                                   (2, 512, 64, 4), (1, 1000, 200, 3), (3, 260, 36, 2), (2, 1156, 128, 4)],
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("strided", [False, True], ids=["dense", "half_of_xz"])
 def test_conv_silu_matches_pytorch(shape, strided):
