@@ -494,6 +494,160 @@ static bool staged_x_map(CUtensorMap* tm, const float* x, long long B, long long
   return make_tensor_map_3d_f32(tm, x, dims, strides, box);
 }
 
+// Staged backward.  Stage = x rows [t0-(K-1), t0+64+(K-1)) | grad_bld rows [t0, t0+64+(K-1)) (both channel
+// contiguous, 256 B per row) | grad_bdl as [64 channels][68 steps] (time contiguous; a thread reads its channels'
+// steps with 16-byte loads).  Nothing is transposed by hand and nothing waits on a register load; the weight and
+// bias sums stay in registers across the tiles a CTA walks.
+template <int K>
+__global__ void __launch_bounds__(32 * kVWarps)
+conv_silu_backward_staged_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g2,
+                                 const __grid_constant__ CUtensorMap tm_g1, ConvParams p, int tiles_per_cta, int ring) {
+  constexpr int halo = K - 1;
+  constexpr int kXBytes = (kVT + 2 * halo) * kSC * 4;
+  constexpr int kG2Bytes = (kVT + halo) * kSC * 4;
+  constexpr int kG1Pitch = kVT + 4;                         // steps per channel row of the time-contiguous tile
+  constexpr int kG1Bytes = kSC * kG1Pitch * 4;
+  constexpr int kStageBytes = kXBytes + kG2Bytes + kG1Bytes;
+  static_assert(kXBytes % 128 == 0 && kG2Bytes % 128 == 0 && kG1Bytes % 128 == 0, "TMA destinations stay 128-byte aligned");
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  unsigned char* ring_base = smem_raw + 1024;
+  const int lane = threadIdx.x, w = threadIdx.y;
+  const bool leader = lane == 0 && w == 0;
+  const int b = blockIdx.z;
+  const int d0 = blockIdx.y * kSC;
+  const int D = (int)p.D;
+  const long long tiles_all = (p.L + kVT - 1) / kVT;
+  const long long tile0 = (long long)blockIdx.x * tiles_per_cta;
+  const int ntiles = (int)(tiles_all - tile0 < tiles_per_cta ? tiles_all - tile0 : tiles_per_cta);
+  const uint32_t tx_bytes = kXBytes + (p.g_bld ? kG2Bytes : 0) + (p.g_bdl ? kG1Bytes : 0);
+  auto issue = [&](int s, long long tile) {
+    unsigned char* st = ring_base + (size_t)s * kStageBytes;
+    const int32_t t0 = (int32_t)(tile * kVT);
+    mbar_expect_tx(&bars[s], tx_bytes);
+    tma_load_3d(st, &tm_x, &bars[s], d0, t0 - halo, b);
+    if (p.g_bld) tma_load_3d(st + kXBytes, &tm_g2, &bars[s], d0, t0, b);
+    if (p.g_bdl) tma_load_3d(st + kXBytes + kG2Bytes, &tm_g1, &bars[s], t0, d0, b);
+  };
+  if (leader) {
+    prefetch_tensormap(&tm_x);
+    if (p.g_bld) prefetch_tensormap(&tm_g2);
+    if (p.g_bdl) prefetch_tensormap(&tm_g1);
+    for (int s = 0; s < ring; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    for (int s = 0; s < ring && s < ntiles; ++s) issue(s, tile0 + s);
+  }
+  const int c = 2 * lane;
+  const bool ok = d0 + c < D;
+  float2 wt[K], accw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    wt[k] = ok ? make_float2(__ldg(p.w + (d0 + c) * K + k), __ldg(p.w + (d0 + c + 1) * K + k)) : make_float2(0.f, 0.f);
+    accw[k] = make_float2(0.f, 0.f);
+  }
+  const float2 bias = (ok && p.bias) ? ldg2(p.bias + d0 + c) : make_float2(0.f, 0.f);
+  float2 accb = make_float2(0.f, 0.f);
+  __syncthreads();
+  int slot = 0;
+  uint32_t parity = 0;
+  for (int i = 0; i < ntiles; ++i) {
+    const long long t0 = (tile0 + i) * kVT;
+    const long long ts = t0 + w * kVSteps;
+    if (!mbar_wait(&bars[slot], parity)) return;
+    const unsigned char* st = ring_base + (size_t)slot * kStageBytes;
+    const float2* xr = reinterpret_cast<const float2*>(st) + (size_t)(w * kVSteps) * (kSC / 2) + lane;   // time ts - halo + j
+    const float2* g2r = reinterpret_cast<const float2*>(st + kXBytes) + (size_t)(w * kVSteps) * (kSC / 2) + lane;
+    const float* g1a = reinterpret_cast<const float*>(st + kXBytes + kG2Bytes) + (size_t)c * kG1Pitch + w * kVSteps;
+    float2 xv[kVSteps + 2 * halo];
+#pragma unroll
+    for (int j = 0; j < kVSteps + 2 * halo; ++j) xv[j] = xr[j * (kSC / 2)];
+    float2 gv[kVSteps + 4];
+#pragma unroll
+    for (int j = 0; j < kVSteps + 4; ++j) gv[j] = make_float2(0.f, 0.f);
+    if (p.g_bld) {
+#pragma unroll
+      for (int j = 0; j < kVSteps + halo; ++j) gv[j] = g2r[j * (kSC / 2)];
+    }
+    if (p.g_bdl) {
+#pragma unroll
+      for (int j = 0; j < kVSteps + 4; j += 4) {
+        if (j < kVSteps + halo) {
+          const float4 a = *reinterpret_cast<const float4*>(g1a + j);
+          const float4 bq = *reinterpret_cast<const float4*>(g1a + kG1Pitch + j);
+          gv[j].x += a.x; gv[j + 1].x += a.y; gv[j + 2].x += a.z; gv[j + 3].x += a.w;
+          gv[j].y += bq.x; gv[j + 1].y += bq.y; gv[j + 2].y += bq.z; gv[j + 3].y += bq.w;
+        }
+      }
+    }
+    float2 dp[kVSteps + halo];
+    float* dst = p.grad_x + ((long long)b * p.L + ts) * p.D + d0 + c;
+#pragma unroll
+    for (int j = 0; j < kVSteps + halo; ++j) {
+      float2 pre = bias;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        pre.x = fmaf(wt[k].x, xv[j + k].x, pre.x);
+        pre.y = fmaf(wt[k].y, xv[j + k].y, pre.y);
+      }
+      const float sx = __fdividef(1.0f, 1.0f + __expf(-pre.x)), sy = __fdividef(1.0f, 1.0f + __expf(-pre.y));
+      const bool live = ok && ts + j < p.L;
+      dp[j].x = live ? gv[j].x * (sx * fmaf(pre.x, 1.0f - sx, 1.0f)) : 0.0f;
+      dp[j].y = live ? gv[j].y * (sy * fmaf(pre.y, 1.0f - sy, 1.0f)) : 0.0f;
+      if (j < kVSteps) {          // the steps after the warp's own belong to the next warp's sums
+        accb.x += dp[j].x; accb.y += dp[j].y;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          accw[k].x = fmaf(dp[j].x, xv[j + k].x, accw[k].x);
+          accw[k].y = fmaf(dp[j].y, xv[j + k].y, accw[k].y);
+        }
+      }
+      if (j >= halo) {            // grad_x[ts + j - halo] = sum_k w[k] * dpre[ts + j - k]
+        float2 gx = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          gx.x = fmaf(wt[k].x, dp[j - k].x, gx.x);
+          gx.y = fmaf(wt[k].y, dp[j - k].y, gx.y);
+        }
+        if (ok && ts + j - halo < p.L) *reinterpret_cast<float2*>(dst) = gx;
+        dst += p.D;
+      }
+    }
+    __syncthreads();          // the stage has been read
+    if (leader && i + ring < ntiles) {
+      fence_proxy_async();
+      issue(slot, tile0 + i + ring);
+    }
+    if (++slot == ring) { slot = 0; parity ^= 1; }
+  }
+  // sums over the CTA's warps, one atomic per (channel, tap)
+  float* red = reinterpret_cast<float*>(ring_base);            // [warp][K + 1][kSC]; every stage has been consumed
+#pragma unroll
+  for (int k = 0; k < K; ++k) *reinterpret_cast<float2*>(red + (w * (K + 1) + k) * kSC + c) = accw[k];
+  *reinterpret_cast<float2*>(red + (w * (K + 1) + K) * kSC + c) = accb;
+  __syncthreads();
+  const int cr = w * 32 + lane;
+  if (cr < kSC && d0 + cr < D) {
+#pragma unroll
+    for (int k = 0; k <= K; ++k) {
+      float s = 0.0f;
+#pragma unroll
+      for (int j = 0; j < kVWarps; ++j) s += red[(j * (K + 1) + k) * kSC + cr];
+      if (k < K) atomicAdd(p.grad_w + (d0 + cr) * K + k, s);
+      else if (p.grad_bias) atomicAdd(p.grad_bias + d0 + cr, s);
+    }
+  }
+}
+
+// Tensor map (time, channels, batch) over a time-contiguous [B, D, L] array; boxes of 68 steps x 64 channels.
+static bool staged_bdl_map(CUtensorMap* tm, const float* g, long long B, long long L, long long D) {
+  if ((L & 3) != 0) return false;
+  const uint64_t dims[3] = {(uint64_t)L, (uint64_t)D, (uint64_t)B};
+  const uint64_t strides[2] = {(uint64_t)L * 4, (uint64_t)D * (uint64_t)L * 4};
+  const uint32_t box[3] = {(uint32_t)(kVT + 4), (uint32_t)kSC, 1};
+  return make_tensor_map_3d_f32(tm, g, dims, strides, box);
+}
+
 static inline bool aligned(const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; }
 
 static bool forward_vec_ok(const ConvParams& p) {
@@ -532,6 +686,25 @@ static void launch_forward(const ConvParams& p, cudaStream_t stream) {
 }
 template <int K>
 static void launch_backward(const ConvParams& p, cudaStream_t stream) {
+  CUtensorMap tx, t2, t1;
+  memset(&tx, 0, sizeof(tx));
+  memset(&t2, 0, sizeof(t2));
+  memset(&t1, 0, sizeof(t1));
+  if (backward_vec_ok(p) && p.L >= 4 * kVT && staged_x_map(&tx, p.x, p.B, p.L, p.D, p.ldx, kVT + 2 * (K - 1)) &&
+      (!p.g_bld || staged_x_map(&t2, p.g_bld, p.B, p.L, p.D, p.D, kVT + K - 1)) &&
+      (!p.g_bdl || staged_bdl_map(&t1, p.g_bdl, p.B, p.L, p.D))) {
+    const int ring = 2;
+    const size_t stage = (size_t)(kVT + 2 * (K - 1)) * kSC * 4 + (size_t)(kVT + K - 1) * kSC * 4 + (size_t)kSC * (kVT + 4) * 4;
+    const size_t smem = 1024 + ring * stage;
+    if (ensure_dynamic_smem(reinterpret_cast<const void*>(conv_silu_backward_staged_kernel<K>), smem) == kOk) {
+      const long long tiles_t = (p.L + kVT - 1) / kVT, dblocks = (p.D + kSC - 1) / kSC;
+      long long per_cta = tiles_t * dblocks * p.B / (8LL * sm_count());
+      per_cta = per_cta < 1 ? 1 : (per_cta > 16 ? 16 : per_cta);
+      dim3 grid((unsigned)((tiles_t + per_cta - 1) / per_cta), (unsigned)dblocks, (unsigned)p.B);
+      conv_silu_backward_staged_kernel<K><<<grid, dim3(32, kVWarps), smem, stream>>>(tx, t2, t1, p, (int)per_cta, ring);
+      return;
+    }
+  }
   if (backward_vec_ok(p)) {
     // enough CTAs for a few waves, as few partial sums (atomics) as that allows
     const long long tiles_t = (p.L + kVT - 1) / kVT, dblocks = (p.D + kVDB - 1) / kVDB;
