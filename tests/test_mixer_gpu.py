@@ -64,15 +64,18 @@ def test_conv_silu_matches_pytorch(shape, strided):
     assert record(tag, "grad_bias", rel(bd.grad, b64.grad), 1e-5) <= 1e-5
 
 
-def test_conv_single_output_gradient():
-    """Only one of the two outputs is used downstream: the other gradient is absent, not zero-filled."""
+@pytest.mark.parametrize("length", [50, 576], ids=["vector_kernels", "staged_kernels"])
+@pytest.mark.parametrize("which", [0, 1], ids=["time_contiguous_only", "channel_contiguous_only"])
+def test_conv_single_output_gradient(length, which):
+    """Only one of the two outputs is used downstream: the other gradient is absent, not zero-filled (the staged
+    backward then leaves that operand's tile out of its stages)."""
     from ossm_b200.mixer import causal_conv1d_silu
 
-    gen = torch.Generator().manual_seed(1)
-    x = torch.randn(2, 50, 16, generator=gen).cuda().requires_grad_(True)
+    gen = torch.Generator().manual_seed(1 + which)
+    x = torch.randn(2, length, 16, generator=gen).cuda().requires_grad_(True)
     w = (torch.randn(16, 1, 4, generator=gen) * 0.5).cuda().requires_grad_(True)
-    o1, _ = causal_conv1d_silu(x, w, None)
-    o1.square().sum().backward()
+    out = causal_conv1d_silu(x, w, None)[which]
+    out.square().sum().backward()
     x64, w64 = x.detach().double().cpu().requires_grad_(True), w.detach().double().cpu().requires_grad_(True)
     F.silu(F.conv1d(F.pad(x64.transpose(1, 2), (3, 0)), w64, None, groups=16)).square().sum().backward()
     assert rel(x.grad, x64.grad) <= 1e-5 and rel(w.grad, w64.grad) <= 1e-5
@@ -88,7 +91,7 @@ CHILD = textwrap.dedent('''
     report = {}
     for d_state in (16, 64):
         mixer = mambarec._MambaMixer(32, d_state=d_state, d_conv=4, expand=2)
-        x = torch.randn(2, 90, 32)
+        x = torch.randn(2, 90 if d_state == 16 else 320, 32)
         ref_mod = copy.deepcopy(mixer).double()
         xr = x.double().requires_grad_(True)
         y_ref = ref_mod(xr)                                  # CPU: ossm's own forward
