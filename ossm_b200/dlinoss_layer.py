@@ -22,6 +22,8 @@ layer passes to ``run_dlinoss``.  CUDA float32 only; there is no other path.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 from torch import Tensor
 
@@ -110,12 +112,18 @@ class DLinossLayerFn(torch.autograd.Function):
         return None, grad_a, grad_g, grad_step, grad_B, grad_C, grad_D, grad_u
 
 
-def dlinoss_layer(variant: str, a_diag: Tensor, g_diag: Tensor, step: Tensor, B: Tensor, C: Tensor, D: Tensor,
+def dlinoss_layer(variant: str, a_diag: Tensor, g_diag: Optional[Tensor], step: Tensor, B: Tensor, C: Tensor, D: Tensor,
                   u: Tensor) -> Tensor:
-    """``y [B, L, H]`` of the D-LinOSS layer body for ``u [B, L, H]`` (float32, CUDA)."""
+    """``y [B, L, H]`` of the D-LinOSS layer body for ``u [B, L, H]`` (float32, CUDA).  The LinOSS layer has the same
+    body around an undamped recurrence (``linoss.py:199-243``): variants ``linoss_im`` / ``linoss_imex`` with
+    ``g_diag=None``."""
     variant = variant.lower()
-    if variant not in ("imex1", "imex2", "im", "ex"):
+    if variant not in ("imex1", "imex2", "im", "ex", "linoss_im", "linoss_imex"):
         raise ValueError(f"Unknown D-LinOSS variant '{variant}'.")
+    if variant.startswith("linoss"):
+        g_diag = None
+    elif g_diag is None:
+        raise ValueError("the damped variants need g_diag")
     if u.dim() != 3:
         raise ValueError("inputs must have shape (batch, length, hidden_dim).")
     if not u.is_cuda or u.dtype != torch.float32:
@@ -137,7 +145,9 @@ def dlinoss_layer(variant: str, a_diag: Tensor, g_diag: Tensor, step: Tensor, B:
         B = pad(B, (0, 0, 0, pad_h, 0, pad_p))
         C = pad(C, (0, 0, 0, pad_p, 0, pad_h))
         D = pad(D, (0, pad_h))
-        a_diag, g_diag = pad(a_diag, (0, pad_p)), pad(g_diag, (0, pad_p))
+        a_diag = pad(a_diag, (0, pad_p))
+        g_diag = pad(g_diag, (0, pad_p)) if g_diag is not None else None
         step = pad(step, (0, pad_p), value=0.5)
-    y = DLinossLayerFn.apply(variant, a_diag.contiguous(), g_diag.contiguous(), step.contiguous(), B, C, D, u)
+    y = DLinossLayerFn.apply(variant, a_diag.contiguous(), g_diag.contiguous() if g_diag is not None else None,
+                             step.contiguous(), B, C, D, u)
     return y[..., :hidden] if pad_h else y

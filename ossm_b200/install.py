@@ -125,8 +125,50 @@ def _wrap_mixer_forward(original):
     return forward
 
 
-def install_as_ossm_kernels(patch_ops: bool = True, fuse_mixer: bool = False) -> None:
-    """``fuse_mixer=True`` also replaces ``_MambaMixer.forward`` (the class, its parameters and its state dict
+def _layer_covered(self, inputs) -> bool:
+    """What the fused layer body takes: a float32 / bfloat16 / float16 CUDA batch of non-empty sequences, float32
+    parameters on the same device, no autocast region (ossm's matmuls would then run in the autocast dtype)."""
+    return bool(torch.is_tensor(inputs) and inputs.is_cuda and inputs.dim() == 3 and inputs.numel() > 0
+                and inputs.dtype in (torch.float32, torch.bfloat16, torch.float16)
+                and inputs.size(-1) == self.hidden_dim and self.B.is_cuda and self.B.dtype == torch.float32
+                and not torch.is_autocast_enabled())
+
+
+def _wrap_dlinoss_layer_forward(original):
+    def forward(self, inputs):
+        if _layer_covered(self, inputs):
+            from .dlinoss_layer import dlinoss_layer
+
+            # the class's own parameter projection (dlinoss.py:252-267), then the fused body (dlinoss.py:217-247)
+            a_diag, g_diag, step = self._project_parameters(device=inputs.device, dtype=torch.float32)
+            y = dlinoss_layer(self.variant, a_diag, g_diag, step, self.B, self.C, self.D, inputs.float())
+            return y.to(inputs.dtype)
+        return original(self, inputs)
+
+    forward.__wrapped__ = original
+    return forward
+
+
+def _wrap_linoss_layer_forward(original):
+    def forward(self, inputs):
+        if _layer_covered(self, inputs) and inputs.dtype == torch.float32 and self.discretization in ("IM", "IMEX"):
+            from .dlinoss_layer import dlinoss_layer
+
+            # linoss.py:213-214 (parameter projection) and :216-243 (the body)
+            a_diag, step = torch.relu(self.A_diag), torch.sigmoid(self.steps)
+            return dlinoss_layer("linoss_im" if self.discretization == "IM" else "linoss_imex", a_diag, None, step,
+                                 self.B, self.C, self.D, inputs)
+        return original(self, inputs)
+
+    forward.__wrapped__ = original
+    return forward
+
+
+def install_as_ossm_kernels(patch_ops: bool = True, fuse_mixer: bool = False, fuse_layer: bool = False) -> None:
+    """``fuse_layer=True`` replaces ``DampedLinOSSLayer.forward`` and ``LinOSSLayer.forward`` (the classes, their
+    parameters and state dicts stay ossm's) by :func:`ossm_b200.dlinoss_layer.dlinoss_layer`: the four GEMMs on the
+    tcgen05 tensor cores with the permutes and the ``D*u`` term inside them, around this package's scan.
+    ``fuse_mixer=True`` also replaces ``_MambaMixer.forward`` (the class, its parameters and its state dict
     stay ossm's) by :func:`ossm_b200.mixer.mamba_mixer_forward`: causal conv1d + SiLU in one kernel and
     ``softplus(dt_proj(.))`` folded into the scan (``mambarec.py:143-171``); inputs outside the library's scope
     keep ossm's own forward."""
@@ -183,6 +225,13 @@ def install_as_ossm_kernels(patch_ops: bool = True, fuse_mixer: bool = False) ->
             original = getattr(mods[name], attr)
             original = getattr(original, "__wrapped__", original)
             setattr(mods[name], attr, _wrap_diag_fn(diag.DiagScanFn, original))
+    if fuse_layer:
+        if "dlinoss" in mods:
+            cls = mods["dlinoss"].DampedLinOSSLayer
+            cls.forward = _wrap_dlinoss_layer_forward(getattr(cls.forward, "__wrapped__", cls.forward))
+        if "linoss" in mods:
+            cls = mods["linoss"].LinOSSLayer
+            cls.forward = _wrap_linoss_layer_forward(getattr(cls.forward, "__wrapped__", cls.forward))
     if fuse_mixer and "mambarec" in mods:
         cls = mods["mambarec"]._MambaMixer
         original = getattr(cls.forward, "__wrapped__", cls.forward)

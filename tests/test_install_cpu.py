@@ -42,8 +42,11 @@ CHILD = textwrap.dedent('''
     before = [m(x).detach() for m, x in cases]
     from ossm_b200.install import install_as_ossm_kernels
     import ossm_b200.kernels as K
-    install_as_ossm_kernels()
-    install_as_ossm_kernels()                           # twice: wrappers must not nest
+    install_as_ossm_kernels(fuse_layer=True, fuse_mixer=True)
+    install_as_ossm_kernels(fuse_layer=True, fuse_mixer=True)     # twice: wrappers must not nest
+    for cls in (dlinoss.DampedLinOSSLayer, linoss.LinOSSLayer, mambarec._MambaMixer):
+        assert cls.forward.__wrapped__.__module__.startswith("ossm.models"), cls
+        assert not hasattr(cls.forward.__wrapped__, "__wrapped__"), cls
     from ossm.models import _dlinoss_scan, _sdlinoss_scan, _selective_scan, s5
     assert sys.modules["ossm._kernels"] is K
     assert dlinoss.run_dlinoss is _dlinoss_scan.run_dlinoss

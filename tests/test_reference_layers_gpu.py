@@ -31,10 +31,11 @@ pytestmark = pytest.mark.gpu
 CHILD = textwrap.dedent('''
     import copy, json, sys
     import torch
-    patch_ops = sys.argv[1] == "1"
+    patch_ops = sys.argv[1] in ("1", "2")
+    fuse_layer = sys.argv[1] == "2"
     which = sys.argv[2]
     from ossm_b200.install import install_as_ossm_kernels
-    install_as_ossm_kernels(patch_ops=patch_ops)
+    install_as_ossm_kernels(patch_ops=patch_ops, fuse_layer=fuse_layer)
     import ossm
     from ossm.models import dlinoss, linoss, lru, mambarec, sdlinoss, _dlinoss_scan
     import ossm_b200.kernels as K
@@ -51,7 +52,7 @@ CHILD = textwrap.dedent('''
         return wrapper
     for name in ("lti_scan_forward", "lti_scan_backward", "linoss_scan", "linoss_scan_backward", "selective_scan_fwd",
                  "selective_scan_bwd", "sdlinoss_scan_forward", "sdlinoss_scan_backward", "diag_scan_forward",
-                 "diag_scan_backward"):
+                 "diag_scan_backward", "gemm_tf32x3"):
         setattr(K, name, counted(name))
 
     def make(kind):
@@ -96,6 +97,8 @@ CHILD = textwrap.dedent('''
         calls.clear()
         y, g = run(module.cuda(), x.cuda())                        # CUDA float32: this library
         assert calls, f"{kind}: no kernel of the library was called"
+        if fuse_layer and kind.split("_")[0] in ("dlinoss", "linoss"):
+            assert calls.get("gemm_tf32x3", 0) >= 4, (kind, calls)      # the projections ran on the tensor cores
         errs = {"output": rel(y, y_ref)}
         assert set(g) == set(g_ref), (sorted(g), sorted(g_ref))
         for n in g_ref:
@@ -111,6 +114,20 @@ CHILD = textwrap.dedent('''
 
 KINDS = ["dlinoss_imex1,dlinoss_imex2,dlinoss_im,dlinoss_ex", "linoss_IM,linoss_IMEX", "mamba_16,mamba_256",
          "sdlinoss,lru"]
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("kinds", KINDS[:2])
+def test_fused_layer_body_behind_unmodified_classes(kinds):
+    """``install_as_ossm_kernels(fuse_layer=True)``: ossm's ``DampedLinOSSLayer`` / ``LinOSSLayer`` objects, their
+    parameters untouched, with the layer body (projections on the tensor cores around the scan) of this package."""
+    src = reference_src()
+    if src is None:
+        pytest.skip("no ossm package (checkout or oracle/_ref/pkg)")
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([ROOT, src, env.get("PYTHONPATH", "")])
+    res = subprocess.run([sys.executable, "-c", CHILD, "2", kinds], capture_output=True, text=True, env=env, timeout=580)
+    assert res.returncode == 0 and "REPORT " in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
 
 @pytest.mark.timeout(600)
