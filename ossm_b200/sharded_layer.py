@@ -12,11 +12,11 @@ The time axis is cut into ``chunks`` pieces for the output projection: the reduc
 GEMM writes each piece directly as one plane per destination rank, so nothing is repacked or cloned
 before the collective.
 
-Backward: the gradient of the shard is all-gathered (the transpose of the reduce-scatter), every rank
+Backward: the gradient of the shard is all-gathered (the transpose of the reduce-scatter) in the same
+time pieces, the gather of piece ``k+1`` running beside the two GEMMs of piece ``k``; every rank
 computes ``grad_x_r``, runs its scan backward and the local weight gradients; the gradient of the
-replicated input is the sum over ranks of ``grad_bu_r B_r`` (one all-reduce, started before the
-weight gradient of ``B`` so that it runs beside it) plus the ranks' disjoint ``grad_y D`` slices (an
-all-gather).
+replicated input is one all-reduce, started before the weight gradient of ``B`` so that it runs
+beside it: every rank contributes ``grad_bu_r B_r`` plus, on its own hidden columns, ``grad_y D``.
 
 The math of one shard is the body of ``DampedLinOSSLayer.forward``
 (``src/ossm/models/dlinoss.py:217-247``); the reference has no distributed code, the oracle is the
@@ -31,7 +31,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-__all__ = ["sharded_dlinoss_layer", "CopyToShards", "OwnColumns", "hidden_shard"]
+__all__ = ["sharded_dlinoss_layer", "CopyToShards", "hidden_shard"]
 
 
 def _world(group) -> int:
@@ -72,26 +72,31 @@ def _torch_project(a2d: Tensor, w: Tensor) -> Tensor:
     return a2d @ w.t()
 
 
-class OwnColumns(torch.autograd.Function):
-    """``u[..., hidden_shard(H)]`` of a replicated ``u [B, L, H]``; the gradient on ``u`` is the ranks' slices
-    gathered (each rank contributes only its own columns, so an all-gather replaces a sum)."""
+class _SkipTerm(torch.autograd.Function):
+    """``y + u[..., cols] * D`` on the rank's own hidden columns.  The gradient of this term on the replicated ``u``
+    is not returned here: it is left in ``box`` for :class:`_ProjectIn`, whose backward adds it to the rank's
+    columns of ``grad_u`` before the all-reduce it starts anyway (each rank contributes its own columns once, so
+    the sum over ranks assembles the whole term without a second collective)."""
 
     @staticmethod
-    def forward(ctx, u: Tensor, group) -> Tensor:
-        ctx.group = group
-        ctx.hidden = u.size(-1)
-        return u[..., hidden_shard(u.size(-1), group)]
+    def forward(ctx, y: Tensor, u: Tensor, D: Tensor, cols: slice, box: dict) -> Tensor:
+        u_own = u[..., cols]
+        ctx.save_for_backward(u_own, D)
+        ctx.box = box
+        return y + u_own * D
 
     @staticmethod
     def backward(ctx, grad: Tensor):
-        world = _world(ctx.group)
+        u_own, D = ctx.saved_tensors
         grad = grad.contiguous()
-        if world == 1:
-            return grad, None
-        batch, length, hs = grad.shape
-        gathered = torch.empty((world, batch, length, hs), dtype=grad.dtype, device=grad.device)
-        dist.all_gather_into_tensor(gathered.view(world * batch, length, hs), grad, group=ctx.group)
-        return gathered.permute(1, 2, 0, 3).reshape(batch, length, ctx.hidden), None
+        if grad.is_cuda and grad.size(-1) % 4 == 0:
+            from . import kernels
+
+            grad_D = kernels.colwise_dot(grad.view(-1, grad.size(-1)), u_own.contiguous().view(-1, grad.size(-1)))
+        else:
+            grad_D = (grad * u_own).sum(dim=(0, 1))
+        ctx.box["skip"] = grad * D
+        return grad, None, grad_D, None, None
 
 
 class _ProjectIn(torch.autograd.Function):
@@ -100,8 +105,8 @@ class _ProjectIn(torch.autograd.Function):
     runs beside it."""
 
     @staticmethod
-    def forward(ctx, u: Tensor, w_in: Tensor, use_kernels: bool, group) -> Tensor:
-        ctx.group = group
+    def forward(ctx, u: Tensor, w_in: Tensor, use_kernels: bool, group, box: Optional[dict], cols) -> Tensor:
+        ctx.group, ctx.box, ctx.cols = group, box, cols
         batch, length, hidden = u.shape
         p2 = w_in.size(0)
         u2 = u.contiguous().view(batch * length, hidden)
@@ -134,6 +139,8 @@ class _ProjectIn(torch.autograd.Function):
                                 length=length)
         else:
             grad_u = (g.permute(1, 0, 2).reshape(batch * length, p2) @ w_in).view(batch, length, hidden)
+        if ctx.box is not None and ctx.box.get("skip") is not None:
+            grad_u[..., ctx.cols] += ctx.box.pop("skip")        # the D*u term of this rank's output columns
         work = None
         if _world(ctx.group) > 1:
             work = dist.all_reduce(grad_u, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
@@ -145,7 +152,7 @@ class _ProjectIn(torch.autograd.Function):
             grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
         if work is not None:
             work.wait()
-        return grad_u, grad_w, None, None
+        return grad_u, grad_w, None, None, None, None
 
 
 class _ProjectOutReduce(torch.autograd.Function):
@@ -195,7 +202,7 @@ class _ProjectOutReduce(torch.autograd.Function):
         for work, mine, _part, l0, l1 in pending:
             work.wait()
             out[:, l0:l1].copy_(mine)
-        ctx.group, ctx.scatter, ctx.use_kernels = group, scatter, use_kernels
+        ctx.group, ctx.scatter, ctx.use_kernels, ctx.chunks = group, scatter, use_kernels, chunks
         ctx.save_for_backward(xr, w_out)
         return out
 
@@ -205,28 +212,45 @@ class _ProjectOutReduce(torch.autograd.Function):
         length, batch, p2 = xr.shape
         hidden = w_out.size(0)
         group, world = ctx.group, _world(ctx.group)
-        gy = grad_out.contiguous()
-        if ctx.scatter and world > 1:
-            gathered = torch.empty((world,) + tuple(gy.shape), dtype=gy.dtype, device=gy.device)
-            dist.all_gather_into_tensor(gathered.view(world * gy.size(0), *gy.shape[1:]), gy, group=group)
-            gy = gathered.permute(1, 2, 0, 3).reshape(batch, length, hidden)   # [B, L, H] again
-        gy2 = gy.reshape(batch * length, hidden)
+        gathering = ctx.scatter and world > 1
+        gy = grad_out.contiguous()                              # [B, L, H / world] or [B, L, H]
+        grad_x = torch.empty((length, batch, p2 // 2), dtype=torch.complex64, device=xr.device)
+        gxr = torch.view_as_real(grad_x).view(length, batch, p2)
         if ctx.use_kernels:
             from . import kernels
-
-            grad_x = torch.empty((length, batch, p2 // 2), dtype=torch.complex64, device=xr.device)
-            kernels.gemm_tf32x3(gy2, *kernels.split_tf32(w_out.t().contiguous()),
-                                torch.view_as_real(grad_x).view(length * batch, p2),
-                                row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=length)
-        else:
-            flat = (gy2 @ w_out).view(batch, length, p2 // 2, 2).permute(1, 0, 2, 3).contiguous()
-            grad_x = torch.view_as_complex(flat)
-        if ctx.use_kernels:
             from .dlinoss_layer import weight_gradient
 
-            grad_w = weight_gradient(gy2, False, xr.view(length * batch, p2), True, batch, length)
-        else:
-            grad_w = torch.bmm(gy2.view(batch, length, hidden).transpose(1, 2), xr.permute(1, 0, 2)).sum(0)
+            wt_hi, wt_lo = kernels.split_tf32(w_out.t().contiguous())
+        # the time axis in pieces, as in the forward: the all-gather of piece k+1 (NCCL, its own stream) runs while
+        # the two GEMMs of piece k (grad_x and the weight gradient) compute
+        chunks = max(1, min(int(ctx.chunks), length)) if gathering else 1
+        bounds = [(length * i) // chunks for i in range(chunks + 1)]
+        spans = [(l0, l1) for l0, l1 in zip(bounds[:-1], bounds[1:]) if l1 > l0]
+        pending = []
+        if gathering:
+            hs = gy.size(-1)
+            for l0, l1 in spans:
+                mine = gy[:, l0:l1].contiguous()
+                got = torch.empty((world, batch, l1 - l0, hs), dtype=gy.dtype, device=gy.device)
+                work = dist.all_gather_into_tensor(got.view(world * batch, l1 - l0, hs), mine, group=group, async_op=True)
+                pending.append((work, got, mine))
+        grad_w = None
+        for i, (l0, l1) in enumerate(spans):
+            lc = l1 - l0
+            if gathering:
+                work, got, _mine = pending[i]
+                work.wait()
+                piece = got.permute(1, 2, 0, 3).reshape(batch * lc, hidden)     # [B, lc, H] again, dense
+            else:
+                piece = gy.view(batch * length, hidden)
+            if ctx.use_kernels:
+                kernels.gemm_tf32x3(piece, wt_hi, wt_lo, gxr[l0:l1].view(lc * batch, p2),
+                                    row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=lc)
+                part = weight_gradient(piece, False, xr[l0:l1].reshape(lc * batch, p2), True, batch, lc)
+            else:
+                gxr[l0:l1].copy_((piece @ w_out).view(batch, lc, p2).permute(1, 0, 2))
+                part = torch.bmm(piece.view(batch, lc, hidden).transpose(1, 2), xr[l0:l1].permute(1, 0, 2)).sum(0)
+            grad_w = part if grad_w is None else grad_w + part
         return grad_x, grad_w, None, None, None, None
 
 
@@ -247,11 +271,13 @@ def sharded_dlinoss_layer(variant: str, a: Tensor, g: Tensor, step: Tensor, B: T
         use_kernels = u.is_cuda
     if scan is None:
         from .dlinoss import run_dlinoss as scan
-    bu = _ProjectIn.apply(u, pack_input_weights(B), use_kernels, group)               # [L, B, P_r]
+    box = {} if scatter_output else None
+    cols = hidden_shard(u.size(-1), group) if scatter_output else None
+    bu = _ProjectIn.apply(u, pack_input_weights(B), use_kernels, group, box, cols)    # [L, B, P_r]
     x = scan(variant, a, g, step, bu)
     y = _ProjectOutReduce.apply(x, pack_output_weights(C), group, chunks, scatter_output, use_kernels)
     if scatter_output:
         # each rank adds D*u on its own columns; the gradients of these terms on u are disjoint slices
-        return y + OwnColumns.apply(u, group) * D
+        return _SkipTerm.apply(y, u, D, cols, box)
     # replicated output and replicated D: every rank adds the whole term, so it stays outside the summed gradient
     return y + u * D
