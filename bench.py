@@ -76,6 +76,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--length", type=int, default=4096)
     ap.add_argument("--ssm", type=int, default=256, help="oscillators per GPU")
+    ap.add_argument("--side-state", type=int, default=0,
+                    help="state size of the selective-scan side workload (default 16, BASELINE config 3)")
     ap.add_argument("--side-length", type=int, default=0,
                     help="sequence length of the linoss / mamba side workloads (0 = the BASELINE config's own)")
     ap.add_argument("--e2e-steps", type=int, default=3)
@@ -384,7 +386,7 @@ def side_workload(name, args, dev):
                 f"causal conv1d(k=4) + bias + SiLU fwd+bwd, B={Bz} D={Dn} L={L}, float32, both output layouts",
                 "conv1d_silu_fwd_bwd_gelem_per_s")
     if name == "mamba":
-        Bz, Dn, L, N = (args.side_batch or 32), 2048, (args.side_length or 8192), 16
+        Bz, Dn, L, N = (args.side_batch or 32), 2048, (args.side_length or 8192), (args.side_state or 16)
         io = torch.bfloat16
         u = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
         z = torch.randn(Bz, Dn, L, generator=gen, device=dev).to(io)
@@ -399,7 +401,7 @@ def side_workload(name, args, dev):
                 lambda saved: kernels.selective_scan_bwd(go, u, delta, A, Bt.transpose(1, 2), Ct.transpose(1, 2), z,
                                                          saved[1], Dv),
                 Bz * Dn * L, 10, 18,
-                f"Mamba selective scan fwd+bwd, B={Bz} D={Dn} L={L} N={N}, bf16 I/O, fp32 state (BASELINE config 3)",
+                f"Mamba selective scan fwd+bwd, B={Bz} D={Dn} L={L} N={N}, bf16 I/O, fp32 state " + ("(BASELINE config 3)" if N == 16 else "(time-parallel kernels)"),
                 "selective_scan_fwd_bwd_gelem_per_s")
     raise ValueError(name)
 

@@ -343,6 +343,7 @@ struct Params {
   int cpw;             // channels per warp (<= kCI); smaller for small problems so the grid fills the GPU
   int state_tile;      // backward: states processed per pass over a chunk (even; >= N means a single pass)
   bool vec_ok;
+  bool bc_vec_ok;      // B / C rows may be read with 16-byte loads
 };
 
 // (A[d,2p], A[d,2p+1]) * log2(e); a missing odd partner gets 0 (decay 1, no forcing).
@@ -803,6 +804,12 @@ static int dispatch_items(bool backward, const Params& p, cudaStream_t stream) {
 
 namespace ossm_b200 {
 namespace sscan {
+#include "selective_scan_split.cuh"
+}  // namespace sscan
+}  // namespace ossm_b200
+
+namespace ossm_b200 {
+namespace sscan {
 
 // Serial-in-time kernels (selective_scan_serial.cuh) are used for the state sizes they are built for.
 static int g_use_serial = 1;
@@ -894,6 +901,11 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
     p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm);
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_serial<float>(p, stream)
                                            : sscan::launch_fwd_serial<__nv_bfloat16>(p, stream);
+  }
+  if (sscan::g_use_serial && sscan::split_ok(N) && (!chunk_states || sscan::aligned16(chunk_states))) {
+    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && (L * es) % 16 == 0;
+    return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_split<float>(p, stream)
+                                           : sscan::launch_fwd_split<__nv_bfloat16>(p, stream);
   }
   return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::dispatch_items<float>(false, p, stream)
                                          : sscan::dispatch_items<__nv_bfloat16>(false, p, stream);
