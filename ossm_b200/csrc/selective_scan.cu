@@ -815,7 +815,11 @@ namespace sscan {
 static int g_use_serial = 1;
 static bool serial_ok(long long N) { return g_use_serial && N == 16; }
 // Steps between the states the forward saves for the backward.
-static int state_interval_for(long long N) { return serial_ok(N) ? kSerialInterval : 32 * items_bwd(N); }
+static int state_interval_for(long long N) {
+  if (serial_ok(N)) return kSerialInterval;
+  if (g_use_serial && split_bwd_ok(N)) return kSplitChunk;
+  return 32 * items_bwd(N);
+}
 
 // Channels per warp: the most that still gives one CTA per SM.
 static int pick_cpw(long long B, long long D) {
@@ -902,7 +906,11 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_serial<float>(p, stream)
                                            : sscan::launch_fwd_serial<__nv_bfloat16>(p, stream);
   }
-  if (sscan::g_use_serial && sscan::split_ok(N) && (!chunk_states || sscan::aligned16(chunk_states))) {
+  if (sscan::g_use_serial && sscan::split_ok(N)) {
+    if (!sscan::aligned16(chunk_states)) {
+      set_last_error("selective_scan_forward: chunk_states must be 16-byte aligned");
+      return kErrInvalidArgument;
+    }
     p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && (L * es) % 16 == 0;
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_split<float>(p, stream)
                                            : sscan::launch_fwd_split<__nv_bfloat16>(p, stream);
@@ -966,6 +974,15 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
     p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(dB) && sscan::aligned16(dC);
     rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_serial<float>(p, stream)
                                          : sscan::launch_bwd_serial<__nv_bfloat16>(p, stream);
+  } else if (sscan::g_use_serial && sscan::split_bwd_ok(N)) {
+    if (!sscan::aligned16(chunk_states)) {
+      set_last_error("selective_scan_backward: chunk_states must be 16-byte aligned");
+      return kErrInvalidArgument;
+    }
+    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(dB) && sscan::aligned16(dC) &&
+                  (L * es) % 16 == 0 && (L * 4) % 16 == 0;
+    rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_split<float>(p, stream)
+                                         : sscan::launch_bwd_split<__nv_bfloat16>(p, stream);
   } else {
     rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::dispatch_items<float>(true, p, stream)
                                          : sscan::dispatch_items<__nv_bfloat16>(true, p, stream);
