@@ -128,10 +128,7 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
 }
 
 static bool split_ok(long long N) { return N == 32 || N == 64 || N == 128 || N == 256; }
-// The backward below pays 16 shared-memory atomics per lane and step for the sums of dB_t, dC_t over the channels;
-// it beats the time-parallel backward only where a warp holds a single channel (measured at B=8, D=2048, L=8192:
-// 204 against 265 ms at 256 states, 141 against 70 ms at 64).
-static bool split_bwd_ok(long long N) { return N == 256; }
+static bool split_bwd_ok(long long N) { return split_ok(N); }
 
 template <typename IO>
 static int launch_fwd_split(const Params& p, cudaStream_t stream) {
@@ -159,10 +156,12 @@ static int launch_fwd_split(const Params& p, cudaStream_t stream) {
 //            registers, then the adjoint  g_t = C_t gy_t + a_{t+1} g_{t+1}  forming du, ddt, dz (sums over the states:
 //            one exchange between the lanes of a channel per window, eight steps at a time), dA, dD (register
 //            accumulators over the whole sequence) and dB_t[n] = g_t dt_t u_t, dC_t[n] = gy_t h_t (sums over the
-//            channels): every lane adds its 16 values of a step into a per-window tile in shared memory
-//            (red.shared, conflict-free slots), and after the window the CTA adds the tile -- the sum over its
-//            256 / S channels -- to global memory with one 16-byte vector atomic per (n, 4 steps).
-// Shared memory: B|C chunk tile in the I/O type [32][2N] | window sums float [8][2N] | window-entry states [3][8][256].
+//            channels): every lane stores its 16 values of a step into its warp's private slice of a half-window
+//            buffer (conflict-free, no atomics); after every four steps the CTA sums the slices -- over its 8 warps
+//            and the 32 / S channels of each -- and adds the result to global memory with one 16-byte vector atomic
+//            per (n, 4 steps).
+// Shared memory: B|C chunk tile in the I/O type [32][2N] | partial sums float [8 warps][4 steps][16][32] |
+// window-entry states [3][8][256].
 constexpr int kSplitChunk = 32;
 constexpr int kSplitWindows = kSplitChunk / kSplitGroup;
 
@@ -174,8 +173,8 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
   const int N = (int)p.N;
   const int S = N / kSplitStates;
   IO* bc = reinterpret_cast<IO*>(split_smem);
-  float* accum = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));
-  float* wstate = accum + G * 2 * N;
+  float* part = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));
+  float* wstate = part + kSplitWarps * 4 * 16 * 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % S;
   const int per_warp = 32 / S;
@@ -221,16 +220,35 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
       }
     }
   };
-  auto lane_sum = [&](float v) {
-    for (int m = 1; m < S; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-    return v;
+  // sums of one half window (steps 4*hq .. 4*hq+3 of the window at t0) over the CTA's channels, added to dB / dC
+  auto flush_half = [&](int hq, long long t0) {
+    const int per_warp_ch = 32 / S;
+    for (int i = threadIdx.x; i < 2 * N; i += kSplitThreads) {
+      const int is_c = i / N, r = i - is_c * N;
+      const int k = r / S, sb = r - k * S;
+      const int v = is_c * 8 + k;
+      float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int w = 0; w < kSplitWarps; ++w) {
+        for (int cw = 0; cw < per_warp_ch; ++cw) {
+          const float* src = part + (size_t)((w * 4) * 16 + v) * 32 + cw * S + sb;
+          s4.x += src[0]; s4.y += src[16 * 32]; s4.z += src[2 * 16 * 32]; s4.w += src[3 * 16 * 32];
+        }
+      }
+      const int n = sb * kSplitStates + k;
+      float* dst = (is_c ? p.dC : p.dB) + (b * N + n) * p.L + t0 + 4 * hq;
+      if (p.bc_vec_ok && t0 + G <= p.L) {
+        red_add_v4(dst, s4);
+      } else {
+        const float vals[4] = {s4.x, s4.y, s4.z, s4.w};
+        for (int kk = 0; kk < 4; ++kk)
+          if (t0 + 4 * hq + kk < p.L) atomicAdd(dst + kk, vals[kk]);
+      }
+    }
   };
-
-  for (int i = threadIdx.x; i < G * 2 * N; i += kSplitThreads) accum[i] = 0.0f;
   const long long nchunks = (p.L + kSplitChunk - 1) / kSplitChunk;
   for (long long c = nchunks - 1; c >= 0; --c) {
     const long long t_c = c * kSplitChunk;
-    __syncthreads();                       // the previous chunk's tile has been consumed (and accum is clear)
+    __syncthreads();                       // the previous chunk's tile has been consumed
     {
       constexpr int kVec = 16 / (int)sizeof(IO);
       for (int i = threadIdx.x; i < 2 * N * (kSplitChunk / kVec); i += kSplitThreads) {
@@ -340,8 +358,12 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
         yv[j] = acc.x + acc.y;
       }
       if (z_row) {
+        for (int m = 1; m < S; m <<= 1) {          // eight independent exchanges per round
 #pragma unroll
-        for (int j = 0; j < G; ++j) yv[j] = fmaf(dskip, u_c[j], lane_sum(yv[j]));
+          for (int j = 0; j < G; ++j) yv[j] += __shfl_xor_sync(0xffffffffu, yv[j], m);
+        }
+#pragma unroll
+        for (int j = 0; j < G; ++j) yv[j] = fmaf(dskip, u_c[j], yv[j]);
       }
       // adjoint, right to left
       float du_v[G], ddt_v[G], dz_v[G], gyd_v[G];
@@ -359,7 +381,7 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
         }
         const float2 gy2 = splat(gy), dtv = splat(dt_c[j]), dtu = splat(dt_c[j] * u_c[j]);
         float2 gb = make_float2(0.f, 0.f), dd = make_float2(0.f, 0.f);
-        float* acc_b = accum + (size_t)j * 2 * N + sub;          // slot k * S + sub of state sub * 8 + k
+        float* pp = part + (size_t)((warp * 4 + (j & 3)) * 16) * 32 + lane;   // [warp][step of the half][value][lane]
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const float2 h_after = (j == G - 1) ? h[q] : hw[(j + 1) % G][q];
@@ -371,20 +393,32 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
           gb = p2fma(g, Bp[q], gb);
           const float2 dBv = p2mul(g, dtu);
           ag[q] = p2mul(a[j][q], g);
-          atomicAdd(acc_b + (2 * q) * S, dBv.x);
-          atomicAdd(acc_b + (2 * q + 1) * S, dBv.y);
-          atomicAdd(acc_b + N + (2 * q) * S, dCv.x);
-          atomicAdd(acc_b + N + (2 * q + 1) * S, dCv.y);
+          pp[(2 * q) * 32] = dBv.x;
+          pp[(2 * q + 1) * 32] = dBv.y;
+          pp[(8 + 2 * q) * 32] = dCv.x;
+          pp[(8 + 2 * q + 1) * 32] = dCv.y;
         }
         du_v[j] = gb.x + gb.y;
         ddt_v[j] = (dd.x + dd.y) * kLn2;                          // A2 carries log2(e)
         gyd_v[j] = gy * dskip;
         dDacc = fmaf(gy, u_c[j], dDacc);
+        if ((j & 3) == 0) {         // a half window is complete in every warp's slice
+          __syncthreads();
+          flush_half(j >> 2, t0);
+          __syncthreads();
+        }
+      }
+      for (int m = 1; m < S; m <<= 1) {            // sixteen independent exchanges per round
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          du_v[j] += __shfl_xor_sync(0xffffffffu, du_v[j], m);
+          ddt_v[j] += __shfl_xor_sync(0xffffffffu, ddt_v[j], m);
+        }
       }
 #pragma unroll
       for (int j = 0; j < G; ++j) {
-        const float sgb = lane_sum(du_v[j]);
-        const float sdd = lane_sum(ddt_v[j]);
+        const float sgb = du_v[j];
+        const float sdd = ddt_v[j];
         du_v[j] = fmaf(dt_c[j], sgb, gyd_v[j]);
         ddt_v[j] = fmaf(u_c[j], sgb, sdd);
         if constexpr (kStep) {     // gradient with respect to the raw step
@@ -397,29 +431,6 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
         store_items<float, G>(p.ddt + row, t0, p.L, p.vec_ok, ddt_v);
         if (z_row) store_items<IO, G>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dz_v);
       }
-      __syncthreads();            // every warp's sums of this window are in the tile
-      for (int i = threadIdx.x; i < 2 * N * 2; i += kSplitThreads) {
-        const int val = i % (2 * N), jq = i / (2 * N);
-        float4 s4;
-        s4.x = accum[(size_t)(4 * jq) * 2 * N + val];
-        s4.y = accum[(size_t)(4 * jq + 1) * 2 * N + val];
-        s4.z = accum[(size_t)(4 * jq + 2) * 2 * N + val];
-        s4.w = accum[(size_t)(4 * jq + 3) * 2 * N + val];
-        accum[(size_t)(4 * jq) * 2 * N + val] = 0.0f;
-        accum[(size_t)(4 * jq + 1) * 2 * N + val] = 0.0f;
-        accum[(size_t)(4 * jq + 2) * 2 * N + val] = 0.0f;
-        accum[(size_t)(4 * jq + 3) * 2 * N + val] = 0.0f;
-        const int slot = val % N, n = (slot % S) * kSplitStates + slot / S;
-        float* dst = (val >= N ? p.dC : p.dB) + (b * N + n) * p.L + t0 + 4 * jq;
-        if (p.bc_vec_ok && t0 + G <= p.L) {
-          red_add_v4(dst, s4);
-        } else {
-          const float vals[4] = {s4.x, s4.y, s4.z, s4.w};
-          for (int k = 0; k < 4; ++k)
-            if (t0 + 4 * jq + k < p.L) atomicAdd(dst + k, vals[k]);
-        }
-      }
-      __syncthreads();            // the tile is clear again
     }
   }
   if (active) {
@@ -438,7 +449,7 @@ template <typename IO>
 static int launch_bwd_split(const Params& p, cudaStream_t stream) {
   const int per_cta = kSplitWarps * (32 / (int)(p.N / kSplitStates));
   dim3 grid((unsigned)((p.D + per_cta - 1) / per_cta), (unsigned)p.B);
-  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)kSplitGroup * 2 * p.N * sizeof(float) +
+  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)kSplitWarps * 4 * 16 * 32 * sizeof(float) +
                       (size_t)(kSplitWindows - 1) * kSplitStates * kSplitThreads * sizeof(float);
   if (p.delta_bias || p.delta_softplus) {
     if (int rc = set_smem(sscan_backward_split_kernel<IO, true>, smem)) return rc;
