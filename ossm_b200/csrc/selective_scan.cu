@@ -841,6 +841,7 @@ int ossm_b200_selective_scan_chunk(int64_t N) { return sscan::state_interval_for
 
 int ossm_b200_selective_scan_set_tuning(const char* key, int value) {
   if (key != nullptr && !strcmp(key, "serial")) { sscan::g_use_serial = value != 0; return kOk; }
+  if (key != nullptr && !strcmp(key, "split_bwd_wide_from") && value > 0) { sscan::g_split_bwd_wide_from = value; return kOk; }
   if (key != nullptr && !strcmp(key, "bwd_split") && (value == 2 || value == 4)) { sscan::g_bwd_split = value; return kOk; }
   set_last_error("selective_scan_set_tuning: unknown key %s", key ? key : "(null)");
   return kErrInvalidArgument;

@@ -165,8 +165,12 @@ static int launch_fwd_split(const Params& p, cudaStream_t stream) {
 constexpr int kSplitChunk = 32;
 constexpr int kSplitWindows = kSplitChunk / kSplitGroup;
 
-template <typename IO, bool kStep>
-__global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(Params p) {
+// kBwdWarps: 8 (one CTA per SM) where a warp holds a single channel and the B|C tile is the larger cost, else 4 (two
+// CTAs per SM, whose barriers and phases overlap).
+template <typename IO, bool kStep, int kBwdWarps>
+__global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_split_kernel(Params p) {
+  constexpr int kSplitBwdWarps = kBwdWarps;
+  constexpr int kSplitBwdThreads = kBwdWarps * 32;
   constexpr int G = kSplitGroup;
   constexpr int NQ = kSplitStates / 2;
   extern __shared__ __align__(16) unsigned char split_smem[];
@@ -174,12 +178,12 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
   const int S = N / kSplitStates;
   IO* bc = reinterpret_cast<IO*>(split_smem);
   float* part = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));
-  float* wstate = part + kSplitWarps * 4 * 16 * 32;
+  float* wstate = part + kSplitBwdWarps * 4 * 16 * 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % S;
   const int per_warp = 32 / S;
   const long long b = blockIdx.y;
-  const long long dch = (long long)blockIdx.x * (kSplitWarps * per_warp) + warp * per_warp + lane / S;
+  const long long dch = (long long)blockIdx.x * (kSplitBwdWarps * per_warp) + warp * per_warp + lane / S;
   const bool active = dch < p.D;
   const long long d = active ? dch : 0;                  // idle groups shadow channel 0 with a zero upstream gradient
   const long long row = (b * p.D + d) * p.L;
@@ -223,12 +227,12 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
   // sums of one half window (steps 4*hq .. 4*hq+3 of the window at t0) over the CTA's channels, added to dB / dC
   auto flush_half = [&](int hq, long long t0) {
     const int per_warp_ch = 32 / S;
-    for (int i = threadIdx.x; i < 2 * N; i += kSplitThreads) {
+    for (int i = threadIdx.x; i < 2 * N; i += kSplitBwdThreads) {
       const int is_c = i / N, r = i - is_c * N;
       const int k = r / S, sb = r - k * S;
       const int v = is_c * 8 + k;
       float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int w = 0; w < kSplitWarps; ++w) {
+      for (int w = 0; w < kSplitBwdWarps; ++w) {
         for (int cw = 0; cw < per_warp_ch; ++cw) {
           const float* src = part + (size_t)((w * 4) * 16 + v) * 32 + cw * S + sb;
           s4.x += src[0]; s4.y += src[16 * 32]; s4.z += src[2 * 16 * 32]; s4.w += src[3 * 16 * 32];
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
     __syncthreads();                       // the previous chunk's tile has been consumed
     {
       constexpr int kVec = 16 / (int)sizeof(IO);
-      for (int i = threadIdx.x; i < 2 * N * (kSplitChunk / kVec); i += kSplitThreads) {
+      for (int i = threadIdx.x; i < 2 * N * (kSplitChunk / kVec); i += kSplitBwdThreads) {
         const int r = i % (2 * N), cv = i / (2 * N);
         const long long t = t_c + (long long)kVec * cv;
         const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
@@ -304,8 +308,8 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
         }
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
-          wstate[((w * kSplitStates) + 2 * q) * kSplitThreads + threadIdx.x] = h[q].x;
-          wstate[((w * kSplitStates) + 2 * q + 1) * kSplitThreads + threadIdx.x] = h[q].y;
+          wstate[((w * kSplitStates) + 2 * q) * kSplitBwdThreads + threadIdx.x] = h[q].x;
+          wstate[((w * kSplitStates) + 2 * q + 1) * kSplitBwdThreads + threadIdx.x] = h[q].y;
         }
       }
     }
@@ -334,8 +338,8 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
       } else {
 #pragma unroll
         for (int q = 0; q < NQ; ++q)
-          h[q] = make_float2(wstate[(((w - 1) * kSplitStates) + 2 * q) * kSplitThreads + threadIdx.x],
-                             wstate[(((w - 1) * kSplitStates) + 2 * q + 1) * kSplitThreads + threadIdx.x]);
+          h[q] = make_float2(wstate[(((w - 1) * kSplitStates) + 2 * q) * kSplitBwdThreads + threadIdx.x],
+                             wstate[(((w - 1) * kSplitStates) + 2 * q + 1) * kSplitBwdThreads + threadIdx.x]);
       }
       const IO* steps = bc + (size_t)(w * G) * 2 * N + sub * kSplitStates;
       // re-run of the window
@@ -445,18 +449,26 @@ __global__ void __launch_bounds__(kSplitThreads, 1) sscan_backward_split_kernel(
   }
 }
 
-template <typename IO>
-static int launch_bwd_split(const Params& p, cudaStream_t stream) {
-  const int per_cta = kSplitWarps * (32 / (int)(p.N / kSplitStates));
+template <typename IO, int kSplitBwdWarps>
+static int launch_bwd_split_w(const Params& p, cudaStream_t stream) {
+  constexpr int kSplitBwdThreads = kSplitBwdWarps * 32;
+  const int per_cta = kSplitBwdWarps * (32 / (int)(p.N / kSplitStates));
   dim3 grid((unsigned)((p.D + per_cta - 1) / per_cta), (unsigned)p.B);
-  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)kSplitWarps * 4 * 16 * 32 * sizeof(float) +
-                      (size_t)(kSplitWindows - 1) * kSplitStates * kSplitThreads * sizeof(float);
+  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)kSplitBwdWarps * 4 * 16 * 32 * sizeof(float) +
+                      (size_t)(kSplitWindows - 1) * kSplitStates * kSplitBwdThreads * sizeof(float);
   if (p.delta_bias || p.delta_softplus) {
-    if (int rc = set_smem(sscan_backward_split_kernel<IO, true>, smem)) return rc;
-    sscan_backward_split_kernel<IO, true><<<grid, kSplitThreads, smem, stream>>>(p);
+    if (int rc = set_smem(sscan_backward_split_kernel<IO, true, kSplitBwdWarps>, smem)) return rc;
+    sscan_backward_split_kernel<IO, true, kSplitBwdWarps><<<grid, kSplitBwdThreads, smem, stream>>>(p);
   } else {
-    if (int rc = set_smem(sscan_backward_split_kernel<IO, false>, smem)) return rc;
-    sscan_backward_split_kernel<IO, false><<<grid, kSplitThreads, smem, stream>>>(p);
+    if (int rc = set_smem(sscan_backward_split_kernel<IO, false, kSplitBwdWarps>, smem)) return rc;
+    sscan_backward_split_kernel<IO, false, kSplitBwdWarps><<<grid, kSplitBwdThreads, smem, stream>>>(p);
   }
   return check_cuda(cudaGetLastError(), "sscan_backward_split_kernel launch");
+}
+
+static int g_split_bwd_wide_from = 128;     // state sizes from which the backward uses 8-warp CTAs (measured)
+
+template <typename IO>
+static int launch_bwd_split(const Params& p, cudaStream_t stream) {
+  return p.N >= g_split_bwd_wide_from ? launch_bwd_split_w<IO, 8>(p, stream) : launch_bwd_split_w<IO, 4>(p, stream);
 }
