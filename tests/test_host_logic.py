@@ -99,10 +99,13 @@ def test_selective_scan_host_checks():
     with pytest.raises(RuntimeError, match="A must have shape"):
         kernels.selective_scan_fwd(u, u, torch.zeros(4, 16), Bm, Bm)
     assert kernels.selective_scan_chunk(16) == 8          # serial kernels: a saved state every 8 steps
-    assert kernels.selective_scan_chunk(32) == 64         # time-parallel kernels
+    assert kernels.selective_scan_chunk(32) == 32         # states split over lanes: a saved state every 32 steps
+    assert kernels.selective_scan_chunk(256) == 32
+    assert kernels.selective_scan_chunk(24) == 64         # no serial kernel for this size: time-parallel kernels
     kernels.set_selective_scan_tuning("serial", 0)
     try:
         assert kernels.selective_scan_chunk(16) == 128
+        assert kernels.selective_scan_chunk(32) == 64
     finally:
         kernels.set_selective_scan_tuning("serial", 1)
     with pytest.raises(RuntimeError, match="unknown key"):
