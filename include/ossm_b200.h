@@ -216,6 +216,10 @@ int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int
 /* grad_D of the layer (y = ... + D * u, dlinoss.py:247): partial[c, n] = sum over the rows of CTA c of
  * X[m, n] * Y[m, n] for dense float32 [rows, cols] matrices (cols a multiple of 4, 16-byte aligned).  `partial` has
  * ossm_b200_colwise_dot_partials(rows) rows of `cols` floats; the caller adds them (fixed order: deterministic). */
+/* Key "reserve_sms" (0 .. 64, default 0): SMs the persistent projection and weight-gradient kernels leave free, for a
+ * caller that runs a collective beside them (their CTAs fill an SM's shared memory).  Read at launch time; the workspace
+ * query and the launch of one weight gradient must see the same value. */
+int ossm_b200_layer_set_tuning(const char* key, int value);
 int ossm_b200_colwise_dot_partials(int64_t rows);
 int ossm_b200_colwise_dot(const float* X, const float* Y, float* partial, int64_t rows, int64_t cols,
                           ossm_b200_stream_t stream);

@@ -53,6 +53,7 @@ SIGNATURES = {
     "ossm_b200_wgrad_tf32x3_workspace_bytes": (c_size_t, [c_int64] * 4),
     "ossm_b200_wgrad_tf32x3": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t, POINTER(c_int)]
                                + [c_int64] * 4 + [c_void_p]),
+    "ossm_b200_layer_set_tuning": (c_int, [c_char_p, c_int]),
     "ossm_b200_colwise_dot_partials": (c_int, [c_int64]),
     "ossm_b200_colwise_dot": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "ossm_b200_conv1d_silu_forward": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

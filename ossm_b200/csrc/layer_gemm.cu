@@ -48,6 +48,14 @@ constexpr int kATile = kBM * kPK * 4;   // 8 KiB
 
 enum RowMap : int { kRowIdentity = 0, kRowBatchToTime = 1, kRowTimeToBatch = 2 };
 
+// SMs the persistent kernels leave free (a caller that runs a collective beside them sets this: a CTA of these
+// kernels fills an SM's shared memory, so a library kernel launched meanwhile would otherwise wait for the whole grid).
+static int g_reserve_sms = 0;
+static int sm_budget() {
+  const int n = sm_count() - g_reserve_sms;
+  return n < 1 ? 1 : n;
+}
+
 struct GemmParams {
   float* out;            // [rows_out, ldo]
   const float* aux;      // nullable, same indexing as out
@@ -628,7 +636,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& th, const CUten
   const size_t smem = S::bytes(stages);
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN>), smem)) return rc;
   const long long ntiles = p.tiles_m * p.tiles_n;
-  const unsigned grid = (unsigned)(ntiles < (long long)sm_count() ? ntiles : (long long)sm_count());
+  const unsigned grid = (unsigned)(ntiles < (long long)sm_budget() ? ntiles : (long long)sm_budget());
   gemm_tf32x3_kernel<BN><<<grid, kThreads, smem, stream>>>(ta, th, tl, p);
   return check_cuda(cudaGetLastError(), "gemm_tf32x3_kernel launch");
 }
@@ -641,7 +649,8 @@ static int wgrad_splits(long long M, long long N, long long batch, long long len
   const long long bm = (long long)kBM * wgrad_row_tiles(M);
   const long long tiles = ((M + bm - 1) / bm) * ((N + BN - 1) / BN);
   const long long total = batch * ((length + kBK - 1) / kBK);
-  long long splits = (sm_count() + tiles - 1) / tiles;
+  long long splits = (sm_budget() + tiles - 1) / tiles;
+  if (splits * tiles > sm_budget() && splits > 1) --splits;     // never more CTAs than the budget
   if (splits > total) splits = total;
   if (splits > 512) splits = 512;
   return splits < 1 ? 1 : (int)splits;
@@ -678,6 +687,15 @@ int ossm_b200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count
 size_t ossm_b200_wgrad_tf32x3_workspace_bytes(int64_t M, int64_t N, int64_t batch, int64_t length) {
   if (M <= 0 || N <= 0 || batch <= 0 || length <= 0) return 0;
   return (size_t)layer::wgrad_splits(M, N, batch, length) * (size_t)M * (size_t)N * sizeof(float);
+}
+
+int ossm_b200_layer_set_tuning(const char* key, int value) {
+  if (key != nullptr && !strcmp(key, "reserve_sms") && value >= 0 && value <= 64) {
+    layer::g_reserve_sms = value;
+    return kOk;
+  }
+  set_last_error("layer_set_tuning: unknown key or value out of range");
+  return kErrInvalidArgument;
 }
 
 int ossm_b200_wgrad_tf32x3(const float* X, int x_time_major, const float* Y, int y_time_major, float* partial,

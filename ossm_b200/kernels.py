@@ -737,6 +737,24 @@ def wgrad_tf32x3(X: Tensor, x_time_major: bool, Y: Tensor, y_time_major: bool, b
     return partial[: splits.value * M * N].view(splits.value, M, N).sum(0)
 
 
+class reserved_sms:
+    """``with reserved_sms(16): ...``: the projection / weight-gradient kernels launched inside leave that many SMs free,
+    so that a collective launched meanwhile (NCCL on its own stream) finds room to run beside them."""
+
+    def __init__(self, count: int):
+        self.count = int(count)
+
+    def __enter__(self):
+        if self.count > 0:
+            _lib.check(_lib.load().ossm_b200_layer_set_tuning(b"reserve_sms", self.count), "layer_set_tuning")
+        return self
+
+    def __exit__(self, *exc):
+        if self.count > 0:
+            _lib.check(_lib.load().ossm_b200_layer_set_tuning(b"reserve_sms", 0), "layer_set_tuning")
+        return False
+
+
 def colwise_dot(X: Tensor, Y: Tensor) -> Tensor:
     """``out[n] = sum_m X[m, n] * Y[m, n]`` for dense float32 ``[rows, cols]`` CUDA matrices (``cols`` a multiple of 4):
     the layer's ``grad_D`` in one pass over both operands."""

@@ -34,6 +34,20 @@ from torch import Tensor
 __all__ = ["sharded_dlinoss_layer", "CopyToShards", "hidden_shard"]
 
 
+COMM_SMS = 16   # SMs the tensor-core kernels leave to NCCL while a collective runs beside them (several ranks only)
+
+
+def _reserve(group, use_kernels: bool):
+    """Context for the projection / weight-gradient launches that overlap a collective."""
+    if use_kernels and _world(group) > 1:
+        from . import kernels
+
+        return kernels.reserved_sms(COMM_SMS)
+    import contextlib
+
+    return contextlib.nullcontext()
+
+
 def _world(group) -> int:
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 
@@ -147,7 +161,8 @@ class _ProjectIn(torch.autograd.Function):
         if ctx.use_kernels:
             from .dlinoss_layer import weight_gradient
 
-            grad_w = weight_gradient(g.view(length * batch, p2), True, u2, False, batch, length)
+            with _reserve(ctx.group, True):
+                grad_w = weight_gradient(g.view(length * batch, p2), True, u2, False, batch, length)
         else:
             grad_w = torch.bmm(g.permute(1, 2, 0), u2.view(batch, length, hidden)).sum(0)
         if work is not None:
@@ -183,8 +198,9 @@ class _ProjectOutReduce(torch.autograd.Function):
             # one plane [B, lc, hs] per destination rank, written by the GEMM itself
             part = torch.empty((planes, batch, lc, hs), dtype=torch.float32, device=x.device)
             if use_kernels:
-                kernels.gemm_tf32x3(rows, w_hi, w_lo, part.view(planes, batch * lc, hs), row_map=kernels.ROWS_TIME_TO_BATCH,
-                                    batch=batch, length=lc, col_block=hs)
+                with _reserve(group, True):
+                    kernels.gemm_tf32x3(rows, w_hi, w_lo, part.view(planes, batch * lc, hs),
+                                        row_map=kernels.ROWS_TIME_TO_BATCH, batch=batch, length=lc, col_block=hs)
             else:
                 full = _torch_project(rows, w_out).view(lc, batch, planes, hs)
                 part.copy_(full.permute(2, 1, 0, 3))
@@ -244,9 +260,10 @@ class _ProjectOutReduce(torch.autograd.Function):
             else:
                 piece = gy.view(batch * length, hidden)
             if ctx.use_kernels:
-                kernels.gemm_tf32x3(piece, wt_hi, wt_lo, gxr[l0:l1].view(lc * batch, p2),
-                                    row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=lc)
-                part = weight_gradient(piece, False, xr[l0:l1].reshape(lc * batch, p2), True, batch, lc)
+                with _reserve(group, True):
+                    kernels.gemm_tf32x3(piece, wt_hi, wt_lo, gxr[l0:l1].view(lc * batch, p2),
+                                        row_map=kernels.ROWS_BATCH_TO_TIME, batch=batch, length=lc)
+                    part = weight_gradient(piece, False, xr[l0:l1].reshape(lc * batch, p2), True, batch, lc)
             else:
                 gxr[l0:l1].copy_((piece @ w_out).view(batch, lc, p2).permute(1, 0, 2))
                 part = torch.bmm(piece.view(batch, lc, hidden).transpose(1, 2), xr[l0:l1].permute(1, 0, 2)).sum(0)
