@@ -34,12 +34,13 @@ from torch import Tensor
 __all__ = ["sharded_dlinoss_layer", "CopyToShards", "hidden_shard"]
 
 
-COMM_SMS = 16   # SMs the tensor-core kernels leave to NCCL while a collective runs beside them (several ranks only)
+COMM_SMS = 0    # SMs the tensor-core kernels leave to NCCL while a collective runs beside them; 0 = none (measured on
+                # 2 GPUs: 16 / 32 reserved SMs slow the GEMMs by more than the collectives gain)
 
 
 def _reserve(group, use_kernels: bool):
     """Context for the projection / weight-gradient launches that overlap a collective."""
-    if use_kernels and _world(group) > 1:
+    if use_kernels and COMM_SMS > 0 and _world(group) > 1:
         from . import kernels
 
         return kernels.reserved_sms(COMM_SMS)
