@@ -65,8 +65,13 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
       const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
       float v[kVec];
       load_items<IO, kVec>(src, t, p.L, p.bc_vec_ok, v);
+      // state n = 8 * sub + 4 * half + e lives at ((half * S + sub) * 4 + e): a lane's two 16-byte reads of a step
+      // are then 16 bytes apart from its neighbours' (read straight as [sub][8] they are 32 bytes apart and
+      // conflict two ways: 41 % of the kernel's shared-memory wavefronts in the profile)
+      const int rr = r < N ? r : r - N;
+      const int pos = (r < N ? 0 : N) + ((((rr & 7) >> 2) * S + (rr >> 3)) << 2) + (rr & 3);
 #pragma unroll
-      for (int j = 0; j < kVec; ++j) split_tile[(kVec * cv + j) * 2 * N + r] = v[j];
+      for (int j = 0; j < kVec; ++j) split_tile[(kVec * cv + j) * 2 * N + pos] = v[j];
     }
     __syncthreads();
     const int groups = tile_steps / G;
@@ -86,13 +91,13 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
         for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
       }
       float y[G];
-      const float* steps = split_tile + (size_t)(gi * G) * 2 * N + sub * kSplitStates;
+      const float* steps = split_tile + (size_t)(gi * G) * 2 * N + sub * 4;
 #pragma unroll
       for (int j = 0; j < G; ++j) {
         const float4 b0 = *reinterpret_cast<const float4*>(steps + j * 2 * N);
-        const float4 b1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + 4);
+        const float4 b1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + 4 * S);
         const float4 c0 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N);
-        const float4 c1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N + 4);
+        const float4 c1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N + 4 * S);
         const float2 Bp[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
         const float2 Cp[4] = {make_float2(c0.x, c0.y), make_float2(c0.z, c0.w), make_float2(c1.x, c1.y), make_float2(c1.z, c1.w)};
         const float2 dtv = splat(dt_c[j]);
