@@ -308,7 +308,8 @@ int ossm_b200_selective_scan_chunk(int64_t N);
  * state sizes they cover (d_state 16), 0 the time-parallel kernels for every size; it changes the
  * value of ossm_b200_selective_scan_chunk(), so forward and backward of one scan must run under the
  * same setting.  Key "bwd_split" = 2 (default) or 4: lanes per channel in the serial backward of d_state 16.
- * Key "split_bwd_wide_from": state size from which the backward of d_state 32 .. 256 uses 8-warp CTAs. */
+ * Key "split_bwd_wide_from": state size from which the backward of d_state 32 .. 256 uses 8-warp CTAs.
+ * Key "split_flush_parts": threads sharing one item of that backward's dB / dC sums (0 = measured default by state size). */
 int ossm_b200_selective_scan_set_tuning(const char* key, int value);
 size_t ossm_b200_selective_scan_state_bytes(int64_t B, int64_t D, int64_t L, int64_t N);
 size_t ossm_b200_selective_scan_backward_workspace_bytes(int64_t B, int64_t D, int64_t L, int64_t N);

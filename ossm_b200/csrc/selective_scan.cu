@@ -344,6 +344,7 @@ struct Params {
   int state_tile;      // backward: states processed per pass over a chunk (even; >= N means a single pass)
   bool vec_ok;
   bool bc_vec_ok;      // B / C rows may be read with 16-byte loads
+  int split_flush_parts;   // split backward: threads per item of the dB / dC sums (0 = all the CTA has)
 };
 
 // (A[d,2p], A[d,2p+1]) * log2(e); a missing odd partner gets 0 (decay 1, no forcing).
@@ -842,6 +843,7 @@ int ossm_b200_selective_scan_chunk(int64_t N) { return sscan::state_interval_for
 int ossm_b200_selective_scan_set_tuning(const char* key, int value) {
   if (key != nullptr && !strcmp(key, "serial")) { sscan::g_use_serial = value != 0; return kOk; }
   if (key != nullptr && !strcmp(key, "split_bwd_wide_from") && value > 0) { sscan::g_split_bwd_wide_from = value; return kOk; }
+  if (key != nullptr && !strcmp(key, "split_flush_parts") && value >= 0) { sscan::g_split_flush_parts = value; return kOk; }
   if (key != nullptr && !strcmp(key, "bwd_split") && (value == 2 || value == 4)) { sscan::g_bwd_split = value; return kOk; }
   set_last_error("selective_scan_set_tuning: unknown key %s", key ? key : "(null)");
   return kErrInvalidArgument;

@@ -21,6 +21,51 @@ constexpr int kSplitStates = 8;                 // states per lane
 constexpr int kSplitGroup = 8;                  // steps per register group
 constexpr int kSplitTileFloats = 8192;          // floats per B|C tile: 4096 / N steps of 2 N values (32 KiB; 64 KiB is no faster)
 
+// Sums the eight per-step values v[0..7] over the S lanes of a channel (S = 4 .. 32, a power of two).  Each of the
+// first rounds halves the values a lane carries (the lane with the mask bit clear keeps the lower half and hands the
+// upper half over), so the exchange costs 4 + 2 + 1 (+ 1 per further round) shuffles instead of 8 per round.  On
+// return v[0] is the total of step `sub >> (lgS - 3)` (S >= 8; lanes that agree in those bits hold the same total),
+// resp. v[0], v[1] the totals of steps 2 sub, 2 sub + 1 (S = 4).
+__device__ __forceinline__ void group_reduce_scatter8(float (&v)[8], int S, int lane) {
+  int m = S >> 1;
+  {
+    const bool hi = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float send = hi ? v[i] : v[i + 4], keep = hi ? v[i + 4] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+    }
+    m >>= 1;
+  }
+  {
+    const bool hi = (lane & m) != 0;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float send = hi ? v[i] : v[i + 2], keep = hi ? v[i + 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+    }
+    m >>= 1;
+  }
+  if (m == 0) return;
+  {
+    const bool hi = (lane & m) != 0;
+    const float send = hi ? v[0] : v[1], keep = hi ? v[1] : v[0];
+    v[0] = keep + __shfl_xor_sync(0xffffffffu, send, m);
+    m >>= 1;
+  }
+  for (; m > 0; m >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], m);
+}
+// The steps of a window whose totals a lane holds after group_reduce_scatter8, and whether it is the lane that
+// stores them (the first of the lanes holding the same total).
+__device__ __forceinline__ void group_owned_steps(int S, int sub, int& first, int& count, bool& owner) {
+  if (S >= 8) {
+    const int lg = 31 - __clz(S);
+    first = sub >> (lg - 3); count = 1; owner = (sub & ((S >> 3) - 1)) == 0;
+  } else {
+    first = 2 * sub; count = 2; owner = true;
+  }
+}
+
 template <typename IO, bool kStep>
 __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Params p) {
   extern __shared__ __align__(16) float split_tile[];            // [steps][2 N]
@@ -54,13 +99,18 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
   const float dbias = (kStep && p.delta_bias) ? __ldg(p.delta_bias + d) : 0.0f;
   float* snaps = p.chunk_states ? p.chunk_states + (b * p.D + d) * p.nstates * p.N + sub * kSplitStates : nullptr;
 
+  int own_first, own_count;
+  bool own_lane;
+  group_owned_steps(S, sub, own_first, own_count, own_lane);
+  const int save_every = p.state_interval / G;                   // groups between saved states (the interval is a multiple of 8)
+  int until_save = 0;
   for (long long t_tile = 0; t_tile < p.L; t_tile += tile_steps) {
     __syncthreads();                       // the previous tile has been consumed
     // rows of B then C, one 16-byte vector of consecutive steps per item, transposed into [step][value]
     // (fetching the next tile into registers during the steps of this one was measured: no faster)
     constexpr int kVec = 16 / (int)sizeof(IO);
     for (int i = threadIdx.x; i < 2 * N * (tile_steps / kVec); i += kSplitThreads) {
-      const int r = i % (2 * N), cv = i / (2 * N);
+      const int r = i & (2 * N - 1), cv = i >> (32 - __clz(N));      // N is a power of two
       const long long t = t_tile + (long long)kVec * cv;
       const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
       float v[kVec];
@@ -78,11 +128,15 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
     for (int gi = 0; gi < groups; ++gi) {
       const long long t0 = t_tile + (long long)gi * G;
       if (t0 >= p.L) break;                // block-uniform
-      if (snaps && (t0 % p.state_interval) == 0 && active) {
-        float* dst = snaps + (t0 / p.state_interval) * p.N;
-        *reinterpret_cast<float4*>(dst) = make_float4(h[0].x, h[0].y, h[1].x, h[1].y);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(h[2].x, h[2].y, h[3].x, h[3].y);
+      if (until_save == 0) {               // a counter instead of 64-bit divisions of t0 in the step loop
+        until_save = save_every;
+        if (snaps && active) {
+          *reinterpret_cast<float4*>(snaps) = make_float4(h[0].x, h[0].y, h[1].x, h[1].y);
+          *reinterpret_cast<float4*>(snaps + 4) = make_float4(h[2].x, h[2].y, h[3].x, h[3].y);
+          snaps += p.N;
+        }
       }
+      --until_save;
       float u_c[G], dt_c[G];
       load_items<IO, G>(u_row, t0, p.L, p.vec_ok, u_c);
       load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
@@ -112,21 +166,21 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
         }
         y[j] = acc.x + acc.y;
       }
-      // sum over the lanes of the channel, eight steps at a time
-      for (int m = 1; m < S; m <<= 1) {
-#pragma unroll
-        for (int j = 0; j < G; ++j) y[j] += __shfl_xor_sync(0xffffffffu, y[j], m);
-      }
-      if (sub == 0 && active) {
-#pragma unroll
-        for (int j = 0; j < G; ++j) y[j] = fmaf(dskip, u_c[j], y[j]);
-        if (z_row) {
-          float zz[G];
-          load_items<IO, G>(z_row, t0, p.L, p.vec_ok, zz);
-#pragma unroll
-          for (int j = 0; j < G; ++j) y[j] *= zz[j] * sigmoidf(zz[j]);
+      // sum over the lanes of the channel, eight steps at a time; the totals end up spread over the lanes, each of
+      // which finishes and stores its own step (the owners of a window store 8 consecutive elements in one instruction)
+      group_reduce_scatter8(y, S, lane);
+      if (own_lane && active) {
+        for (int e = 0; e < own_count; ++e) {
+          const long long t = t0 + own_first + e;
+          if (t < p.L) {
+            float yy = fmaf(dskip, io_load<IO>(u_row + t), e == 0 ? y[0] : y[1]);
+            if (z_row) {
+              const float zz = io_load<IO>(z_row + t);
+              yy *= zz * sigmoidf(zz);
+            }
+            io_store<IO>(out_row + t, yy);
+          }
         }
-        store_items<IO, G>(out_row, t0, p.L, p.vec_ok, y);
       }
     }
   }
@@ -162,11 +216,12 @@ static int launch_fwd_split(const Params& p, cudaStream_t stream) {
 //            one exchange between the lanes of a channel per window, eight steps at a time), dA, dD (register
 //            accumulators over the whole sequence) and dB_t[n] = g_t dt_t u_t, dC_t[n] = gy_t h_t (sums over the
 //            channels): every lane stores its 16 values of a step into its warp's private slice of a half-window
-//            buffer (conflict-free, no atomics); after every four steps the CTA sums the slices -- over its 8 warps
-//            and the 32 / S channels of each -- and adds the result to global memory with one 16-byte vector atomic
-//            per (n, 4 steps).
-// Shared memory: B|C chunk tile in the I/O type [32][2N] | partial sums float [8 warps][4 steps][16][32] |
-// window-entry states [3][8][256].
+//            buffer (conflict-free, no atomics); after every four steps the CTA sums the slices -- over its warps
+//            and the 32 / S channels of each, with 16-byte loads, every thread a share of the rows -- and adds the
+//            result to global memory with 16-byte vector atomics per (n, 4 steps).  Two half-window buffers
+//            alternate, so one barrier per half window is enough.
+// Shared memory: B|C chunk tile in the I/O type [32][2N] | partial sums float [2][warps][4 steps][16][32] |
+// window-entry states [3][8][threads].
 constexpr int kSplitChunk = 32;
 constexpr int kSplitWindows = kSplitChunk / kSplitGroup;
 
@@ -182,13 +237,15 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   const int N = (int)p.N;
   const int S = N / kSplitStates;
   IO* bc = reinterpret_cast<IO*>(split_smem);
-  float* part = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));
-  float* wstate = part + kSplitBwdWarps * 4 * 16 * 32;
+  constexpr int kPartFloats = kSplitBwdWarps * 4 * 16 * 32;     // one half-window buffer
+  float* part = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));   // two of them
+  float* wstate = part + 2 * kPartFloats;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane % S;
-  const int per_warp = 32 / S;
+  const int lgN = 31 - __clz(N), lgS = lgN - 3;                 // N is a power of two
+  const int sub = lane & (S - 1);
+  const int per_warp = 32 >> lgS;
   const long long b = blockIdx.y;
-  const long long dch = (long long)blockIdx.x * (kSplitBwdWarps * per_warp) + warp * per_warp + lane / S;
+  const long long dch = (long long)blockIdx.x * (kSplitBwdWarps * per_warp) + warp * per_warp + (lane >> lgS);
   const bool active = dch < p.D;
   const long long d = active ? dch : 0;                  // idle groups shadow channel 0 with a zero upstream gradient
   const long long row = (b * p.D + d) * p.L;
@@ -211,6 +268,9 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   const float dskip = p.Dskip ? __ldg(p.Dskip + d) : 0.0f;
   const float dbias = (kStep && p.delta_bias) ? __ldg(p.delta_bias + d) : 0.0f;
   float dDacc = 0.0f, dBiasAcc = 0.0f;
+  int own_first, own_count;
+  bool own_lane;
+  group_owned_steps(S, sub, own_first, own_count, own_lane);
 
   // (state pairs of this lane) of B and C of one step of the tile
   auto load_bc8 = [&](const IO* stepp, float2 (&Bp)[NQ], float2 (&Cp)[NQ]) {
@@ -229,26 +289,45 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       }
     }
   };
-  // sums of one half window (steps 4*hq .. 4*hq+3 of the window at t0) over the CTA's channels, added to dB / dC
+  // sums of one half window (steps 4*hq .. 4*hq+3 of the window at t0, buffer hq) over the CTA's channels, added to
+  // dB / dC.  An item is (value v of 16, four consecutive lanes of a channel): a thread reads it with 16-byte loads from
+  // its share of the (warp, channel-of-the-warp) rows, for the four steps, and issues one vector atomic per lane of the
+  // four.  The rows are divided over `nparts` threads per item so that every thread of the CTA has work; the channel
+  // index is rotated by v so that the loads of a quarter-warp fall into distinct banks.
+  const int flush_items = 4 * S, lgI = lgS + 2;
+  const int flush_rows = kSplitBwdWarps * per_warp;
+  int nparts = kSplitBwdThreads >> lgI;
+  if (p.split_flush_parts > 0 && p.split_flush_parts < nparts) nparts = p.split_flush_parts;
+  const int rows_per_part = flush_rows / nparts;
   auto flush_half = [&](int hq, long long t0) {
-    const int per_warp_ch = 32 / S;
-    for (int i = threadIdx.x; i < 2 * N; i += kSplitBwdThreads) {
-      const int is_c = i / N, r = i - is_c * N;
-      const int k = r / S, sb = r - k * S;
-      const int v = is_c * 8 + k;
-      float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int w = 0; w < kSplitBwdWarps; ++w) {
-        for (int cw = 0; cw < per_warp_ch; ++cw) {
-          const float* src = part + (size_t)((w * 4) * 16 + v) * 32 + cw * S + sb;
-          s4.x += src[0]; s4.y += src[16 * 32]; s4.z += src[2 * 16 * 32]; s4.w += src[3 * 16 * 32];
-        }
-      }
-      const int n = sb * kSplitStates + k;
-      float* dst = (is_c ? p.dC : p.dB) + (b * N + n) * p.L + t0 + 4 * hq;
+    const int part_id = threadIdx.x >> lgI;
+    if (part_id >= nparts) return;
+    const int i = threadIdx.x & (flush_items - 1);
+    const int v = i >> (lgS - 2), s4 = i & ((S >> 2) - 1);
+    const float* pb = part + hq * kPartFloats + v * 32 + 4 * s4;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+    const int r0 = part_id * rows_per_part;
+#pragma unroll 4
+    for (int rr = r0; rr < r0 + rows_per_part; ++rr) {
+      const int w = rr >> (5 - lgS), cw = (rr ^ v) & (per_warp - 1);
+      const float4* src = reinterpret_cast<const float4*>(pb + (size_t)(w * 4 * 16) * 32 + cw * S);
+      const float4 x0 = src[0], x1 = src[16 * 32 / 4], x2 = src[2 * 16 * 32 / 4], x3 = src[3 * 16 * 32 / 4];
+      a0.x += x0.x; a0.y += x0.y; a0.z += x0.z; a0.w += x0.w;
+      a1.x += x1.x; a1.y += x1.y; a1.z += x1.z; a1.w += x1.w;
+      a2.x += x2.x; a2.y += x2.y; a2.z += x2.z; a2.w += x2.w;
+      a3.x += x3.x; a3.y += x3.y; a3.z += x3.z; a3.w += x3.w;
+    }
+    const int k = v & 7;
+    float* base = ((v >> 3) ? p.dC : p.dB) + (b * N + (4 * s4) * kSplitStates + k) * p.L + t0 + 4 * hq;
+    const float4 o[4] = {make_float4(a0.x, a1.x, a2.x, a3.x), make_float4(a0.y, a1.y, a2.y, a3.y),
+                         make_float4(a0.z, a1.z, a2.z, a3.z), make_float4(a0.w, a1.w, a2.w, a3.w)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float* dst = base + (long long)e * kSplitStates * p.L;     // state (4 s4 + e) * 8 + k
       if (p.bc_vec_ok && t0 + G <= p.L) {
-        red_add_v4(dst, s4);
+        red_add_v4(dst, o[e]);
       } else {
-        const float vals[4] = {s4.x, s4.y, s4.z, s4.w};
+        const float vals[4] = {o[e].x, o[e].y, o[e].z, o[e].w};
         for (int kk = 0; kk < 4; ++kk)
           if (t0 + 4 * hq + kk < p.L) atomicAdd(dst + kk, vals[kk]);
       }
@@ -261,7 +340,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
     {
       constexpr int kVec = 16 / (int)sizeof(IO);
       for (int i = threadIdx.x; i < 2 * N * (kSplitChunk / kVec); i += kSplitBwdThreads) {
-        const int r = i % (2 * N), cv = i / (2 * N);
+        const int r = i & (2 * N - 1), cv = i >> (lgN + 1);
         const long long t = t_c + (long long)kVec * cv;
         const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
         IO v[kVec];
@@ -366,31 +445,20 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
         }
         yv[j] = acc.x + acc.y;
       }
-      if (z_row) {
-        for (int m = 1; m < S; m <<= 1) {          // eight independent exchanges per round
-#pragma unroll
-          for (int j = 0; j < G; ++j) yv[j] += __shfl_xor_sync(0xffffffffu, yv[j], m);
-        }
-#pragma unroll
-        for (int j = 0; j < G; ++j) yv[j] = fmaf(dskip, u_c[j], yv[j]);
-      }
-      // adjoint, right to left
-      float du_v[G], ddt_v[G], dz_v[G], gyd_v[G];
+      // adjoint, right to left (the partial outputs yv are summed over the lanes after it, with du and ddt)
+      float du_v[G], ddt_v[G];
 #pragma unroll
       for (int j = G - 1; j >= 0; --j) {
         float2 Bp[NQ], Cp[NQ];
         load_bc8(steps + (size_t)j * 2 * N, Bp, Cp);
         float gy = go_c[j];
-        dz_v[j] = 0.0f;
         if (z_row) {
           const float zv = z_c[j];
-          const float sg = __fdividef(1.0f, 1.0f + ex2(-zv * kLog2e));
-          gy = go_c[j] * zv * sg;
-          dz_v[j] = go_c[j] * yv[j] * (sg * fmaf(zv, 1.0f - sg, 1.0f));
+          gy = go_c[j] * zv * __fdividef(1.0f, 1.0f + ex2(-zv * kLog2e));
         }
         const float2 gy2 = splat(gy), dtv = splat(dt_c[j]), dtu = splat(dt_c[j] * u_c[j]);
         float2 gb = make_float2(0.f, 0.f), dd = make_float2(0.f, 0.f);
-        float* pp = part + (size_t)((warp * 4 + (j & 3)) * 16) * 32 + lane;   // [warp][step of the half][value][lane]
+        float* pp = part + (j >> 2) * kPartFloats + (size_t)((warp * 4 + (j & 3)) * 16) * 32 + lane;   // [half][warp][step][value][lane]
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const float2 h_after = (j == G - 1) ? h[q] : hw[(j + 1) % G][q];
@@ -409,38 +477,48 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
         }
         du_v[j] = gb.x + gb.y;
         ddt_v[j] = (dd.x + dd.y) * kLn2;                          // A2 carries log2(e)
-        gyd_v[j] = gy * dskip;
         dDacc = fmaf(gy, u_c[j], dDacc);
-        if ((j & 3) == 0) {         // a half window is complete in every warp's slice
+        if ((j & 3) == 0) {
+          // the half window is complete in every warp's slice of buffer j >> 2; the other buffer, which the next four
+          // steps fill, was summed before this barrier, and this one is next written after the following barrier
           __syncthreads();
           flush_half(j >> 2, t0);
-          __syncthreads();
         }
       }
-      for (int m = 1; m < S; m <<= 1) {            // sixteen independent exchanges per round
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-          du_v[j] += __shfl_xor_sync(0xffffffffu, du_v[j], m);
-          ddt_v[j] += __shfl_xor_sync(0xffffffffu, ddt_v[j], m);
+      // sums over the states: the totals of the window's steps end up spread over the lanes of the channel, and the
+      // lane holding a step finishes du, ddt, dz of that step from the step's scalars and stores them
+      group_reduce_scatter8(du_v, S, lane);
+      group_reduce_scatter8(ddt_v, S, lane);
+      if (z_row) group_reduce_scatter8(yv, S, lane);
+      if (own_lane && active) {
+        for (int e = 0; e < own_count; ++e) {
+          const long long t = t0 + own_first + e;
+          if (t >= p.L) break;
+          const float sgb = e == 0 ? du_v[0] : du_v[1], sdd = e == 0 ? ddt_v[0] : ddt_v[1];
+          const float u_m = io_load<IO>(u_row + t), go_m = io_load<IO>(go_row + t);
+          float dt_m = __ldg(dt_row + t);
+          if constexpr (kStep) dt_m = step_transform(dt_m, dbias, p.delta_softplus != 0);
+          float gy = go_m;
+          if (z_row) {
+            const float zv = io_load<IO>(z_row + t);
+            const float sg = __fdividef(1.0f, 1.0f + ex2(-zv * kLog2e));
+            const float y_m = fmaf(dskip, u_m, e == 0 ? yv[0] : yv[1]);
+            gy = go_m * zv * sg;
+            io_store<IO>(static_cast<IO*>(p.dz) + row + t, go_m * y_m * (sg * fmaf(zv, 1.0f - sg, 1.0f)));
+          }
+          io_store<IO>(static_cast<IO*>(p.du) + row + t, fmaf(dt_m, sgb, gy * dskip));
+          float ddt_m = fmaf(u_m, sgb, sdd);
+          if constexpr (kStep) {     // gradient with respect to the raw step
+            ddt_m *= step_transform_grad(dt_m, p.delta_softplus != 0);
+            dBiasAcc += ddt_m;
+          }
+          p.ddt[row + t] = ddt_m;
         }
-      }
-#pragma unroll
-      for (int j = 0; j < G; ++j) {
-        const float sgb = du_v[j];
-        const float sdd = ddt_v[j];
-        du_v[j] = fmaf(dt_c[j], sgb, gyd_v[j]);
-        ddt_v[j] = fmaf(u_c[j], sgb, sdd);
-        if constexpr (kStep) {     // gradient with respect to the raw step
-          ddt_v[j] = (t0 + j < p.L) ? ddt_v[j] * step_transform_grad(dt_c[j], p.delta_softplus != 0) : 0.0f;
-          dBiasAcc += ddt_v[j];
-        }
-      }
-      if (sub == 0 && active) {
-        store_items<IO, G>(static_cast<IO*>(p.du) + row, t0, p.L, p.vec_ok, du_v);
-        store_items<float, G>(p.ddt + row, t0, p.L, p.vec_ok, ddt_v);
-        if (z_row) store_items<IO, G>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dz_v);
       }
     }
+  }
+  if (p.dbias_part) {                      // the steps of a channel were finished by different lanes
+    for (int m = 1; m < S; m <<= 1) dBiasAcc += __shfl_xor_sync(0xffffffffu, dBiasAcc, m);
   }
   if (active) {
 #pragma unroll
@@ -459,7 +537,7 @@ static int launch_bwd_split_w(const Params& p, cudaStream_t stream) {
   constexpr int kSplitBwdThreads = kSplitBwdWarps * 32;
   const int per_cta = kSplitBwdWarps * (32 / (int)(p.N / kSplitStates));
   dim3 grid((unsigned)((p.D + per_cta - 1) / per_cta), (unsigned)p.B);
-  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)kSplitBwdWarps * 4 * 16 * 32 * sizeof(float) +
+  const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)2 * kSplitBwdWarps * 4 * 16 * 32 * sizeof(float) +
                       (size_t)(kSplitWindows - 1) * kSplitStates * kSplitBwdThreads * sizeof(float);
   if (p.delta_bias || p.delta_softplus) {
     if (int rc = set_smem(sscan_backward_split_kernel<IO, true, kSplitBwdWarps>, smem)) return rc;
@@ -472,8 +550,12 @@ static int launch_bwd_split_w(const Params& p, cudaStream_t stream) {
 }
 
 static int g_split_bwd_wide_from = 128;     // state sizes from which the backward uses 8-warp CTAs (measured)
+static int g_split_flush_parts = 0;         // threads sharing the rows of one flush item; 0 = measured default by state size
 
 template <typename IO>
 static int launch_bwd_split(const Params& p, cudaStream_t stream) {
-  return p.N >= g_split_bwd_wide_from ? launch_bwd_split_w<IO, 8>(p, stream) : launch_bwd_split_w<IO, 4>(p, stream);
+  Params q = p;
+  // fewer threads per item mean fewer vector atomics: 32 / 64 states ran fastest with 2, 128 / 256 with 1
+  q.split_flush_parts = g_split_flush_parts > 0 ? g_split_flush_parts : (q.N >= 128 ? 1 : 2);
+  return q.N >= g_split_bwd_wide_from ? launch_bwd_split_w<IO, 8>(q, stream) : launch_bwd_split_w<IO, 4>(q, stream);
 }

@@ -291,7 +291,9 @@ _IO_DTYPES = {torch.float32: 0, torch.bfloat16: 1}
 def set_selective_scan_tuning(key: str, value: int) -> None:
     """``"serial"``: 1 (default) = serial-in-time kernels for the state sizes they cover (16; 32 / 64 / 128 / 256 with
     the states of a channel split over lanes), 0 = the time-parallel kernels for every size.  Forward and backward of
-    one scan must agree.  ``"split_bwd_wide_from"``: state size from which the split backward uses 8-warp CTAs."""
+    one scan must agree.  ``"split_bwd_wide_from"``: state size from which the split backward uses 8-warp CTAs.
+    ``"split_flush_parts"``: threads that share one item of the split backward's ``dB_t / dC_t`` sums (0 = the
+    measured default for the state size)."""
     _lib.check(_lib.load().ossm_b200_selective_scan_set_tuning(key.encode(), int(value)), "selective_scan_set_tuning")
 
 
