@@ -10,16 +10,61 @@
 // done for eight steps at a time after the recurrence of those steps (shuffles off the dependent path).
 //
 // A CTA is 8 warps = 256 / S channels of one batch element; B_t / C_t tiles of 4096 / N steps are transposed into
-// shared memory as float32 [step][B_0..B_{N-1} | C_0..C_{N-1}] and read back with 16-byte loads (the lanes of a
-// channel read consecutive 32-byte pieces).  u, dt, z arrive as one 8-step vector per row and group, the output leaves
-// the same way from the group's first lane.  The state entering every p.state_interval steps is saved in the
-// layout the time-parallel backward reads ([B, D, L / interval, N]).
+// shared memory as float32 [step][B | C][half][lane][4] and read back with 16-byte loads (neighbouring lanes 16 bytes
+// apart).  u, dt arrive as one 8-step vector per row and group; the lane that ends up with a step's output after the
+// exchange gates and stores it (staging u, dt, z one group ahead with asynchronous copies, as the backward does per
+// chunk, was measured 5-10 % slower here: three resident CTAs already cover that latency).  The state entering
+// every p.state_interval steps is saved in the layout the time-parallel backward reads ([B, D, L / interval, N]).
 
 constexpr int kSplitWarps = 8;
 constexpr int kSplitThreads = kSplitWarps * 32;
 constexpr int kSplitStates = 8;                 // states per lane
 constexpr int kSplitGroup = 8;                  // steps per register group
 constexpr int kSplitTileFloats = 8192;          // floats per B|C tile: 4096 / N steps of 2 N values (32 KiB; 64 KiB is no faster)
+
+// One 16-byte vector of a row, elements t .. t + 16 / elem_bytes - 1, into shared memory: an asynchronous copy where
+// the row is 16-byte aligned and the vector lies inside it, else element by element with zeros past the end.
+__device__ __forceinline__ void stage_vec(uint4* dst, const void* rowp, int elem_bytes, long long t, long long L,
+                                          bool vec_ok) {
+  const char* src = static_cast<const char*>(rowp) + t * elem_bytes;
+  const int per = 16 / elem_bytes;
+  if (vec_ok && t + per <= L) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+  } else {
+    uint4 tmp = make_uint4(0u, 0u, 0u, 0u);
+    char* tb = reinterpret_cast<char*>(&tmp);
+    for (int j = 0; j < per; ++j)
+      if (t + j < L)
+        for (int k = 0; k < elem_bytes; ++k) tb[j * elem_bytes + k] = src[j * elem_bytes + k];
+    *dst = tmp;
+  }
+}
+// eight consecutive elements of a staged row (two vectors of float32, one of a 16-bit type) as floats
+template <typename T>
+__device__ __forceinline__ void read_staged8(const uint4* src, float (&out)[8]) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      const uint4 r = src[v];
+      out[4 * v] = __uint_as_float(r.x); out[4 * v + 1] = __uint_as_float(r.y);
+      out[4 * v + 2] = __uint_as_float(r.z); out[4 * v + 3] = __uint_as_float(r.w);
+    }
+  } else {
+    const uint4 r = src[0];
+    const uint32_t wv[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[2 * j] = __uint_as_float(wv[j] << 16);
+      out[2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+    }
+  }
+}
+// element j of a staged row
+template <typename T>
+__device__ __forceinline__ float read_staged1(const uint4* src, int j) {
+  if constexpr (sizeof(T) == 4) return reinterpret_cast<const float*>(src)[j];
+  else return __uint_as_float((uint32_t) reinterpret_cast<const unsigned short*>(src)[j] << 16);
+}
 
 // Sums the eight per-step values v[0..7] over the S lanes of a channel (S = 4 .. 32, a power of two).  Each of the
 // first rounds halves the values a lane carries (the lane with the mask bit clear keeps the lower half and hands the
@@ -55,6 +100,12 @@ __device__ __forceinline__ void group_reduce_scatter8(float (&v)[8], int S, int 
   }
   for (; m > 0; m >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], m);
 }
+// a += x as two packed additions
+__device__ __forceinline__ void add4(float4& a, const float4& x) {
+  const float2 lo = p2add(make_float2(a.x, a.y), make_float2(x.x, x.y));
+  const float2 hi = p2add(make_float2(a.z, a.w), make_float2(x.z, x.w));
+  a = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
 // The steps of a window whose totals a lane holds after group_reduce_scatter8, and whether it is the lane that
 // stores them (the first of the lanes holding the same total).
 __device__ __forceinline__ void group_owned_steps(int S, int sub, int& first, int& count, bool& owner) {
@@ -67,7 +118,7 @@ __device__ __forceinline__ void group_owned_steps(int S, int sub, int& first, in
 }
 
 template <typename IO, bool kStep>
-__global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Params p) {
+__global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(Params p) {
   extern __shared__ __align__(16) float split_tile[];            // [steps][2 N]
   constexpr int G = kSplitGroup;
   const int N = (int)p.N;
@@ -140,6 +191,13 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
       float u_c[G], dt_c[G];
       load_items<IO, G>(u_row, t0, p.L, p.vec_ok, u_c);
       load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
+      // gate values of the steps this lane will finish: requested here so that the latency passes during the recurrence
+      float z_m[2] = {0.0f, 0.0f};
+      if (z_row && own_lane) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (e < own_count && t0 + own_first + e < p.L) z_m[e] = io_load<IO>(z_row + t0 + own_first + e);
+      }
       if constexpr (kStep) {               // steps past the end of the sequence stay zero (no-ops)
 #pragma unroll
         for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
@@ -175,7 +233,7 @@ __global__ void __launch_bounds__(kSplitThreads) sscan_forward_split_kernel(Para
           if (t < p.L) {
             float yy = fmaf(dskip, io_load<IO>(u_row + t), e == 0 ? y[0] : y[1]);
             if (z_row) {
-              const float zz = io_load<IO>(z_row + t);
+              const float zz = e == 0 ? z_m[0] : z_m[1];
               yy *= zz * sigmoidf(zz);
             }
             io_store<IO>(out_row + t, yy);
@@ -220,8 +278,10 @@ static int launch_fwd_split(const Params& p, cudaStream_t stream) {
 //            and the 32 / S channels of each, with 16-byte loads, every thread a share of the rows -- and adds the
 //            result to global memory with 16-byte vector atomics per (n, 4 steps).  Two half-window buffers
 //            alternate, so one barrier per half window is enough.
+// u, dt, z, dout of a chunk are copied into shared memory asynchronously one chunk ahead by the lanes of the channel, so
+// that no global-load latency sits inside the window loops.
 // Shared memory: B|C chunk tile in the I/O type [32][2N] | partial sums float [2][warps][4 steps][16][32] |
-// window-entry states [3][8][threads].
+// window-entry states [3][8][threads] | chunk operands [2][channels][8 + 3 * (4 or 8) + 1 vectors].
 constexpr int kSplitChunk = 32;
 constexpr int kSplitWindows = kSplitChunk / kSplitGroup;
 
@@ -240,6 +300,12 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   constexpr int kPartFloats = kSplitBwdWarps * 4 * 16 * 32;     // one half-window buffer
   float* part = reinterpret_cast<float*>(split_smem + (size_t)kSplitChunk * 2 * N * sizeof(IO));   // two of them
   float* wstate = part + 2 * kPartFloats;
+  // dt | u | z | dout of a chunk of 32 steps, per channel, copied asynchronously one chunk ahead by the lanes of the
+  // channel (an odd pitch in vectors keeps the channels of a warp on distinct banks)
+  constexpr int kVIO = kSplitChunk * (int)sizeof(IO) / 16;      // vectors of u, z or dout per chunk: 4 or 8
+  constexpr int kWIO = G * (int)sizeof(IO) / 16;                // ... per window: 1 or 2
+  constexpr int kCV = 8 + 3 * kVIO, kCS = kCV + 1;
+  uint4* cslab = reinterpret_cast<uint4*>(wstate + (kSplitWindows - 1) * kSplitStates * kSplitBwdThreads);   // [2][channels][kCS]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int lgN = 31 - __clz(N), lgS = lgN - 3;                 // N is a power of two
   const int sub = lane & (S - 1);
@@ -271,6 +337,24 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   int own_first, own_count;
   bool own_lane;
   group_owned_steps(S, sub, own_first, own_count, own_lane);
+  const int ch_cta = warp * per_warp + (lane >> lgS);
+  const int nch = kSplitBwdWarps * per_warp;
+  auto issue_chunk = [&](long long cn) {
+    if (cn >= 0) {
+      const long long tn = cn * kSplitChunk;
+      uint4* dst = cslab + ((size_t)(cn & 1) * nch + ch_cta) * kCS;
+      for (int v = sub; v < kCV; v += S) {
+        if (v < 8) {
+          stage_vec(dst + v, dt_row, 4, tn + 4 * v, p.L, p.vec_ok);
+        } else {
+          const int k = (v - 8) / kVIO, vv = (v - 8) - k * kVIO;
+          const IO* rowp = k == 0 ? u_row : (k == 1 ? z_row : go_row);
+          if (rowp) stage_vec(dst + v, rowp, (int)sizeof(IO), tn + vv * (16 / (int)sizeof(IO)), p.L, p.vec_ok);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 
   // (state pairs of this lane) of B and C of one step of the tile
   auto load_bc8 = [&](const IO* stepp, float2 (&Bp)[NQ], float2 (&Cp)[NQ]) {
@@ -312,10 +396,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       const int w = rr >> (5 - lgS), cw = (rr ^ v) & (per_warp - 1);
       const float4* src = reinterpret_cast<const float4*>(pb + (size_t)(w * 4 * 16) * 32 + cw * S);
       const float4 x0 = src[0], x1 = src[16 * 32 / 4], x2 = src[2 * 16 * 32 / 4], x3 = src[3 * 16 * 32 / 4];
-      a0.x += x0.x; a0.y += x0.y; a0.z += x0.z; a0.w += x0.w;
-      a1.x += x1.x; a1.y += x1.y; a1.z += x1.z; a1.w += x1.w;
-      a2.x += x2.x; a2.y += x2.y; a2.z += x2.z; a2.w += x2.w;
-      a3.x += x3.x; a3.y += x3.y; a3.z += x3.z; a3.w += x3.w;
+      add4(a0, x0); add4(a1, x1); add4(a2, x2); add4(a3, x3);
     }
     const int k = v & 7;
     float* base = ((v >> 3) ? p.dC : p.dB) + (b * N + (4 * s4) * kSplitStates + k) * p.L + t0 + 4 * hq;
@@ -334,28 +415,12 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
     }
   };
   const long long nchunks = (p.L + kSplitChunk - 1) / kSplitChunk;
+  issue_chunk(nchunks - 1);
   for (long long c = nchunks - 1; c >= 0; --c) {
     const long long t_c = c * kSplitChunk;
-    __syncthreads();                       // the previous chunk's tile has been consumed
-    {
-      constexpr int kVec = 16 / (int)sizeof(IO);
-      for (int i = threadIdx.x; i < 2 * N * (kSplitChunk / kVec); i += kSplitBwdThreads) {
-        const int r = i & (2 * N - 1), cv = i >> (lgN + 1);
-        const long long t = t_c + (long long)kVec * cv;
-        const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
-        IO v[kVec];
-        if (p.bc_vec_ok && t + kVec <= p.L) {
-          *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src + t);
-        } else {
-#pragma unroll
-          for (int j = 0; j < kVec; ++j) v[j] = (t + j < p.L) ? src[t + j] : IO(0.0f);
-        }
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) bc[(kVec * cv + j) * 2 * N + r] = v[j];
-      }
-    }
-    __syncthreads();
-    // the state entering the chunk
+    __syncthreads();                       // the previous chunk's tile and the operand buffer of chunk c + 1 have been consumed
+    issue_chunk(c - 1);
+    // the state entering the chunk (in flight during the tile load)
     float2 h0[NQ];
     {
       const float* sp = snaps + c * p.N;
@@ -363,6 +428,45 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       h0[0] = make_float2(s0.x, s0.y); h0[1] = make_float2(s0.z, s0.w);
       h0[2] = make_float2(s1.x, s1.y); h0[3] = make_float2(s1.z, s1.w);
     }
+    {
+      // rows of B then C, one 16-byte vector of consecutive steps per item, transposed into [step][value]; four
+      // loads in flight per thread before the first store
+      constexpr int kVec = 16 / (int)sizeof(IO);
+      const int total = 2 * N * (kSplitChunk / kVec);
+      for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kSplitBwdThreads) {
+        uint4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = i0 + k * kSplitBwdThreads;
+          v[k] = make_uint4(0u, 0u, 0u, 0u);
+          if (i < total) {
+            const int r = i & (2 * N - 1), cv = i >> (lgN + 1);
+            const long long t = t_c + (long long)kVec * cv;
+            const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
+            if (p.bc_vec_ok && t + kVec <= p.L) {
+              v[k] = *reinterpret_cast<const uint4*>(src + t);
+            } else {
+              IO* e = reinterpret_cast<IO*>(&v[k]);
+#pragma unroll
+              for (int j = 0; j < kVec; ++j) e[j] = (t + j < p.L) ? src[t + j] : IO(0.0f);
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = i0 + k * kSplitBwdThreads;
+          if (i < total) {
+            const int r = i & (2 * N - 1), cv = i >> (lgN + 1);
+            const IO* e = reinterpret_cast<const IO*>(&v[k]);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) bc[(kVec * cv + j) * 2 * N + r] = e[j];
+          }
+        }
+      }
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");   // this chunk's operands have landed
+    __syncthreads();
+    const uint4* cs = cslab + ((size_t)(c & 1) * nch + ch_cta) * kCS;
     // ---- pass A: states entering windows 1 .. 3
     {
       float2 h[NQ];
@@ -373,8 +477,8 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
         const long long t0 = t_c + (long long)w * G;
         if (t0 + G >= p.L) break;            // no later window inside the sequence (block-uniform)
         float u_c[G], dt_c[G];
-        load_items<IO, G>(u_row, t0, p.L, p.vec_ok, u_c);
-        load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
+        read_staged8<float>(cs + 2 * w, dt_c);
+        read_staged8<IO>(cs + 8 + kWIO * w, u_c);
         if constexpr (kStep) {
 #pragma unroll
           for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
@@ -403,14 +507,14 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       const long long t0 = t_c + (long long)w * G;
       if (t0 >= p.L) continue;               // block-uniform
       float u_c[G], dt_c[G], z_c[G], go_c[G];
-      load_items<IO, G>(u_row, t0, p.L, p.vec_ok, u_c);
-      load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
+      read_staged8<float>(cs + 2 * w, dt_c);
+      read_staged8<IO>(cs + 8 + kWIO * w, u_c);
       if constexpr (kStep) {
 #pragma unroll
         for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
       }
-      if (z_row) load_items<IO, G>(z_row, t0, p.L, p.vec_ok, z_c);
-      load_items<IO, G>(go_row, t0, p.L, p.vec_ok, go_c);
+      if (z_row) read_staged8<IO>(cs + 8 + kVIO + kWIO * w, z_c);
+      read_staged8<IO>(cs + 8 + 2 * kVIO + kWIO * w, go_c);
       if (!active) {
 #pragma unroll
         for (int j = 0; j < G; ++j) go_c[j] = 0.0f;
@@ -495,12 +599,13 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
           const long long t = t0 + own_first + e;
           if (t >= p.L) break;
           const float sgb = e == 0 ? du_v[0] : du_v[1], sdd = e == 0 ? ddt_v[0] : ddt_v[1];
-          const float u_m = io_load<IO>(u_row + t), go_m = io_load<IO>(go_row + t);
-          float dt_m = __ldg(dt_row + t);
+          const int jc = w * G + own_first + e;          // step inside the chunk
+          const float u_m = read_staged1<IO>(cs + 8, jc), go_m = read_staged1<IO>(cs + 8 + 2 * kVIO, jc);
+          float dt_m = read_staged1<float>(cs, jc);
           if constexpr (kStep) dt_m = step_transform(dt_m, dbias, p.delta_softplus != 0);
           float gy = go_m;
           if (z_row) {
-            const float zv = io_load<IO>(z_row + t);
+            const float zv = read_staged1<IO>(cs + 8 + kVIO, jc);
             const float sg = __fdividef(1.0f, 1.0f + ex2(-zv * kLog2e));
             const float y_m = fmaf(dskip, u_m, e == 0 ? yv[0] : yv[1]);
             gy = go_m * zv * sg;
@@ -517,6 +622,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (p.dbias_part) {                      // the steps of a channel were finished by different lanes
     for (int m = 1; m < S; m <<= 1) dBiasAcc += __shfl_xor_sync(0xffffffffu, dBiasAcc, m);
   }
@@ -538,7 +644,8 @@ static int launch_bwd_split_w(const Params& p, cudaStream_t stream) {
   const int per_cta = kSplitBwdWarps * (32 / (int)(p.N / kSplitStates));
   dim3 grid((unsigned)((p.D + per_cta - 1) / per_cta), (unsigned)p.B);
   const size_t smem = (size_t)kSplitChunk * 2 * p.N * sizeof(IO) + (size_t)2 * kSplitBwdWarps * 4 * 16 * 32 * sizeof(float) +
-                      (size_t)(kSplitWindows - 1) * kSplitStates * kSplitBwdThreads * sizeof(float);
+                      (size_t)(kSplitWindows - 1) * kSplitStates * kSplitBwdThreads * sizeof(float) +
+                      2 * (size_t)per_cta * (8 + 3 * (kSplitChunk * sizeof(IO) / 16) + 1) * 16;
   if (p.delta_bias || p.delta_softplus) {
     if (int rc = set_smem(sscan_backward_split_kernel<IO, true, kSplitBwdWarps>, smem)) return rc;
     sscan_backward_split_kernel<IO, true, kSplitBwdWarps><<<grid, kSplitBwdThreads, smem, stream>>>(p);
