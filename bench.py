@@ -65,7 +65,8 @@ def parse_args():
     ap.add_argument("--no-config4", action="store_true", help="skip the sharded long-sequence configuration")
     ap.add_argument("--config4-length", type=int, default=131072)
     ap.add_argument("--workload", default="dlinoss",
-                    choices=["dlinoss", "linoss", "lru", "mamba", "sdlinoss", "generic", "layer", "shard", "conv", "sharded_layer"],
+                    choices=["dlinoss", "linoss", "lru", "mamba", "sdlinoss", "generic", "layer", "shard", "conv", "mixer",
+                             "sharded_layer"],
                     help="dlinoss = the headline (BASELINE config 1); linoss = config 2 (LinOSS IM, B=128 L=16384 "
                          "P=128); mamba = config 3 (selective scan, bf16 I/O, B=32 D=2048 L=8192 N=16); "
                          "sharded_layer = config 4 (D-LinOSS layer, B=8 H=512 P=2048 split over the ranks; "
@@ -77,7 +78,8 @@ def parse_args():
     ap.add_argument("--length", type=int, default=4096)
     ap.add_argument("--ssm", type=int, default=256, help="oscillators per GPU")
     ap.add_argument("--side-state", type=int, default=0,
-                    help="state size of the selective-scan side workload (default 16, BASELINE config 3)")
+                    help="state size of the selective-scan side workload (default 16, BASELINE config 3) and of the "
+                         "mixer workload (default 256, ossm's Mamba4Rec configuration)")
     ap.add_argument("--side-length", type=int, default=0,
                     help="sequence length of the linoss / mamba side workloads (0 = the BASELINE config's own)")
     ap.add_argument("--e2e-steps", type=int, default=3)
@@ -912,6 +914,10 @@ def run_ours(args):
             side["layer"] = run_layer_side(args, dev, 5, 3)
         except Exception as exc:
             side["layer"] = {"error": str(exc)[:300]}
+        try:
+            side["mixer"] = run_mixer_side(args, dev, 10, 3)
+        except Exception as exc:
+            side["mixer"] = {"error": str(exc)[:300]}
         if _lib.device_status() != 0:
             side["device_status"] = "non-zero"
 
@@ -959,6 +965,85 @@ def pin_to_gpu_numa_node(local_rank):
         pass
 
 
+def run_mixer_side(args, dev, steps, warmup):
+    """Mamba mixer (ossm ``_MambaMixer``, ``mambarec.py:64-184``) forward + backward at the Mamba4Rec shape
+    (``configs/model/mambarec.yaml``: d_model 64, expand 2, d_state 256, d_conv 4; batch 128 of ``training/seqrec.yaml``,
+    length 200 of ``dataset/ml1m.yaml``), on a stand-in module with ossm's attribute names and initialisation ranges.
+    Two arms on the same parameters: this package's fused forward (conv1d + SiLU kernel, step transform inside the
+    scan), and the sequence of passes ossm's forward runs (transpose, pad, conv1d, SiLU, softplus(dt_proj)) around
+    this package's selective-scan op."""
+    import math
+
+    import torch
+    import torch.nn.functional as F
+    from torch import nn
+
+    from ossm_b200.mixer import mamba_mixer_forward
+    from ossm_b200.selective_scan import selective_scan
+
+    d_model, expand, d_state, d_conv = 64, 2, (args.side_state or 256), 4
+    Bz, L = (args.side_batch or 128), (args.side_length or 200)
+
+    class Mixer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.d_inner, self.d_state, self.d_conv = expand * d_model, d_state, d_conv
+            self.dt_rank = math.ceil(d_model / 16)
+            self.in_proj = nn.Linear(d_model, 2 * self.d_inner, bias=False)
+            self.conv1d = nn.Conv1d(self.d_inner, self.d_inner, d_conv, groups=self.d_inner, bias=True, padding=0)
+            self.x_proj = nn.Linear(self.d_inner, self.dt_rank + 2 * d_state, bias=False)
+            self.dt_proj = nn.Linear(self.dt_rank, self.d_inner, bias=True)
+            self.out_proj = nn.Linear(self.d_inner, d_model, bias=False)
+            dt = torch.exp(torch.rand(self.d_inner) * (math.log(0.1) - math.log(0.001)) + math.log(0.001)).clamp(min=1e-4)
+            with torch.no_grad():
+                self.dt_proj.bias.copy_(dt + torch.log(-torch.expm1(-dt)))
+            self.A_log = nn.Parameter(torch.log(torch.arange(1, d_state + 1, dtype=torch.float32).repeat(self.d_inner, 1)))
+
+    torch.manual_seed(0)
+    m = Mixer().to(dev)
+    x = torch.randn(Bz, L, d_model, device=dev, requires_grad=True)
+    gy = torch.randn(Bz, L, d_model, device=dev)
+
+    def reset():
+        x.grad = None
+        for q in m.parameters():
+            q.grad = None
+
+    def fused():
+        reset()
+        return mamba_mixer_forward(m, x)
+
+    def composed():
+        reset()
+        xz = m.in_proj(x)
+        xi, z = xz.chunk(2, dim=-1)
+        xc = m.conv1d(F.pad(xi.transpose(1, 2), (d_conv - 1, 0)))
+        xc = F.silu(xc)
+        proj = m.x_proj(xc.transpose(1, 2))
+        dt_raw, Bg, Cg = torch.split(proj, [m.dt_rank, d_state, d_state], dim=-1)
+        dt = F.softplus(m.dt_proj(dt_raw)).transpose(1, 2)
+        y = selective_scan(xc, dt, -torch.exp(m.A_log.float()), Bg, Cg, z.transpose(1, 2), None)
+        return m.out_proj(y.transpose(1, 2))
+
+    f_ms, b_ms, ms = time_pair(fused, lambda y: y.backward(gy), steps, warmup)
+    cf_ms, cb_ms, cms = time_pair(composed, lambda y: y.backward(gy), steps, warmup)
+    with torch.no_grad():
+        diff = float((fused() - composed()).abs().max())
+    elems = Bz * m.d_inner * L
+    out = {"metric": "mamba_mixer_fwd_bwd_gelem_per_s", "value": elems / (ms * 1e-3) / 1e9, "unit": UNIT,
+           "ms_per_step": ms, "steps": steps,
+           "workload": f"Mamba mixer fwd+bwd (ossm _MambaMixer), B={Bz} L={L} d_model={d_model} d_inner={m.d_inner} "
+                       f"d_state={d_state} d_conv={d_conv}, float32",
+           "kernel_ms": {"forward": f_ms, "backward": b_ms},
+           "passes_as_in_ossm_forward": {"ms_per_step": cms, "kernel_ms": {"forward": cf_ms, "backward": cb_ms},
+                                         "what": "transpose, pad, conv1d, SiLU, softplus(dt_proj) as separate library "
+                                                 "passes around this package's selective-scan op",
+                                         "max_abs_difference_of_outputs": diff}}
+    del m
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_single(args):
     """One side workload on its own (single GPU): one JSON line with its own metric name."""
     import torch
@@ -970,6 +1055,8 @@ def run_single(args):
     dev = torch.device("cuda", 0)
     if args.workload == "layer":
         out = run_layer_side(args, dev, args.steps, args.warmup)
+    elif args.workload == "mixer":
+        out = run_mixer_side(args, dev, args.steps, args.warmup)
     else:
         out = run_side(args.workload, args, dev, args.steps, args.warmup)
     if _lib.device_status() != 0:

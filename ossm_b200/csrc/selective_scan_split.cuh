@@ -190,17 +190,26 @@ __global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(P
       --until_save;
       float u_c[G], dt_c[G];
       load_items<IO, G>(u_row, t0, p.L, p.vec_ok, u_c);
-      load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
+      if constexpr (kStep) {
+        // the step transform once per step, not once per lane: lane `sub` of the channel transforms step sub (and
+        // sub + 4 where the channel has four lanes), then every lane collects the eight values.  Steps past the end
+        // of the sequence stay zero (no-ops).
+        const long long ta = t0 + (sub & 7), tb = ta + 4;
+        const float va = ta < p.L ? step_transform(__ldg(dt_row + ta), dbias, p.delta_softplus != 0) : 0.0f;
+        const float vb = (S == 4 && tb < p.L) ? step_transform(__ldg(dt_row + tb), dbias, p.delta_softplus != 0) : 0.0f;
+        const int base = lane & ~(S - 1);
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+          dt_c[j] = __shfl_sync(0xffffffffu, (S == 4 && j >= 4) ? vb : va, base + (S == 4 ? (j & 3) : j));
+      } else {
+        load_items<float, G>(dt_row, t0, p.L, p.vec_ok, dt_c);
+      }
       // gate values of the steps this lane will finish: requested here so that the latency passes during the recurrence
       float z_m[2] = {0.0f, 0.0f};
       if (z_row && own_lane) {
 #pragma unroll
         for (int e = 0; e < 2; ++e)
           if (e < own_count && t0 + own_first + e < p.L) z_m[e] = io_load<IO>(z_row + t0 + own_first + e);
-      }
-      if constexpr (kStep) {               // steps past the end of the sequence stay zero (no-ops)
-#pragma unroll
-        for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
       }
       float y[G];
       const float* steps = split_tile + (size_t)(gi * G) * 2 * N + sub * 4;
@@ -357,10 +366,14 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   };
 
   // (state pairs of this lane) of B and C of one step of the tile
+  // A float32 tile is laid out [step][B|C][half][lane][4] as in the forward (a lane's two 16-byte reads 16 bytes from
+  // its neighbours'); a 16-bit tile keeps [step][B|C][state], where a lane's eight states are one 16-byte read.
+  constexpr bool kPermuted = sizeof(IO) == 4;
+  const int bc_lane = kPermuted ? sub * 4 : sub * kSplitStates;   // this lane's offset inside a step's B (or C) values
   auto load_bc8 = [&](const IO* stepp, float2 (&Bp)[NQ], float2 (&Cp)[NQ]) {
     if constexpr (sizeof(IO) == 4) {
-      const float4 x0 = *reinterpret_cast<const float4*>(stepp), x1 = *reinterpret_cast<const float4*>(stepp + 4);
-      const float4 y0 = *reinterpret_cast<const float4*>(stepp + N), y1 = *reinterpret_cast<const float4*>(stepp + N + 4);
+      const float4 x0 = *reinterpret_cast<const float4*>(stepp), x1 = *reinterpret_cast<const float4*>(stepp + 4 * S);
+      const float4 y0 = *reinterpret_cast<const float4*>(stepp + N), y1 = *reinterpret_cast<const float4*>(stepp + N + 4 * S);
       Bp[0] = make_float2(x0.x, x0.y); Bp[1] = make_float2(x0.z, x0.w); Bp[2] = make_float2(x1.x, x1.y); Bp[3] = make_float2(x1.z, x1.w);
       Cp[0] = make_float2(y0.x, y0.y); Cp[1] = make_float2(y0.z, y0.w); Cp[2] = make_float2(y1.x, y1.y); Cp[3] = make_float2(y1.z, y1.w);
     } else {
@@ -458,15 +471,28 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
           if (i < total) {
             const int r = i & (2 * N - 1), cv = i >> (lgN + 1);
             const IO* e = reinterpret_cast<const IO*>(&v[k]);
+            int pos = r;
+            if constexpr (kPermuted) {
+              const int rr = r & (N - 1);
+              pos = (r & N) + ((((rr & 7) >> 2) * S + (rr >> 3)) << 2) + (rr & 3);
+            }
 #pragma unroll
-            for (int j = 0; j < kVec; ++j) bc[(kVec * cv + j) * 2 * N + r] = e[j];
+            for (int j = 0; j < kVec; ++j) bc[(kVec * cv + j) * 2 * N + pos] = e[j];
           }
         }
       }
     }
     asm volatile("cp.async.wait_group 1;" ::: "memory");   // this chunk's operands have landed
+    uint4* cs = cslab + ((size_t)(c & 1) * nch + ch_cta) * kCS;
+    if constexpr (kStep) {
+      // the step transform once per step of the chunk, in place, shared by the lanes of the channel and by both
+      // passes; steps past the end of the sequence were staged as zeros and stay zero (no-ops)
+      __syncwarp();
+      float* dts = reinterpret_cast<float*>(cs);
+      for (int j = sub; j < kSplitChunk; j += S)
+        if (t_c + j < p.L) dts[j] = step_transform(dts[j], dbias, p.delta_softplus != 0);
+    }
     __syncthreads();
-    const uint4* cs = cslab + ((size_t)(c & 1) * nch + ch_cta) * kCS;
     // ---- pass A: states entering windows 1 .. 3
     {
       float2 h[NQ];
@@ -479,14 +505,10 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
         float u_c[G], dt_c[G];
         read_staged8<float>(cs + 2 * w, dt_c);
         read_staged8<IO>(cs + 8 + kWIO * w, u_c);
-        if constexpr (kStep) {
-#pragma unroll
-          for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
-        }
 #pragma unroll
         for (int j = 0; j < G; ++j) {
           float2 Bp[NQ], Cp[NQ];
-          load_bc8(bc + (size_t)(w * G + j) * 2 * N + sub * kSplitStates, Bp, Cp);
+          load_bc8(bc + (size_t)(w * G + j) * 2 * N + bc_lane, Bp, Cp);
           const float2 dtv = splat(dt_c[j]), dtu = splat(dt_c[j] * u_c[j]);
 #pragma unroll
           for (int q = 0; q < NQ; ++q) {
@@ -509,10 +531,6 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       float u_c[G], dt_c[G], z_c[G], go_c[G];
       read_staged8<float>(cs + 2 * w, dt_c);
       read_staged8<IO>(cs + 8 + kWIO * w, u_c);
-      if constexpr (kStep) {
-#pragma unroll
-        for (int j = 0; j < G; ++j) dt_c[j] = (t0 + j < p.L) ? step_transform(dt_c[j], dbias, p.delta_softplus != 0) : 0.0f;
-      }
       if (z_row) read_staged8<IO>(cs + 8 + kVIO + kWIO * w, z_c);
       read_staged8<IO>(cs + 8 + 2 * kVIO + kWIO * w, go_c);
       if (!active) {
@@ -529,7 +547,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
           h[q] = make_float2(wstate[(((w - 1) * kSplitStates) + 2 * q) * kSplitBwdThreads + threadIdx.x],
                              wstate[(((w - 1) * kSplitStates) + 2 * q + 1) * kSplitBwdThreads + threadIdx.x]);
       }
-      const IO* steps = bc + (size_t)(w * G) * 2 * N + sub * kSplitStates;
+      const IO* steps = bc + (size_t)(w * G) * 2 * N + bc_lane;
       // re-run of the window
       float2 a[G][NQ], hw[G][NQ];
       float yv[G];
@@ -601,8 +619,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
           const float sgb = e == 0 ? du_v[0] : du_v[1], sdd = e == 0 ? ddt_v[0] : ddt_v[1];
           const int jc = w * G + own_first + e;          // step inside the chunk
           const float u_m = read_staged1<IO>(cs + 8, jc), go_m = read_staged1<IO>(cs + 8 + 2 * kVIO, jc);
-          float dt_m = read_staged1<float>(cs, jc);
-          if constexpr (kStep) dt_m = step_transform(dt_m, dbias, p.delta_softplus != 0);
+          const float dt_m = read_staged1<float>(cs, jc);         // already transformed
           float gy = go_m;
           if (z_row) {
             const float zv = read_staged1<IO>(cs + 8 + kVIO, jc);
