@@ -333,6 +333,28 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
                                       float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
                                       int64_t D, int64_t L, int64_t N, int io_dtype, ossm_b200_stream_t stream);
 
+/* The same pair with Bm, Cm given [B, L, N] -- the order of ossm's own arguments (a step's N values contiguous,
+ * bindings.cpp:199-222) -- with bc_pitch elements between the rows of consecutive steps (N for dense tensors; the
+ * mixer's B and C are column slices of one projection, mambarec.py:153-154, whose row pitch is dt_rank + 2 N), so
+ * that the caller's transposing copies disappear; dB, dC stay dense [B, N, L].  Taken for the
+ * state sizes whose kernels keep a [step][state] tile in shared memory: ossm_b200_selective_scan_step_major_bc(N)
+ * returns 1 for them (d_state 32, 64, 128, 256 under the default kernel choice), 0 otherwise, and the calls
+ * return an error for any other N. */
+int ossm_b200_selective_scan_step_major_bc(int64_t N);
+int ossm_b200_selective_scan_forward_step_major_bc(const void* u, const float* dt, const float* A, const void* Bm,
+                                                   const void* Cm, const void* z, const float* Dskip,
+                                                   const float* delta_bias, int delta_softplus, void* out,
+                                                   float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
+                                                   int64_t bc_pitch, int io_dtype, ossm_b200_stream_t stream);
+int ossm_b200_selective_scan_backward_step_major_bc(const void* u, const float* dt, const float* A, const void* Bm,
+                                                    const void* Cm, const void* z, const float* Dskip,
+                                                    const float* delta_bias, int delta_softplus, const void* dout,
+                                                    const float* chunk_states, void* du, float* ddt, float* dA,
+                                                    float* dB, float* dC, void* dz, float* dD, float* ddelta_bias,
+                                                    void* workspace, size_t workspace_bytes, int64_t B, int64_t D,
+                                                    int64_t L, int64_t N, int64_t bc_pitch, int io_dtype,
+                                                    ossm_b200_stream_t stream);
+
 /* ---- causal depthwise conv1d + bias + SiLU of the Mamba mixer ----------------------------------
  * Replaces the chain transpose -> F.pad -> nn.Conv1d(groups = D) -> nn.SiLU -> transpose of
  * _MambaMixer.forward (src/ossm/models/mambarec.py:143-151) by one pass that reads x once and writes

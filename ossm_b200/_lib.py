@@ -48,6 +48,11 @@ SIGNATURES = {
                                          + [c_int, c_void_p]),
     "ossm_b200_selective_scan_backward": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 11 + [c_size_t]
                                           + [c_int64] * 4 + [c_int, c_void_p]),
+    "ossm_b200_selective_scan_step_major_bc": (c_int, [c_int64]),
+    "ossm_b200_selective_scan_forward_step_major_bc": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 2 + [c_int64] * 5
+                                                       + [c_int, c_void_p]),
+    "ossm_b200_selective_scan_backward_step_major_bc": (c_int, [c_void_p] * 8 + [c_int] + [c_void_p] * 11 + [c_size_t]
+                                                        + [c_int64] * 5 + [c_int, c_void_p]),
     "ossm_b200_split_tf32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "ossm_b200_gemm_tf32x3": (c_int, [c_void_p] * 6 + [c_int64] * 6 + [c_int, c_int64, c_int64, c_void_p]),
     "ossm_b200_wgrad_tf32x3_workspace_bytes": (c_size_t, [c_int64] * 4),

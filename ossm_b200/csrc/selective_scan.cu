@@ -345,6 +345,8 @@ struct Params {
   bool vec_ok;
   bool bc_vec_ok;      // B / C rows may be read with 16-byte loads
   int split_flush_parts;   // split backward: threads per item of the dB / dC sums (0 = all the CTA has)
+  bool bc_step_major;      // split kernels: B / C are given [B, L, N] (a step's N values contiguous), not [B, N, L]
+  long long bc_pitch;      // ... with this many elements between the rows of consecutive steps (>= N)
 };
 
 // (A[d,2p], A[d,2p+1]) * log2(e); a missing odd partner gets 0 (decay 1, no forcing).
@@ -877,11 +879,20 @@ static int sscan_check(const char* fn, const void* u, const float* dt, const flo
   return kOk;
 }
 
-int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float* A, const void* Bm, const void* Cm,
-                                     const void* z, const float* Dskip, const float* delta_bias, int delta_softplus,
-                                     void* out, float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
-                                     int io_dtype, cudaStream_t stream) {
+static int selective_scan_forward_impl(bool step_major, int64_t bc_pitch, const void* u, const float* dt, const float* A, const void* Bm,
+                                       const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
+                                       int delta_softplus, void* out, float* chunk_states, int64_t B, int64_t D,
+                                       int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_forward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
+  if (step_major && !(sscan::g_use_serial && sscan::split_ok(N))) {
+    set_last_error("selective_scan_forward: B / C in [B, L, N] order are taken for d_state 32, 64, 128, 256 only "
+                   "(ossm_b200_selective_scan_step_major_bc)");
+    return kErrInvalidArgument;
+  }
+  if (step_major && bc_pitch < N) {
+    set_last_error("selective_scan: bc_pitch must be at least N");
+    return kErrInvalidArgument;
+  }
   if (B == 0 || D == 0 || L == 0) return kOk;
   if (!out) { set_last_error("selective_scan_forward: null out"); return kErrInvalidArgument; }
   if (N == 0) {
@@ -914,7 +925,9 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
       set_last_error("selective_scan_forward: chunk_states must be 16-byte aligned");
       return kErrInvalidArgument;
     }
-    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && (L * es) % 16 == 0;
+    p.bc_step_major = step_major;
+    p.bc_pitch = bc_pitch;
+    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && ((step_major ? bc_pitch : L) * es) % 16 == 0;
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_split<float>(p, stream)
                                            : sscan::launch_fwd_split<__nv_bfloat16>(p, stream);
   }
@@ -922,13 +935,41 @@ int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float
                                          : sscan::dispatch_items<__nv_bfloat16>(false, p, stream);
 }
 
-int ossm_b200_selective_scan_backward(const void* u, const float* dt, const float* A, const void* Bm,
-                                      const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
-                                      int delta_softplus, const void* dout, const float* chunk_states, void* du,
-                                      float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
-                                      float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
-                                      int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
+int ossm_b200_selective_scan_forward(const void* u, const float* dt, const float* A, const void* Bm, const void* Cm,
+                                     const void* z, const float* Dskip, const float* delta_bias, int delta_softplus,
+                                     void* out, float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
+                                     int io_dtype, cudaStream_t stream) {
+  return selective_scan_forward_impl(false, 0, u, dt, A, Bm, Cm, z, Dskip, delta_bias, delta_softplus, out, chunk_states,
+                                     B, D, L, N, io_dtype, stream);
+}
+
+int ossm_b200_selective_scan_forward_step_major_bc(const void* u, const float* dt, const float* A, const void* Bm,
+                                                   const void* Cm, const void* z, const float* Dskip,
+                                                   const float* delta_bias, int delta_softplus, void* out,
+                                                   float* chunk_states, int64_t B, int64_t D, int64_t L, int64_t N,
+                                                   int64_t bc_pitch, int io_dtype, cudaStream_t stream) {
+  return selective_scan_forward_impl(true, bc_pitch, u, dt, A, Bm, Cm, z, Dskip, delta_bias, delta_softplus, out, chunk_states,
+                                     B, D, L, N, io_dtype, stream);
+}
+
+int ossm_b200_selective_scan_step_major_bc(int64_t N) { return (sscan::g_use_serial && sscan::split_ok(N)) ? 1 : 0; }
+
+static int selective_scan_backward_impl(bool step_major, int64_t bc_pitch, const void* u, const float* dt, const float* A, const void* Bm,
+                                        const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
+                                        int delta_softplus, const void* dout, const float* chunk_states, void* du,
+                                        float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
+                                        float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
+                                        int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_backward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
+  if (step_major && !(sscan::g_use_serial && sscan::split_bwd_ok(N))) {
+    set_last_error("selective_scan_backward: B / C in [B, L, N] order are taken for d_state 32, 64, 128, 256 only "
+                   "(ossm_b200_selective_scan_step_major_bc)");
+    return kErrInvalidArgument;
+  }
+  if (step_major && bc_pitch < N) {
+    set_last_error("selective_scan: bc_pitch must be at least N");
+    return kErrInvalidArgument;
+  }
   if (D == 0 || N == 0) return kOk;
   if (!dA) { set_last_error("selective_scan_backward: null dA"); return kErrInvalidArgument; }
   if (int rc = check_cuda(cudaMemsetAsync(dA, 0, (size_t)D * N * sizeof(float), stream), "memset dA")) return rc;
@@ -982,8 +1023,11 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
       set_last_error("selective_scan_backward: chunk_states must be 16-byte aligned");
       return kErrInvalidArgument;
     }
+    p.bc_step_major = step_major;
+    p.bc_pitch = bc_pitch;
+    // dB / dC ([B, N, L] in both cases) take 16-byte atomics along t; B / C rows 16-byte loads along t or along n
     p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(dB) && sscan::aligned16(dC) &&
-                  (L * es) % 16 == 0 && (L * 4) % 16 == 0;
+                  ((step_major ? bc_pitch : L) * es) % 16 == 0 && (L * 4) % 16 == 0;
     rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_split<float>(p, stream)
                                          : sscan::launch_bwd_split<__nv_bfloat16>(p, stream);
   } else {
@@ -1003,6 +1047,30 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
     if (int rc2 = check_cuda(cudaGetLastError(), "sscan_reduce_batch_kernel launch")) return rc2;
   }
   return kOk;
+}
+
+int ossm_b200_selective_scan_backward(const void* u, const float* dt, const float* A, const void* Bm,
+                                      const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
+                                      int delta_softplus, const void* dout, const float* chunk_states, void* du,
+                                      float* ddt, float* dA, float* dB, float* dC, void* dz, float* dD,
+                                      float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
+                                      int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
+  return selective_scan_backward_impl(false, 0, u, dt, A, Bm, Cm, z, Dskip, delta_bias, delta_softplus, dout, chunk_states,
+                                      du, ddt, dA, dB, dC, dz, dD, ddelta_bias, workspace, workspace_bytes, B, D, L, N,
+                                      io_dtype, stream);
+}
+
+int ossm_b200_selective_scan_backward_step_major_bc(const void* u, const float* dt, const float* A, const void* Bm,
+                                                    const void* Cm, const void* z, const float* Dskip,
+                                                    const float* delta_bias, int delta_softplus, const void* dout,
+                                                    const float* chunk_states, void* du, float* ddt, float* dA,
+                                                    float* dB, float* dC, void* dz, float* dD, float* ddelta_bias,
+                                                    void* workspace, size_t workspace_bytes, int64_t B, int64_t D,
+                                                    int64_t L, int64_t N, int64_t bc_pitch, int io_dtype,
+                                                    cudaStream_t stream) {
+  return selective_scan_backward_impl(true, bc_pitch, u, dt, A, Bm, Cm, z, Dskip, delta_bias, delta_softplus, dout, chunk_states,
+                                      du, ddt, dA, dB, dC, dz, dD, ddelta_bias, workspace, workspace_bytes, B, D, L, N,
+                                      io_dtype, stream);
 }
 
 }  // extern "C"

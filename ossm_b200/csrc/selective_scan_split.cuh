@@ -136,8 +136,9 @@ __global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(P
   const float* dt_row = p.dt + row;
   const IO* z_row = p.z ? static_cast<const IO*>(p.z) + row : nullptr;
   IO* out_row = static_cast<IO*>(p.out) + row;
-  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
-  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
+  const long long bc_batch = p.bc_step_major ? p.L * p.bc_pitch : p.N * p.L;   // elements per batch entry of B, C
+  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * bc_batch;
+  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * bc_batch;
 
   float2 A2[kSplitStates / 2], h[kSplitStates / 2];
 #pragma unroll
@@ -160,6 +161,39 @@ __global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(P
     // rows of B then C, one 16-byte vector of consecutive steps per item, transposed into [step][value]
     // (fetching the next tile into registers during the steps of this one was measured: no faster)
     constexpr int kVec = 16 / (int)sizeof(IO);
+    if (p.bc_step_major) {
+      // B, C given [B, L, N] (rows p.bc_pitch elements apart): a step's N values are contiguous, 16-byte pieces go
+      // straight to their place in the tile
+      const int lgP = 31 - __clz(N) - (kVec == 8 ? 3 : 2);       // log2 of the pieces per row
+#pragma unroll 4
+      for (int i = threadIdx.x; i < kSplitTileFloats / kVec; i += kSplitThreads) {
+        const int g = i & ((1 << lgP) - 1), wc = (i >> lgP) & 1, st = i >> (lgP + 1);
+        const long long t = t_tile + st;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (t < p.L) {
+          const IO* src = (wc ? Cm_b : Bm_b) + t * p.bc_pitch + g * kVec;
+          if (p.bc_vec_ok) {
+            raw = *reinterpret_cast<const uint4*>(src);
+          } else {
+            IO* e = reinterpret_cast<IO*>(&raw);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) e[j] = src[j];
+          }
+        }
+        float* dstp = split_tile + (size_t)st * 2 * N + wc * N;
+        if constexpr (kVec == 4) {             // states 4g .. 4g+3: lane g >> 1, half g & 1
+          *reinterpret_cast<uint4*>(dstp + ((((g & 1) * S) + (g >> 1)) << 2)) = raw;
+        } else {                               // states 8g .. 8g+7: lane g, both halves
+          const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+          *reinterpret_cast<float4*>(dstp + (g << 2)) =
+              make_float4(__uint_as_float(wv[0] << 16), __uint_as_float(wv[0] & 0xffff0000u),
+                          __uint_as_float(wv[1] << 16), __uint_as_float(wv[1] & 0xffff0000u));
+          *reinterpret_cast<float4*>(dstp + ((S + g) << 2)) =
+              make_float4(__uint_as_float(wv[2] << 16), __uint_as_float(wv[2] & 0xffff0000u),
+                          __uint_as_float(wv[3] << 16), __uint_as_float(wv[3] & 0xffff0000u));
+        }
+      }
+    } else
     for (int i = threadIdx.x; i < 2 * N * (tile_steps / kVec); i += kSplitThreads) {
       const int r = i & (2 * N - 1), cv = i >> (32 - __clz(N));      // N is a power of two
       const long long t = t_tile + (long long)kVec * cv;
@@ -328,8 +362,9 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
   const float* dt_row = p.dt + row;
   const IO* z_row = p.z ? static_cast<const IO*>(p.z) + row : nullptr;
   const IO* go_row = static_cast<const IO*>(p.dout) + row;
-  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * p.N * p.L;
-  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * p.N * p.L;
+  const long long bc_batch = p.bc_step_major ? p.L * p.bc_pitch : p.N * p.L;   // elements per batch entry of B, C
+  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * bc_batch;
+  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * bc_batch;
   const float* snaps = p.chunk_states + (b * p.D + d) * p.nstates * p.N + sub * kSplitStates;
 
   float2 A2[NQ], ag[NQ], dAacc[NQ];
@@ -446,6 +481,40 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 8 / kBwdWarps) sscan_backward_
       // loads in flight per thread before the first store
       constexpr int kVec = 16 / (int)sizeof(IO);
       const int total = 2 * N * (kSplitChunk / kVec);
+      if (p.bc_step_major) {
+        // B, C given [B, L, N] (rows p.bc_pitch elements apart): a step's N values are contiguous, 16-byte pieces
+        // go straight to their place in the tile
+        const int lgP = lgN - (kVec == 8 ? 3 : 2);               // log2 of the pieces per row
+        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kSplitBwdThreads) {
+          uint4 v[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kSplitBwdThreads;
+            v[k] = make_uint4(0u, 0u, 0u, 0u);
+            const int g = i & ((1 << lgP) - 1), wc = (i >> lgP) & 1, st = i >> (lgP + 1);
+            const long long t = t_c + st;
+            if (i < total && t < p.L) {
+              const IO* src = (wc ? Cm_b : Bm_b) + t * p.bc_pitch + g * kVec;
+              if (p.bc_vec_ok) {
+                v[k] = *reinterpret_cast<const uint4*>(src);
+              } else {
+                IO* e = reinterpret_cast<IO*>(&v[k]);
+#pragma unroll
+                for (int j = 0; j < kVec; ++j) e[j] = src[j];
+              }
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kSplitBwdThreads;
+            if (i < total) {
+              const int g = i & ((1 << lgP) - 1), wc = (i >> lgP) & 1, st = i >> (lgP + 1);
+              const int pos = wc * N + (kPermuted ? ((((g & 1) * S) + (g >> 1)) << 2) : g * kVec);
+              *reinterpret_cast<uint4*>(bc + (size_t)st * 2 * N + pos) = v[k];
+            }
+          }
+        }
+      } else
       for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kSplitBwdThreads) {
         uint4 v[4];
 #pragma unroll

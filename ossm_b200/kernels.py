@@ -308,6 +308,24 @@ def _time_major_bc(t: Tensor) -> Tensor:
     return tt if tt.is_contiguous() else tt.contiguous()
 
 
+def _bc_operands(lib, B: Tensor, C: Tensor, n: int):
+    """``(B, C, pitch)`` as handed to the library.  ``pitch == 0``: time-contiguous ``[B, N, L]`` (free when the
+    caller passed transposed views of such tensors, else a transposing copy).  ``pitch > 0``: ossm's ``[B, L, N]``
+    tensors as they are -- dense, or column slices of one projection as in the mixer, ``pitch`` elements between
+    the rows of consecutive steps -- where the kernels of this state size read them in that order (no copy)."""
+    tb, tc = B.transpose(1, 2), C.transpose(1, 2)
+    if tb.is_contiguous() and tc.is_contiguous():
+        return tb, tc, 0
+    if lib.ossm_b200_selective_scan_step_major_bc(n) == 1:
+        length = B.size(1)
+        pitch = B.stride(1)
+        if (B.stride(2) == 1 and C.stride(2) == 1 and C.stride(1) == pitch and pitch >= n
+                and B.stride(0) == length * pitch and C.stride(0) == length * pitch):
+            return B, C, pitch
+        return B.contiguous(), C.contiguous(), n
+    return tb.contiguous(), tc.contiguous(), 0
+
+
 def _check_selective(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tensor, gate: Optional[Tensor]):
     # mirrors _check_inputs of selective_scan_cpu.cpp / selective_scan_cuda.cu:196-250
     if inputs.dim() != 3:
@@ -364,14 +382,18 @@ def selective_scan_fwd(inputs: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: Tens
     u = inputs.contiguous()
     dtc = dt.float().contiguous()
     Ac = A.float().contiguous()
-    Bt, Ct = _time_major_bc(B), _time_major_bc(C)
+    Bt, Ct, pitch = _bc_operands(lib, B, C, n)
     zc = gate.contiguous() if gate is not None else None
     Dc = D.float().contiguous() if D is not None else None
     bias = _delta_bias(delta_bias, ch, dev)
+    head = (_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias), int(bool(delta_softplus)), _p(out),
+            _p(states), bsz, ch, length, n)
+    tail = (_IO_DTYPES[inputs.dtype], _stream(dev))
     with torch.cuda.device(dev):
-        rc = lib.ossm_b200_selective_scan_forward(_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias),
-                                                  int(bool(delta_softplus)), _p(out), _p(states), bsz, ch, length, n,
-                                                  _IO_DTYPES[inputs.dtype], _stream(dev))
+        if pitch:
+            rc = lib.ossm_b200_selective_scan_forward_step_major_bc(*head, pitch, *tail)
+        else:
+            rc = lib.ossm_b200_selective_scan_forward(*head, *tail)
     _lib.check(rc, "selective_scan_forward")
     return out, states
 
@@ -408,7 +430,7 @@ def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tenso
         u = inputs.contiguous()
         dtc = dt.float().contiguous()
         Ac = A.float().contiguous()
-        Bt, Ct = _time_major_bc(B), _time_major_bc(C)
+        Bt, Ct, pitch = _bc_operands(lib, B, C, n)
         zc = gate.contiguous() if gate is not None else None
         Dc = D.float().contiguous() if D is not None else None
         go = grad_output.to(inputs.dtype).contiguous()
@@ -417,10 +439,14 @@ def selective_scan_bwd(grad_output: Tensor, inputs: Tensor, dt: Tensor, A: Tenso
                 or tuple(chunk_states.shape) != (bsz, ch, (length + chunk - 1) // chunk, n)):
             raise RuntimeError("ossm_b200: chunk_states do not belong to these inputs")
         with torch.cuda.device(dev):
-            rc = lib.ossm_b200_selective_scan_backward(
-                _p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias), int(bool(delta_softplus)), _p(go),
-                _p(chunk_states), _p(du), _p(ddt), _p(dA), _p(dBt), _p(dCt), _p(dz), _p(dD), _p(dbias),
-                _p(workspace), ws_bytes, bsz, ch, length, n, _IO_DTYPES[inputs.dtype], _stream(dev))
+            head = (_p(u), _p(dtc), _p(Ac), _p(Bt), _p(Ct), _p(zc), _p(Dc), _p(bias), int(bool(delta_softplus)),
+                    _p(go), _p(chunk_states), _p(du), _p(ddt), _p(dA), _p(dBt), _p(dCt), _p(dz), _p(dD), _p(dbias),
+                    _p(workspace), ws_bytes, bsz, ch, length, n)
+            tail = (_IO_DTYPES[inputs.dtype], _stream(dev))
+            if pitch:
+                rc = lib.ossm_b200_selective_scan_backward_step_major_bc(*head, pitch, *tail)
+            else:
+                rc = lib.ossm_b200_selective_scan_backward(*head, *tail)
         _lib.check(rc, "selective_scan_backward")
     dB = dBt.transpose(1, 2).to(B.dtype)
     dC = dCt.transpose(1, 2).to(C.dtype)

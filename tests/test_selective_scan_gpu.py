@@ -181,6 +181,46 @@ def test_time_contiguous_bc_is_used_in_place():
     assert torch.equal(o1, o2)
 
 
+@pytest.mark.parametrize("shape", [(2, 12, 200, 32), (1, 20, 75, 64), (2, 5, 130, 128), (1, 16, 96, 256)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_bc_layouts_agree(shape, io):
+    """d_state 32 .. 256 read B and C in ossm's own [B, L, N] order (dense, or as column slices of one projection
+    with a row pitch, as the mixer holds them, mambarec.py:153-154) without a copy, and time-contiguous [B, N, L]
+    views as BASELINE config 3 gives them: same kernels behind three loaders, same results (dB, dC are sums of
+    float atomics, compared with a tolerance)."""
+    from ossm_b200 import kernels
+
+    Bz, Dn, L, N = shape
+    u, dt, A, Bm, Cm, gate, go, _ = make_case(Bz, Dn, L, N, seed=17)
+    u, gate, go = dev(u, io), dev(gate, io), dev(go, io)
+    dt, A = dev(dt), dev(A)
+    dense_b, dense_c = dev(Bm, io), dev(Cm, io)
+    proj = torch.zeros(Bz, L, 8 + 2 * N, device="cuda", dtype=io)
+    proj[..., 8:8 + N] = dense_b
+    proj[..., 8 + N:] = dense_c
+    variants = {
+        "dense": (dense_b, dense_c),
+        "pitched": (proj[..., 8:8 + N], proj[..., 8 + N:]),
+        "time_major": (dense_b.transpose(1, 2).contiguous().transpose(1, 2),
+                       dense_c.transpose(1, 2).contiguous().transpose(1, 2)),
+    }
+    results = {}
+    for name, (b_op, c_op) in variants.items():
+        out, states = kernels.selective_scan_fwd(u, dt, A, b_op, c_op, gate)
+        grads = kernels.selective_scan_bwd(go, u, dt, A, b_op, c_op, gate, states)
+        results[name] = (out, grads)
+    ref_out, ref = results["time_major"]
+    for name in ("dense", "pitched"):
+        out, grads = results[name]
+        assert torch.equal(out, ref_out), name
+        for k, (g, r) in enumerate(zip(grads[:6], ref[:6])):
+            if k in (3, 4):
+                assert so.max_rel_err(g.float().cpu().numpy(), r.float().cpu().numpy()) <= 1e-5, (name, NAMES[k])
+            else:
+                assert torch.equal(g, r), (name, NAMES[k])
+
+
 def test_reference_compatible_entry_points():
     from ossm_b200 import kernels
 
