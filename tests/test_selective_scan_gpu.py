@@ -199,9 +199,13 @@ def test_bc_layouts_agree(shape, io):
     proj = torch.zeros(Bz, L, 8 + 2 * N, device="cuda", dtype=io)
     proj[..., 8:8 + N] = dense_b
     proj[..., 8 + N:] = dense_c
+    odd = torch.zeros(Bz, L, 5 + 2 * N, device="cuda", dtype=io)     # rows and bases off the 16-byte grid
+    odd[..., 5:5 + N] = dense_b
+    odd[..., 5 + N:] = dense_c
     variants = {
         "dense": (dense_b, dense_c),
         "pitched": (proj[..., 8:8 + N], proj[..., 8 + N:]),
+        "pitched_unaligned": (odd[..., 5:5 + N], odd[..., 5 + N:]),
         "time_major": (dense_b.transpose(1, 2).contiguous().transpose(1, 2),
                        dense_c.transpose(1, 2).contiguous().transpose(1, 2)),
     }
@@ -211,12 +215,15 @@ def test_bc_layouts_agree(shape, io):
         grads = kernels.selective_scan_bwd(go, u, dt, A, b_op, c_op, gate, states)
         results[name] = (out, grads)
     ref_out, ref = results["time_major"]
-    for name in ("dense", "pitched"):
+    # the order of the atomic additions differs from run to run: float32 rounding, then (bf16 I/O) one rounding of
+    # the sum to bfloat16, whose last place is 2^-8 of the value
+    tol = 1e-5 if io == torch.float32 else 8e-3
+    for name in ("dense", "pitched", "pitched_unaligned"):
         out, grads = results[name]
         assert torch.equal(out, ref_out), name
         for k, (g, r) in enumerate(zip(grads[:6], ref[:6])):
             if k in (3, 4):
-                assert so.max_rel_err(g.float().cpu().numpy(), r.float().cpu().numpy()) <= 1e-5, (name, NAMES[k])
+                assert so.max_rel_err(g.float().cpu().numpy(), r.float().cpu().numpy()) <= tol, (name, NAMES[k])
             else:
                 assert torch.equal(g, r), (name, NAMES[k])
 
