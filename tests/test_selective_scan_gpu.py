@@ -309,6 +309,37 @@ def test_serial_and_time_parallel_kernels_agree(shape):
             assert so.max_rel_err(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(1, 8, 300, 32), (2, 5, 200, 64), (1, 6, 130, 128), (1, 9, 100, 256)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_split_and_time_parallel_kernels_agree(shape):
+    """d_state 32 / 64 / 128 / 256 run the kernels with a channel's states split over lanes by default; the
+    time-parallel kernels, which they replaced for these sizes and which stay selectable, must give the same results
+    on the same inputs (gate, skip term and folded step transform included)."""
+    from ossm_b200 import kernels
+
+    n = shape[3]
+    u, dt, A, Bm, Cm, gate, go, Dv = make_case(*shape, seed=33)
+    bias = torch.randn(shape[1], generator=torch.Generator().manual_seed(5)) * 0.1
+    args = [dev(u), dev(dt) * 20 - 1, dev(A), dev(Bm), dev(Cm), dev(gate)]      # raw steps of either sign
+    results = []
+    for serial in (1, 0):
+        kernels.set_selective_scan_tuning("serial", serial)
+        try:
+            if serial:
+                assert kernels.selective_scan_chunk(n) == 32
+            out, states = kernels.selective_scan_fwd(*args, dev(Dv), delta_bias=dev(bias), delta_softplus=True)
+            grads = kernels.selective_scan_bwd(dev(go), *args, states, dev(Dv), delta_bias=dev(bias),
+                                               delta_softplus=True)
+        finally:
+            kernels.set_selective_scan_tuning("serial", 1)
+        results.append((out, grads))
+    (o1, g1), (o0, g0) = results
+    assert so.max_rel_err(o1.cpu().numpy(), o0.cpu().numpy()) <= 2e-5
+    for a, b in zip(g1, g0):
+        if a is not None:
+            assert so.max_rel_err(a.cpu().numpy(), b.cpu().numpy()) <= 5e-5
+
+
 DELTA = np.load(os.path.join(GOLD, "selective_scan_delta.npz"))
 
 
