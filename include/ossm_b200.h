@@ -338,7 +338,7 @@ int ossm_b200_selective_scan_backward(const void* u, const float* dt, const floa
  * mixer's B and C are column slices of one projection, mambarec.py:153-154, whose row pitch is dt_rank + 2 N), so
  * that the caller's transposing copies disappear; dB, dC stay dense [B, N, L].  Taken for the
  * state sizes whose kernels keep a [step][state] tile in shared memory: ossm_b200_selective_scan_step_major_bc(N)
- * returns 1 for them (d_state 32, 64, 128, 256 under the default kernel choice), 0 otherwise, and the calls
+ * returns 1 for them (d_state 16, 32, 64, 128, 256 under the default kernel choice), 0 otherwise, and the calls
  * return an error for any other N. */
 int ossm_b200_selective_scan_step_major_bc(int64_t N);
 int ossm_b200_selective_scan_forward_step_major_bc(const void* u, const float* dt, const float* A, const void* Bm,

@@ -884,8 +884,8 @@ static int selective_scan_forward_impl(bool step_major, int64_t bc_pitch, const 
                                        int delta_softplus, void* out, float* chunk_states, int64_t B, int64_t D,
                                        int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_forward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
-  if (step_major && !(sscan::g_use_serial && sscan::split_ok(N))) {
-    set_last_error("selective_scan_forward: B / C in [B, L, N] order are taken for d_state 32, 64, 128, 256 only "
+  if (step_major && !(sscan::g_use_serial && (sscan::split_ok(N) || sscan::serial_ok(N)))) {
+    set_last_error("selective_scan_forward: B / C in [B, L, N] order are taken for d_state 16, 32, 64, 128, 256 only "
                    "(ossm_b200_selective_scan_step_major_bc)");
     return kErrInvalidArgument;
   }
@@ -916,7 +916,10 @@ static int selective_scan_forward_impl(bool step_major, int64_t bc_pitch, const 
       return kErrInvalidArgument;
     }
     // the B/C tiles are also read with 16-byte loads
-    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm);
+    p.bc_step_major = step_major;
+    p.bc_pitch = bc_pitch;
+    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && (bc_pitch * es) % 16 == 0;
+    if (!step_major) p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm);
     return io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_fwd_serial<float>(p, stream)
                                            : sscan::launch_fwd_serial<__nv_bfloat16>(p, stream);
   }
@@ -952,7 +955,9 @@ int ossm_b200_selective_scan_forward_step_major_bc(const void* u, const float* d
                                      B, D, L, N, io_dtype, stream);
 }
 
-int ossm_b200_selective_scan_step_major_bc(int64_t N) { return (sscan::g_use_serial && sscan::split_ok(N)) ? 1 : 0; }
+int ossm_b200_selective_scan_step_major_bc(int64_t N) {
+  return (sscan::g_use_serial && (sscan::split_ok(N) || sscan::serial_ok(N))) ? 1 : 0;
+}
 
 static int selective_scan_backward_impl(bool step_major, int64_t bc_pitch, const void* u, const float* dt, const float* A, const void* Bm,
                                         const void* Cm, const void* z, const float* Dskip, const float* delta_bias,
@@ -961,8 +966,8 @@ static int selective_scan_backward_impl(bool step_major, int64_t bc_pitch, const
                                         float* ddelta_bias, void* workspace, size_t workspace_bytes, int64_t B,
                                         int64_t D, int64_t L, int64_t N, int io_dtype, cudaStream_t stream) {
   if (int rc = sscan_check("selective_scan_backward", u, dt, A, Bm, Cm, B, D, L, N, io_dtype)) return rc;
-  if (step_major && !(sscan::g_use_serial && sscan::split_bwd_ok(N))) {
-    set_last_error("selective_scan_backward: B / C in [B, L, N] order are taken for d_state 32, 64, 128, 256 only "
+  if (step_major && !(sscan::g_use_serial && (sscan::split_bwd_ok(N) || sscan::serial_ok(N)))) {
+    set_last_error("selective_scan_backward: B / C in [B, L, N] order are taken for d_state 16, 32, 64, 128, 256 only "
                    "(ossm_b200_selective_scan_step_major_bc)");
     return kErrInvalidArgument;
   }
@@ -1015,7 +1020,11 @@ static int selective_scan_backward_impl(bool step_major, int64_t bc_pitch, const
       return kErrInvalidArgument;
     }
     // B/C tiles, dB and dC are also accessed with 16-byte operations
-    p.vec_ok = p.vec_ok && sscan::aligned16(Bm) && sscan::aligned16(Cm) && sscan::aligned16(dB) && sscan::aligned16(dC);
+    p.bc_step_major = step_major;
+    p.bc_pitch = bc_pitch;
+    p.bc_vec_ok = sscan::aligned16(Bm) && sscan::aligned16(Cm) && (bc_pitch * es) % 16 == 0;
+    p.vec_ok = p.vec_ok && (step_major || (sscan::aligned16(Bm) && sscan::aligned16(Cm))) && sscan::aligned16(dB) &&
+               sscan::aligned16(dC);
     rc = io_dtype == OSSM_B200_DTYPE_F32 ? sscan::launch_bwd_serial<float>(p, stream)
                                          : sscan::launch_bwd_serial<__nv_bfloat16>(p, stream);
   } else if (sscan::g_use_serial && sscan::split_bwd_ok(N)) {

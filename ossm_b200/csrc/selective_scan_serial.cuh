@@ -42,7 +42,10 @@ constexpr int kStage = 32;            // steps per B/C shared-memory tile
 // asynchronous 16-byte copies (cp.async) of the raw rows into a staging buffer, finish() --
 // called by the same thread after the copies have landed -- transposes its own items.  No
 // registers are held in between.  Work item i covers row r = i % 2N (B rows, then C rows) and
-// the kVec consecutive steps of chunk i / 2N.
+// the kVec consecutive steps of chunk i / 2N.  With B and C given step-major ([B, L, N], `pitch`
+// elements between the rows of consecutive steps: ossm's own argument order) item i is the i-th
+// 16-byte piece of the tile itself -- step i / (2N / kVec), B then C, kVec consecutive states --
+// and finish() only converts.
 template <typename IO, int N, int kThreads>
 struct TileLoader {
   static constexpr int kVec = 16 / (int)sizeof(IO);
@@ -50,7 +53,29 @@ struct TileLoader {
   static constexpr int kPerThread = (kItemsTotal + kThreads - 1) / kThreads;
 
   static __device__ __forceinline__ void issue(uint4* raw, const IO* B_b, const IO* C_b, long long t_base,
-                                               long long L, bool vec_ok) {
+                                               long long L, bool vec_ok, bool step_major = false,
+                                               long long pitch = 0) {
+    if (step_major) {
+      constexpr int kPieces = N / kVec;     // pieces of a step's B (or C) row
+#pragma unroll
+      for (int q = 0; q < kPerThread; ++q) {
+        const int i = threadIdx.x + q * kThreads;
+        if (i >= kItemsTotal) continue;
+        const int st = i / (2 * kPieces), wc = (i / kPieces) & 1, g = i % kPieces;
+        const long long t = t_base + st;
+        const IO* src = (wc ? C_b : B_b) + t * pitch + g * kVec;
+        if (vec_ok && t < L) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(raw + i)), "l"(src) : "memory");
+        } else {
+          IO tmp[kVec];
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) tmp[j] = (t < L) ? src[j] : IO(0.0f);
+          raw[i] = *reinterpret_cast<const uint4*>(tmp);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
 #pragma unroll
     for (int q = 0; q < kPerThread; ++q) {
       const int i = threadIdx.x + q * kThreads;
@@ -72,8 +97,21 @@ struct TileLoader {
 
   // TT: element type of the tile, the I/O type or float (converted here, once per CTA, instead of at every use)
   template <typename TT>
-  static __device__ __forceinline__ void finish(const uint4* raw, TT* tile) {
+  static __device__ __forceinline__ void finish(const uint4* raw, TT* tile, bool step_major = false) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (step_major) {
+#pragma unroll
+      for (int q = 0; q < kPerThread; ++q) {
+        const int i = threadIdx.x + q * kThreads;
+        if (i >= kItemsTotal) continue;
+        const uint4 v = raw[i];
+        const IO* e = reinterpret_cast<const IO*>(&v);
+        TT* o = tile + i * kVec;
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) o[j] = static_cast<TT>(e[j]);
+      }
+      return;
+    }
 #pragma unroll
     for (int q = 0; q < kPerThread; ++q) {
       const int i = threadIdx.x + q * kThreads;
@@ -187,7 +225,8 @@ struct GroupStream {
 
 // kStep: the given dt is a raw step to be biased / passed through softplus (a template parameter so that the
 // plain case keeps its register allocation)
-template <typename IO, int N, bool kStep>
+// kStepMajor: B and C are given [B, L, N] (a template parameter for the same reason)
+template <typename IO, int N, bool kStep, bool kStepMajor>
 __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Params p) {
   constexpr int NP = N / 2;
   constexpr int G = kSerialInterval;
@@ -204,8 +243,10 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
   static_assert(kOutVecs == 4 || kOutVecs == 8, "swizzle below");
   __shared__ uint4 ostage[kSerialSpan * kOutVecs];
   const long long b = blockIdx.y;
-  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * N * p.L;
-  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * N * p.L;
+  const long long bc_batch = kStepMajor ? p.L * p.bc_pitch : N * p.L;   // elements per batch entry of B, C
+  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * bc_batch;
+  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * bc_batch;
+  const bool tile_vec = kStepMajor ? p.bc_vec_ok : p.vec_ok;
   const IO* u_all = static_cast<const IO*>(p.u);
   const IO* z_all = static_cast<const IO*>(p.z);
   Stream stream{slab};
@@ -233,9 +274,9 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
   }
 
   const long long nstages = (p.L + kStage - 1) / kStage;
-  Loader::issue(raw, Bm_b, Cm_b, 0, p.L, p.vec_ok);
+  Loader::issue(raw, Bm_b, Cm_b, 0, p.L, tile_vec, kStepMajor, p.bc_pitch);
   stream.issue(0, u_all, p.dt, z_all, off, 0, p.L, p.vec_ok);
-  Loader::finish(raw, tile[0]);   // waits for everything issued so far
+  Loader::finish(raw, tile[0], kStepMajor);   // waits for everything issued so far
   __syncwarp();
 
   for (long long s = 0; s < nstages; ++s) {
@@ -250,7 +291,7 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
       if (g == 0 && s + 1 < nstages) {
         // next stage's B/C rows (each thread transposes only what it copied itself); issued after
         // the group prefetch so that waiting for this group's data does not wait for them
-        Loader::issue(raw, Bm_b, Cm_b, (s + 1) * kStage, p.L, p.vec_ok);
+        Loader::issue(raw, Bm_b, Cm_b, (s + 1) * kStage, p.L, tile_vec, kStepMajor, p.bc_pitch);
         asm volatile("cp.async.wait_group 2;" ::: "memory");
       } else {
         asm volatile("cp.async.wait_group 1;" ::: "memory");   // everything but the prefetch just issued has landed
@@ -346,7 +387,7 @@ __global__ void __launch_bounds__(kSerialLanes) sscan_forward_serial_kernel(Para
       }
       __syncwarp();
     }
-    if (s + 1 < nstages) Loader::finish(raw, tile[buf ^ 1]);
+    if (s + 1 < nstages) Loader::finish(raw, tile[buf ^ 1], kStepMajor);
     __syncwarp();
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -395,7 +436,7 @@ struct BwdSmem {
   float part[2][kBwdWarps][G][32];                     // per-warp channel sums of dB / dC of a window
 };
 
-template <typename IO, int N, int kSplit, bool kStep>
+template <typename IO, int N, int kSplit, bool kStep, bool kStepMajor>
 __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backward_serial_kernel(Params p) {
   using Smem = BwdSmem<IO, N, kSplit>;
   constexpr int G = kSerialInterval;
@@ -428,8 +469,10 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
   const float* dt_row = p.dt + row;
   const IO* z_row = p.z ? static_cast<const IO*>(p.z) + row : nullptr;
   const IO* go_row = static_cast<const IO*>(p.dout) + row;
-  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * N * p.L;
-  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * N * p.L;
+  const long long bc_batch = kStepMajor ? p.L * p.bc_pitch : N * p.L;   // elements per batch entry of B, C
+  const IO* Bm_b = static_cast<const IO*>(p.Bm) + b * bc_batch;
+  const IO* Cm_b = static_cast<const IO*>(p.Cm) + b * bc_batch;
+  const bool tile_vec = kStepMajor ? p.bc_vec_ok : p.vec_ok;
   const float* snaps = p.chunk_states + (b * p.nstates * p.D + d) * N + grp * NH;   // [B, window, D, N]
 
   float2 A2[NQ], ag[NQ], dAacc[NQ];
@@ -548,9 +591,9 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
   };
 
   // prologue: last stage's tiles and the last window's operands
-  Loader::issue(raw, Bm_b, Cm_b, (nstages - 1) * kStage, p.L, p.vec_ok);
+  Loader::issue(raw, Bm_b, Cm_b, (nstages - 1) * kStage, p.L, tile_vec, kStepMajor, p.bc_pitch);
   issue_window((int)((nwin - 1) & 1), nwin - 1);
-  Loader::finish(raw, tile[(nstages - 1) & 1]);
+  Loader::finish(raw, tile[(nstages - 1) & 1], kStepMajor);
   __syncthreads();
 
   for (long long w = nwin - 1; w >= 0; --w) {
@@ -561,7 +604,7 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
     const bool stage_head = (w % kWinPerStage) == kWinPerStage - 1 || w == nwin - 1;   // first window of a stage we process
     issue_window(wb ^ 1, w - 1);
     if (stage_head && s > 0) {
-      Loader::issue(raw, Bm_b, Cm_b, (s - 1) * kStage, p.L, p.vec_ok);
+      Loader::issue(raw, Bm_b, Cm_b, (s - 1) * kStage, p.L, tile_vec, kStepMajor, p.bc_pitch);
       asm volatile("cp.async.wait_group 2;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -685,7 +728,7 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
       if (z_row && grp == (kSplit > 2 ? 2 : 0))
         store_items<IO, G>(static_cast<IO*>(p.dz) + row, t0, p.L, p.vec_ok, dz_v);
     }
-    if (stage_head && s > 0) Loader::finish(raw, tile[tb ^ 1]);
+    if (stage_head && s > 0) Loader::finish(raw, tile[tb ^ 1], kStepMajor);
     __syncthreads();   // partials of this window and (at a stage head) the next tile are visible
     if (threadIdx.x < 64) {
       // value id l = (grp, c): c < NH -> dB[grp*NH + c], else dC[grp*NH + c - NH]; four steps per thread
@@ -725,8 +768,14 @@ __global__ void __launch_bounds__(kBwdThreads, kSplit == 2 ? 2 : 3) sscan_backwa
 template <typename IO>
 static int launch_fwd_serial(const Params& p, cudaStream_t stream) {
   dim3 grid((unsigned)((p.D + kSerialSpan - 1) / kSerialSpan), (unsigned)p.B);
-  if (p.delta_bias || p.delta_softplus) sscan_forward_serial_kernel<IO, 16, true><<<grid, kSerialLanes, 0, stream>>>(p);
-  else sscan_forward_serial_kernel<IO, 16, false><<<grid, kSerialLanes, 0, stream>>>(p);
+  const bool step = p.delta_bias || p.delta_softplus;
+  if (p.bc_step_major) {
+    if (step) sscan_forward_serial_kernel<IO, 16, true, true><<<grid, kSerialLanes, 0, stream>>>(p);
+    else sscan_forward_serial_kernel<IO, 16, false, true><<<grid, kSerialLanes, 0, stream>>>(p);
+  } else {
+    if (step) sscan_forward_serial_kernel<IO, 16, true, false><<<grid, kSerialLanes, 0, stream>>>(p);
+    else sscan_forward_serial_kernel<IO, 16, false, false><<<grid, kSerialLanes, 0, stream>>>(p);
+  }
   return check_cuda(cudaGetLastError(), "sscan_forward_serial_kernel launch");
 }
 
@@ -742,8 +791,11 @@ static int launch_bwd_serial_split(const Params& p, cudaStream_t stream) {
   constexpr int kSpan = kBwdWarps * (32 / kSplit);
   dim3 grid((unsigned)((p.D + kSpan - 1) / kSpan), (unsigned)p.B);
   const size_t smem = sizeof(BwdSmem<IO, 16, kSplit>);
-  auto kernel = (p.delta_bias || p.delta_softplus) ? sscan_backward_serial_kernel<IO, 16, kSplit, true>
-                                                   : sscan_backward_serial_kernel<IO, 16, kSplit, false>;
+  const bool step = p.delta_bias || p.delta_softplus;
+  auto kernel = p.bc_step_major ? (step ? sscan_backward_serial_kernel<IO, 16, kSplit, true, true>
+                                        : sscan_backward_serial_kernel<IO, 16, kSplit, false, true>)
+                                : (step ? sscan_backward_serial_kernel<IO, 16, kSplit, true, false>
+                                        : sscan_backward_serial_kernel<IO, 16, kSplit, false, false>);
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem)) return rc;
   kernel<<<grid, kBwdThreads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "sscan_backward_serial_kernel launch");

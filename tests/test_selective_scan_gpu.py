@@ -181,11 +181,11 @@ def test_time_contiguous_bc_is_used_in_place():
     assert torch.equal(o1, o2)
 
 
-@pytest.mark.parametrize("shape", [(2, 12, 200, 32), (1, 20, 75, 64), (2, 5, 130, 128), (1, 16, 96, 256)],
+@pytest.mark.parametrize("shape", [(2, 70, 330, 16), (2, 12, 200, 32), (1, 20, 75, 64), (2, 5, 130, 128), (1, 16, 96, 256)],
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("io", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_bc_layouts_agree(shape, io):
-    """d_state 32 .. 256 read B and C in ossm's own [B, L, N] order (dense, or as column slices of one projection
+    """d_state 16 .. 256 read B and C in ossm's own [B, L, N] order (dense, or as column slices of one projection
     with a row pitch, as the mixer holds them, mambarec.py:153-154) without a copy, and time-contiguous [B, N, L]
     views as BASELINE config 3 gives them: same kernels behind three loaders, same results (dB, dC are sums of
     float atomics, compared with a tolerance)."""
