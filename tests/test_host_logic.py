@@ -110,3 +110,34 @@ def test_selective_scan_host_checks():
         kernels.set_selective_scan_tuning("serial", 1)
     with pytest.raises(RuntimeError, match="unknown key"):
         kernels.set_selective_scan_tuning("no_such_key", 1)
+
+
+def test_selective_scan_bc_operand_choice():
+    """Which form of ossm's ``B, C [B, L, N]`` arguments reaches the library: time-contiguous views as they are,
+    step-major tensors (dense or pitched column slices of one projection, ``mambarec.py:153-154``) as they are where
+    the kernels of the state size read that order, a transposing copy otherwise."""
+
+    class Lib:
+        def __init__(self, sizes):
+            self.sizes = sizes
+
+        def ossm_b200_selective_scan_step_major_bc(self, n):
+            return 1 if n in self.sizes else 0
+
+    lib = Lib({16, 32, 64, 128, 256})
+    Bz, L, N = 2, 10, 32
+    dense = torch.randn(Bz, L, N)
+    b, c, pitch = kernels._bc_operands(lib, dense, dense.clone(), N)
+    assert pitch == N and b.data_ptr() == dense.data_ptr() and tuple(b.shape) == (Bz, L, N)
+    proj = torch.randn(Bz, L, 4 + 2 * N)
+    b, c, pitch = kernels._bc_operands(lib, proj[..., 4:4 + N], proj[..., 4 + N:], N)
+    assert pitch == 4 + 2 * N and b.data_ptr() == proj[..., 4:].data_ptr() and c.data_ptr() == proj[..., 4 + N:].data_ptr()
+    held = torch.randn(Bz, N, L)                                   # time-contiguous, passed as a transposed view
+    b, c, pitch = kernels._bc_operands(lib, held.transpose(1, 2), held.transpose(1, 2), N)
+    assert pitch == 0 and b.data_ptr() == held.data_ptr() and tuple(b.shape) == (Bz, N, L)
+    # different pitches of B and C: dense copies in step-major order
+    b, c, pitch = kernels._bc_operands(lib, proj[..., 4:4 + N], dense, N)
+    assert pitch == N and b.is_contiguous() and c.is_contiguous() and torch.equal(b, proj[..., 4:4 + N])
+    # a state size whose kernels want [B, N, L]: transposing copy
+    b, c, pitch = kernels._bc_operands(Lib(set()), dense, dense, N)
+    assert pitch == 0 and tuple(b.shape) == (Bz, N, L) and b.is_contiguous() and torch.equal(b, dense.transpose(1, 2))
