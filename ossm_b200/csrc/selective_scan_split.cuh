@@ -117,8 +117,10 @@ __device__ __forceinline__ void group_owned_steps(int S, int sub, int& first, in
   }
 }
 
-template <typename IO, bool kStep>
-__global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(Params p) {
+// kMinCtas: resident CTAs per SM the register allocation leaves room for -- 4 (64 registers) is faster from 64 states
+// on, 3 (80 registers) at 32 states, where a warp carries eight channels and the per-group work per lane is largest.
+template <typename IO, bool kStep, int kMinCtas>
+__global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_kernel(Params p) {
   extern __shared__ __align__(16) float split_tile[];            // [steps][2 N]
   constexpr int G = kSplitGroup;
   const int N = (int)p.N;
@@ -290,18 +292,25 @@ __global__ void __launch_bounds__(kSplitThreads, 3) sscan_forward_split_kernel(P
 static bool split_ok(long long N) { return N == 32 || N == 64 || N == 128 || N == 256; }
 static bool split_bwd_ok(long long N) { return split_ok(N); }
 
+static int g_split_fwd_four_ctas_from = 64;   // state sizes from which the forward is built for four CTAs per SM (measured)
+
 template <typename IO>
 static int launch_fwd_split(const Params& p, cudaStream_t stream) {
   const int per_cta = kSplitWarps * (32 / (int)(p.N / kSplitStates));
   dim3 grid((unsigned)((p.D + per_cta - 1) / per_cta), (unsigned)p.B);
   const size_t smem = kSplitTileFloats * sizeof(float);
-  if (p.delta_bias || p.delta_softplus) {
-    if (int rc = set_smem(sscan_forward_split_kernel<IO, true>, smem)) return rc;
-    sscan_forward_split_kernel<IO, true><<<grid, kSplitThreads, smem, stream>>>(p);
-  } else {
-    if (int rc = set_smem(sscan_forward_split_kernel<IO, false>, smem)) return rc;
-    sscan_forward_split_kernel<IO, false><<<grid, kSplitThreads, smem, stream>>>(p);
-  }
+  const bool step = p.delta_bias || p.delta_softplus;
+  auto launch = [&](auto kernel) -> int {
+    if (int rc = set_smem(kernel, smem)) return rc;
+    kernel<<<grid, kSplitThreads, smem, stream>>>(p);
+    return kOk;
+  };
+  int rc;
+  if (p.N >= g_split_fwd_four_ctas_from)
+    rc = step ? launch(sscan_forward_split_kernel<IO, true, 4>) : launch(sscan_forward_split_kernel<IO, false, 4>);
+  else
+    rc = step ? launch(sscan_forward_split_kernel<IO, true, 3>) : launch(sscan_forward_split_kernel<IO, false, 3>);
+  if (rc) return rc;
   return check_cuda(cudaGetLastError(), "sscan_forward_split_kernel launch");
 }
 
