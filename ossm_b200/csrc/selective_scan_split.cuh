@@ -757,7 +757,7 @@ static int g_split_flush_parts = 0;         // threads sharing the rows of one f
 template <typename IO>
 static int launch_bwd_split(const Params& p, cudaStream_t stream) {
   Params q = p;
-  // fewer threads per item mean fewer vector atomics: 32 / 64 states ran fastest with 2, 128 / 256 with 1
-  q.split_flush_parts = g_split_flush_parts > 0 ? g_split_flush_parts : (q.N >= 128 ? 1 : 2);
+  // fewer threads per item mean fewer vector atomics: 32 states ran fastest with 4, 64 / 128 with 2, 256 with 1
+  q.split_flush_parts = g_split_flush_parts > 0 ? g_split_flush_parts : (q.N <= 32 ? 4 : (q.N <= 128 ? 2 : 1));
   return q.N >= g_split_bwd_wide_from ? launch_bwd_split_w<IO, 8>(q, stream) : launch_bwd_split_w<IO, 4>(q, stream);
 }
