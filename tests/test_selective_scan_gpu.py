@@ -115,13 +115,14 @@ def test_mixer_shaped_scan_with_256_states():
     out, grads = run_autograd(case)
     ref_out, ref_grads = oracle_case(case)
     np.testing.assert_allclose(out.cpu().numpy(), ref_out, rtol=1e-4, atol=5e-5)
+    record("mamba d_state 256 f32", "out", so.max_rel_err(out.cpu().numpy(), ref_out), 1e-4)
     for name, got, want in zip(NAMES, grads, ref_grads):
-        assert so.max_rel_err(got.cpu().numpy(), want) <= 1e-4, name
+        assert record("mamba d_state 256 f32", name, so.max_rel_err(got.cpu().numpy(), want), 1e-4) <= 1e-4, name
     out, grads = run_autograd(case, io=torch.bfloat16)
     ref_out, ref_grads = oracle_case(case, io=torch.bfloat16)
-    assert so.max_rel_err(out.float().cpu().numpy(), ref_out) <= 2e-2
+    assert record("mamba d_state 256 bf16", "out", so.max_rel_err(out.float().cpu().numpy(), ref_out), 2e-2) <= 2e-2
     for name, got, want in zip(NAMES, grads, ref_grads):
-        assert so.max_rel_err(got.float().cpu().numpy(), want) <= 2e-2, name
+        assert record("mamba d_state 256 bf16", name, so.max_rel_err(got.float().cpu().numpy(), want), 2e-2) <= 2e-2, name
 
 
 SHAPES = [
