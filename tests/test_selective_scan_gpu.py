@@ -129,6 +129,7 @@ SHAPES = [
     (1, 1, 1, 1), (2, 3, 7, 4), (1, 5, 255, 16), (2, 9, 256, 16), (1, 70, 257, 16),   # around one chunk, ragged D
     (2, 64, 600, 16), (1, 8, 300, 32), (1, 4, 200, 64), (1, 3, 100, 48), (3, 130, 33, 8),
     (1, 3, 70, 65), (2, 20, 100, 96), (1, 4, 64, 130), (1, 9, 40, 255),     # several state tiles in the backward
+    (1, 3, 5, 32), (2, 2, 33, 256), (1, 17, 9, 128), (1, 1, 1, 64),          # split kernels: shorter than a window / a chunk
 ]
 
 
