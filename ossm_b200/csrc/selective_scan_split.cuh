@@ -119,13 +119,20 @@ __device__ __forceinline__ void group_owned_steps(int S, int sub, int& first, in
 
 // kMinCtas: resident CTAs per SM the register allocation leaves room for -- 4 (64 registers) is faster from 64 states
 // on, 3 (80 registers) at 32 states, where a warp carries eight channels and the per-group work per lane is largest.
-template <typename IO, bool kStep, int kMinCtas>
+// kKeep16: a 16-bit I/O type keeps its tile in that type (half the shared-memory reads, eight unpacking instructions
+// per step): faster from 128 states on (N=256: 15.8 against 18.1 ms), slower below.
+template <typename IO, bool kStep, int kMinCtas, bool kKeep16>
 __global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_kernel(Params p) {
   extern __shared__ __align__(16) float split_tile[];            // [steps][2 N]
   constexpr int G = kSplitGroup;
   const int N = (int)p.N;
   const int S = N / kSplitStates;                                // lanes per channel
-  const int tile_steps = kSplitTileFloats / (2 * N);             // 16 .. 128, a multiple of 8
+  // the tile keeps the I/O type: float32 as [step][B|C][half][lane][4], a 16-bit type as [step][B|C][state] (a lane's
+  // eight states are one 16-byte read) with twice the steps in the same 32 KiB
+  constexpr bool kTile16 = sizeof(IO) == 2 && kKeep16;
+  constexpr int kTileElems = kTile16 ? 2 * kSplitTileFloats : kSplitTileFloats;
+  IO* tile16 = reinterpret_cast<IO*>(split_tile);
+  const int tile_steps = kTileElems / (2 * N);                   // 16 .. 256, a multiple of 8
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % S;                                      // which 8 states of the channel
   const int per_warp = 32 / S;
@@ -168,7 +175,7 @@ __global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_k
       // straight to their place in the tile
       const int lgP = 31 - __clz(N) - (kVec == 8 ? 3 : 2);       // log2 of the pieces per row
 #pragma unroll 4
-      for (int i = threadIdx.x; i < kSplitTileFloats / kVec; i += kSplitThreads) {
+      for (int i = threadIdx.x; i < kTileElems / kVec; i += kSplitThreads) {
         const int g = i & ((1 << lgP) - 1), wc = (i >> lgP) & 1, st = i >> (lgP + 1);
         const long long t = t_tile + st;
         uint4 raw = make_uint4(0u, 0u, 0u, 0u);
@@ -183,9 +190,11 @@ __global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_k
           }
         }
         float* dstp = split_tile + (size_t)st * 2 * N + wc * N;
-        if constexpr (kVec == 4) {             // states 4g .. 4g+3: lane g >> 1, half g & 1
+        if constexpr (kTile16) {               // states 8g .. 8g+7 as they are
+          *reinterpret_cast<uint4*>(tile16 + (size_t)st * 2 * N + wc * N + g * 8) = raw;
+        } else if constexpr (kVec == 4) {      // states 4g .. 4g+3: lane g >> 1, half g & 1
           *reinterpret_cast<uint4*>(dstp + ((((g & 1) * S) + (g >> 1)) << 2)) = raw;
-        } else {                               // states 8g .. 8g+7: lane g, both halves
+        } else {                               // states 8g .. 8g+7: lane g, both halves, as float32
           const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
           *reinterpret_cast<float4*>(dstp + (g << 2)) =
               make_float4(__uint_as_float(wv[0] << 16), __uint_as_float(wv[0] & 0xffff0000u),
@@ -194,6 +203,22 @@ __global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_k
               make_float4(__uint_as_float(wv[2] << 16), __uint_as_float(wv[2] & 0xffff0000u),
                           __uint_as_float(wv[3] << 16), __uint_as_float(wv[3] & 0xffff0000u));
         }
+      }
+    } else if constexpr (kTile16) {
+      for (int i = threadIdx.x; i < 2 * N * (tile_steps / kVec); i += kSplitThreads) {
+        const int r = i & (2 * N - 1), cv = i >> (32 - __clz(N));      // N is a power of two
+        const long long t = t_tile + (long long)kVec * cv;
+        const IO* src = (r < N ? Bm_b + (long long)r * p.L : Cm_b + (long long)(r - N) * p.L);
+        uint4 raw;
+        IO* e = reinterpret_cast<IO*>(&raw);
+        if (p.bc_vec_ok && t + kVec <= p.L) {
+          raw = *reinterpret_cast<const uint4*>(src + t);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) e[j] = (t + j < p.L) ? src[t + j] : IO(0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) tile16[(kVec * cv + j) * 2 * N + r] = e[j];
       }
     } else
     for (int i = threadIdx.x; i < 2 * N * (tile_steps / kVec); i += kSplitThreads) {
@@ -249,14 +274,27 @@ __global__ void __launch_bounds__(kSplitThreads, kMinCtas) sscan_forward_split_k
       }
       float y[G];
       const float* steps = split_tile + (size_t)(gi * G) * 2 * N + sub * 4;
+      const IO* steps16 = tile16 + (size_t)(gi * G) * 2 * N + sub * 8;
 #pragma unroll
       for (int j = 0; j < G; ++j) {
-        const float4 b0 = *reinterpret_cast<const float4*>(steps + j * 2 * N);
-        const float4 b1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + 4 * S);
-        const float4 c0 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N);
-        const float4 c1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N + 4 * S);
-        const float2 Bp[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
-        const float2 Cp[4] = {make_float2(c0.x, c0.y), make_float2(c0.z, c0.w), make_float2(c1.x, c1.y), make_float2(c1.z, c1.w)};
+        float2 Bp[4], Cp[4];
+        if constexpr (kTile16) {
+          const uint4 x = *reinterpret_cast<const uint4*>(steps16 + j * 2 * N);
+          const uint4 y = *reinterpret_cast<const uint4*>(steps16 + j * 2 * N + N);
+          const uint32_t bw[4] = {x.x, x.y, x.z, x.w}, cw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Bp[q] = make_float2(__uint_as_float(bw[q] << 16), __uint_as_float(bw[q] & 0xffff0000u));
+            Cp[q] = make_float2(__uint_as_float(cw[q] << 16), __uint_as_float(cw[q] & 0xffff0000u));
+          }
+        } else {
+          const float4 b0 = *reinterpret_cast<const float4*>(steps + j * 2 * N);
+          const float4 b1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + 4 * S);
+          const float4 c0 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N);
+          const float4 c1 = *reinterpret_cast<const float4*>(steps + j * 2 * N + N + 4 * S);
+          Bp[0] = make_float2(b0.x, b0.y); Bp[1] = make_float2(b0.z, b0.w); Bp[2] = make_float2(b1.x, b1.y); Bp[3] = make_float2(b1.z, b1.w);
+          Cp[0] = make_float2(c0.x, c0.y); Cp[1] = make_float2(c0.z, c0.w); Cp[2] = make_float2(c1.x, c1.y); Cp[3] = make_float2(c1.z, c1.w);
+        }
         const float2 dtv = splat(dt_c[j]);
         const float2 dtu = splat(dt_c[j] * u_c[j]);
         float2 acc = make_float2(0.f, 0.f);
@@ -293,6 +331,7 @@ static bool split_ok(long long N) { return N == 32 || N == 64 || N == 128 || N =
 static bool split_bwd_ok(long long N) { return split_ok(N); }
 
 static int g_split_fwd_four_ctas_from = 64;   // state sizes from which the forward is built for four CTAs per SM (measured)
+static int g_split_fwd_keep16_from = 128;     // state sizes from which a 16-bit I/O type keeps its tile in that type (measured)
 
 template <typename IO>
 static int launch_fwd_split(const Params& p, cudaStream_t stream) {
@@ -306,10 +345,12 @@ static int launch_fwd_split(const Params& p, cudaStream_t stream) {
     return kOk;
   };
   int rc;
-  if (p.N >= g_split_fwd_four_ctas_from)
-    rc = step ? launch(sscan_forward_split_kernel<IO, true, 4>) : launch(sscan_forward_split_kernel<IO, false, 4>);
+  if (sizeof(IO) == 2 && p.N >= g_split_fwd_keep16_from)
+    rc = step ? launch(sscan_forward_split_kernel<IO, true, 4, true>) : launch(sscan_forward_split_kernel<IO, false, 4, true>);
+  else if (p.N >= g_split_fwd_four_ctas_from)
+    rc = step ? launch(sscan_forward_split_kernel<IO, true, 4, false>) : launch(sscan_forward_split_kernel<IO, false, 4, false>);
   else
-    rc = step ? launch(sscan_forward_split_kernel<IO, true, 3>) : launch(sscan_forward_split_kernel<IO, false, 3>);
+    rc = step ? launch(sscan_forward_split_kernel<IO, true, 3, false>) : launch(sscan_forward_split_kernel<IO, false, 3, false>);
   if (rc) return rc;
   return check_cuda(cudaGetLastError(), "sscan_forward_split_kernel launch");
 }
