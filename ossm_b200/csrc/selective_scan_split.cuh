@@ -11,7 +11,8 @@
 //
 // A CTA is 8 warps = 256 / S channels of one batch element; B_t / C_t tiles of 4096 / N steps are transposed into
 // shared memory as float32 [step][B | C][half][lane][4] and read back with 16-byte loads (neighbouring lanes 16 bytes
-// apart).  u, dt arrive as one 8-step vector per row and group; the lane that ends up with a step's output after the
+// apart); a 16-bit I/O type keeps the tile in that type from 128 states on ([step][B | C][state], a lane's eight
+// states one 16-byte read, twice the steps per tile).  u, dt arrive as one 8-step vector per row and group; the lane that ends up with a step's output after the
 // exchange gates and stores it (staging u, dt, z one group ahead with asynchronous copies, as the backward does per
 // chunk, was measured 5-10 % slower here: three resident CTAs already cover that latency).  The state entering
 // every p.state_interval steps is saved in the layout the time-parallel backward reads ([B, D, L / interval, N]).
